@@ -1,0 +1,527 @@
+#!/usr/bin/env python
+"""Benchmark of the GEMM hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
+
+A step is one pass of the hot path over one batch of synthetic input.  The
+default workload is the large bf16 GEMM (M=32768, N=16384, K=8192, A row-major,
+B column-major, fp32 accumulation, bf16 output), the configuration the metric
+"GEMM TFLOP/s at 1/2/4/8 GPUs" is quoted on; with N > 1 ranks (torchrun, one
+process per GPU) A and C are sharded by row blocks, B is broadcast once over
+NCCL before the timed region, and no collective runs inside a step (strong
+scaling: total work fixed).
+
+One JSON line is printed by rank 0:
+  value     whole-job TFLOP/s with operands resident in HBM (CUDA events, max over ranks)
+  e2e       the same through the C ABI with pinned HOST buffers (H2D + kernel + D2H timed)
+  roofline  algorithmic FLOPs per launch / measured launch time against the measured peak
+  cpu_baseline  the reference's CPU kernel timed on this box's host cores (bounded sample)
+  sweep     short timings of the other workloads (fp32 FFMA / 3xTF32 SGEMM, int8, conv)
+
+--impl reference times the reference's own CPU implementation (its generated
+AVX-512 C when available, else the C restatement) on all host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "gemm_tflops"
+UNIT = "TFLOP/s"
+
+BF16_SHAPE = (32768, 16384, 8192)
+SUBBLOCK = 2048  # CPU sample: the 2048^3 sub-block of the bf16 problem, in fp32
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        p["source"] = "measured"
+        return p
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+# ------------------------------------------------------------------ clocks
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while a timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.gpu), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append((time.time(), line.strip()))
+
+    def stop(self, t0: float, t1: float):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        rows = [l for (t, l) in self.lines if t0 <= t <= t1 + 0.2] or [l for (_, l) in self.lines]
+        sm, mx, reasons, power = [], [], set(), []
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for l in rows:
+            parts = [p.strip() for p in l.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+                power.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, v in zip(names, parts[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": max(mx), "power_w_max": max(power),
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ---------------------------------------------------------- CPU reference
+def _cpu_inputs():
+    """The 2048^3 sub-block of the bf16 problem as the reference sees it: bf16
+    values N(0,1)*0.02 widened exactly to fp32, B transposed to row-major."""
+    import numpy as np
+
+    from tests import inputs
+
+    A = inputs.bf16_bits_to_f32(inputs.normal_bf16(1, (SUBBLOCK, SUBBLOCK)))
+    B = np.ascontiguousarray(inputs.bf16_bits_to_f32(inputs.normal_bf16(2, (SUBBLOCK, SUBBLOCK))).T)
+    return A, B
+
+
+_W = {}
+
+
+def _worker_init(kind):
+    import oracle
+
+    _W["kind"] = kind
+    _W["impl"] = oracle.ref() if kind == "reference" else oracle.port()
+
+
+def _worker_run(args):
+    import numpy as np
+
+    r0, r1 = args
+    A, B = _W["A"], _W["B"]
+    C = np.zeros((r1 - r0, B.shape[1]), np.float32)
+    _W["impl"].sgemm(np.ascontiguousarray(A[r0:r1]), B, C)
+    return float(C[0, 0])
+
+
+def cpu_reference_kind():
+    import oracle
+
+    return "reference" if oracle.ref_available() else "port"
+
+
+def run_cpu_single_core(budget_s=10.0):
+    """cpu_baseline leg: one host core (the generated sgemm_exo keeps its tiles in
+    function statics, so it is single-threaded by construction)."""
+    import numpy as np
+
+    import oracle
+
+    kind = cpu_reference_kind()
+    impl = oracle.ref() if kind == "reference" else oracle.port()
+    A, B = _cpu_inputs()
+    C = np.zeros((SUBBLOCK, SUBBLOCK), np.float32)
+    impl.sgemm(A, B, C)  # warm-up
+    times = []
+    t_start = time.perf_counter()
+    while time.perf_counter() - t_start < budget_s and len(times) < 50:
+        C[:] = 0
+        t0 = time.perf_counter()
+        impl.sgemm(A, B, C)
+        times.append(time.perf_counter() - t0)
+    times.sort()
+    med = times[len(times) // 2]
+    return {"value": 2.0 * SUBBLOCK ** 3 / med / 1e12, "unit": UNIT, "cores": 1, "kind": kind,
+            "sample": f"{SUBBLOCK}^3 fp32 sub-block of the bf16 problem (bf16-rounded inputs), "
+                      f"median of {len(times)} runs, {sum(times):.1f} s of CPU work"}
+
+
+def run_reference_arm(args):
+    """--impl reference: the reference CPU kernel on all host cores.  Rows are
+    independent, so P processes each run sgemm_exo on a row block (processes, not
+    threads: the generated code is not reentrant)."""
+    import multiprocessing as mp
+
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    kind = cpu_reference_kind()
+    cores = len(os.sched_getaffinity(0))
+    A, B = _cpu_inputs()
+    _W["A"], _W["B"] = A, B
+    ctx = mp.get_context("fork")
+    blocks = [(i * SUBBLOCK // cores, (i + 1) * SUBBLOCK // cores) for i in range(cores)]
+    with ctx.Pool(cores, initializer=_worker_init, initargs=(kind,)) as pool:
+        for _ in range(args.warmup):
+            pool.map(_worker_run, blocks)
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            pool.map(_worker_run, blocks)
+        dt = time.perf_counter() - t0
+    ms = dt / args.steps * 1e3
+    value = 2.0 * SUBBLOCK ** 3 / (ms / 1e3) / 1e12
+    sample = (f"each step = the {SUBBLOCK}^3 fp32 sub-block of the bf16 problem (bf16-rounded inputs), "
+              f"row-sharded over {cores} processes")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config("bf16", args.gpus),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": kind, "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------- workloads
+def workload_config(name, gpus):
+    if name == "bf16":
+        M, N, K = BF16_SHAPE
+        return {"workload": f"bf16 GEMM M={M} N={N} K={K}, A row-major, B column-major, fp32 accumulate, bf16 out",
+                "sharding": f"A/C row blocks over {gpus} GPU(s), B broadcast once (NCCL) outside the timed region",
+                "l2": "inputs (768 MB) larger than L2; no flush needed"}
+    return {"workload": name}
+
+
+class Workload:
+    """flops per step, a device-resident step, and a host-buffer (e2e) step."""
+
+    def __init__(self, name, lib, torch, rank, world):
+        self.name, self.lib, self.torch, self.rank, self.world = name, lib, torch, rank, world
+        self.launches_per_step = 1
+        getattr(self, f"_setup_{name}")()
+
+    # -- bf16 headline
+    def _setup_bf16(self):
+        t = self.torch
+        M, N, K = BF16_SHAPE
+        self.dtype = "bf16"
+        rows = M // self.world
+        self.shape = (rows, N, K)
+        g = t.Generator(device="cuda").manual_seed(1234 + self.rank)
+        self.A = (t.randn((rows, K), generator=g, device="cuda") * 0.02).to(t.bfloat16)
+        self.B = t.empty((N, K), dtype=t.bfloat16, device="cuda")  # column-major K x N
+        if self.rank == 0:
+            gb = t.Generator(device="cuda").manual_seed(99)
+            self.B.copy_((t.randn((N, K), generator=gb, device="cuda") * 0.02).to(t.bfloat16))
+        self.C = t.empty((rows, N), dtype=t.bfloat16, device="cuda")
+        self.flops_total = 2.0 * M * N * K
+        self.flops_local = 2.0 * rows * N * K
+        self.bound = "tensor"
+
+    def step_bf16(self):
+        r, N, K = self.shape
+        self.lib.gemm_bf16_exo(None, r, N, K, self.A, self.B, self.C)
+
+    def host_bf16(self):
+        t = self.torch
+        self.hA = t.empty(self.A.shape, dtype=self.A.dtype, pin_memory=True).copy_(self.A)
+        self.hB = t.empty(self.B.shape, dtype=self.B.dtype, pin_memory=True).copy_(self.B)
+        self.hC = t.empty(self.C.shape, dtype=self.C.dtype, pin_memory=True)
+        return (self.hA.numel() + self.hB.numel()) * 2, self.hC.numel() * 2
+
+    def e2e_bf16(self):
+        r, N, K = self.shape
+        self.lib.gemm_bf16_exo(None, r, N, K, self.hA, self.hB, self.hC)
+
+    # -- fp32 SGEMM 8192^3 (FFMA exact / 3xTF32)
+    def _setup_sgemm(self, n=8192):
+        t = self.torch
+        self.dtype = "f32"
+        self.shape = (n, n, n)
+        g = t.Generator(device="cuda").manual_seed(5)
+        self.A = t.rand((n, n), generator=g, device="cuda") * 2 - 1
+        self.B = t.rand((n, n), generator=g, device="cuda") * 2 - 1
+        self.C = t.zeros((n, n), device="cuda")
+        self.flops_total = self.flops_local = 2.0 * n ** 3
+        self.bound = "tensor"
+
+    _setup_sgemm_ffma = _setup_sgemm
+
+    def _setup_sgemm_3xtf32(self):
+        self._setup_sgemm()
+        self.launches_per_step = 3  # two split pre-passes + the GEMM
+
+    def step_sgemm_ffma(self):
+        n = self.shape[0]
+        self.lib.sgemm_exo_ffma(None, n, n, n, self.A, self.B, self.C)
+
+    def step_sgemm_3xtf32(self):
+        n = self.shape[0]
+        self.lib.sgemm_exo_3xtf32(None, n, n, n, self.A, self.B, self.C)
+
+    def host_sgemm(self):
+        t = self.torch
+        self.hA = t.empty(self.A.shape, pin_memory=True).copy_(self.A)
+        self.hB = t.empty(self.B.shape, pin_memory=True).copy_(self.B)
+        self.hC = t.zeros(self.C.shape).pin_memory()
+        return (self.hA.numel() + self.hB.numel() + self.hC.numel()) * 4, self.hC.numel() * 4
+
+    host_sgemm_ffma = host_sgemm_3xtf32 = host_sgemm
+
+    def e2e_sgemm_ffma(self):
+        n = self.shape[0]
+        self.lib.sgemm_exo_ffma(None, n, n, n, self.hA, self.hB, self.hC)
+
+    def e2e_sgemm_3xtf32(self):
+        n = self.shape[0]
+        self.lib.sgemm_exo_3xtf32(None, n, n, n, self.hA, self.hB, self.hC)
+
+    # -- int8 4096^3
+    def _setup_i8(self, n=4096):
+        t = self.torch
+        self.dtype = "i8"
+        self.shape = (n, n, n)
+        g = t.Generator(device="cuda").manual_seed(6)
+        self.A = t.randint(-128, 128, (n, n), generator=g, device="cuda", dtype=t.int8)
+        self.B = t.randint(-128, 128, (n, n), generator=g, device="cuda", dtype=t.int8)
+        self.C = t.empty((n, n), dtype=t.int8, device="cuda")
+        self.flops_total = self.flops_local = 2.0 * n ** 3
+        self.bound = "tensor"
+        self.launches_per_step = 2  # B transpose pre-pass + the GEMM
+
+    def step_i8(self):
+        n = self.shape[0]
+        self.lib.matmul_on_cpu(None, n, n, n, 1.0 / 256, False, self.A, self.B, self.C)
+
+    def host_i8(self):
+        t = self.torch
+        self.hA = t.empty(self.A.shape, dtype=t.int8, pin_memory=True).copy_(self.A)
+        self.hB = t.empty(self.B.shape, dtype=t.int8, pin_memory=True).copy_(self.B)
+        self.hC = t.empty(self.C.shape, dtype=t.int8, pin_memory=True)
+        return self.hA.numel() + self.hB.numel(), self.hC.numel()
+
+    def e2e_i8(self):
+        n = self.shape[0]
+        self.lib.matmul_on_cpu(None, n, n, n, 1.0 / 256, False, self.hA, self.hB, self.hC)
+
+    # -- fp32 conv: batch 4, 56x56, 64->64, 3x3, pad 1 (implicit GEMM, exact)
+    def _setup_conv(self):
+        t = self.torch
+        self.dtype = "f32"
+        g = t.Generator(device="cuda").manual_seed(8)
+        self.cv = (4, 56, 56, 64, 64, 3, 1)
+        b, h, w, ci, co, k, pad = self.cv
+        self.A = t.rand((b, h, w, ci), generator=g, device="cuda") * 2 - 1
+        self.B = t.rand((k, k, ci, co), generator=g, device="cuda") * 2 - 1
+        self.bias = t.rand((co,), generator=g, device="cuda") * 2 - 1
+        self.C = t.empty((b, h, w, co), device="cuda")
+        self.flops_total = self.flops_local = 2.0 * b * h * w * co * k * k * ci
+        self.bound = "tensor"
+
+    def step_conv(self):
+        b, h, w, ci, co, k, pad = self.cv
+        self.lib.conv_nhwc_exo(None, b, h, w, ci, co, k, pad, True, self.A, self.C, self.B, self.bias)
+
+    def step(self):
+        getattr(self, f"step_{self.name}")()
+
+    def host(self):
+        return getattr(self, f"host_{self.name}")()
+
+    def e2e_step(self):
+        getattr(self, f"e2e_{self.name}")()
+
+
+def time_steps(torch, fn, steps, warmup, dist=None):
+    """CUDA events on the launching stream, barrier + synchronize on both sides,
+    max over ranks."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+        torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.time()
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    t1 = time.time()
+    ms = e0.elapsed_time(e1)
+    if dist is not None:
+        dist.barrier()
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return ms / steps, t0, t1
+
+
+def run_ours(args):
+    import torch
+
+    import exo_b200
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist_mod.init_process_group("nccl", device_id=torch.device("cuda", local))
+        dist = dist_mod
+    lib = exo_b200.library()
+    peaks = measured_peaks()
+
+    wl = Workload(args.workload, lib, torch, rank, world)
+    bcast_ms = None
+    if dist is not None:
+        # the one exchange of the sharded GEMM: B from rank 0 to every GPU over NVLink
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        dist.broadcast(wl.B, src=0)
+        e1.record()
+        torch.cuda.synchronize()
+        bcast_ms = e0.elapsed_time(e1)
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    ms, t0, t1 = time_steps(torch, wl.step, args.steps, args.warmup, dist)
+    clocks = sampler.stop(t0, t1) if rank == 0 else None
+    lib.synchronize()
+    value = wl.flops_total / (ms / 1e3) / 1e12
+
+    # end to end: pinned host buffers through the C ABI, copies inside the timed region
+    h2d, d2h = wl.host()
+    e2e_steps = max(1, min(args.steps, 5))
+    e2e_ms, _, _ = time_steps(torch, wl.e2e_step, e2e_steps, 1, dist)
+    e2e_value = wl.flops_total / (e2e_ms / 1e3) / 1e12
+
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    peak = peaks["bf16_tflops"]
+    per_launch_tflops = wl.flops_local / (ms / 1e3) / 1e12
+    roofline = {"bound": "tensor", "achieved": per_launch_tflops, "peak": peak, "unit": "TFLOP/s",
+                "frac": per_launch_tflops / peak, "traffic": None,
+                "peak_source": f"{peaks['source']} bf16 burst (sustained: {peaks.get('bf16_tflops_sustained')})",
+                "kernel": "gemm_tc_kernel<bf16>" if args.workload == "bf16" else args.workload}
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic",
+        "config": workload_config(args.workload, world), "clocks": clocks,
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": d2h * world,
+                "ms_per_step": e2e_ms, "steps": e2e_steps},
+        "gpu_launches": wl.launches_per_step * args.steps,
+        "roofline": roofline,
+    }
+    if bcast_ms is not None:
+        line["b_broadcast_ms"] = bcast_ms
+    if world == 1:
+        del wl
+        torch.cuda.empty_cache()
+        if not args.no_sweep:
+            line["sweep"] = run_sweep(lib, torch, peaks, args.workload)
+        if not args.no_cpu:
+            line["cpu_baseline"] = run_cpu_single_core()
+    print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def run_sweep(lib, torch, peaks, skip):
+    """Short device-resident timings of the other workloads (5 steps each)."""
+    out = {}
+    sm_count = torch.cuda.get_device_properties(0).multi_processor_count
+    simt_peak = sm_count * 128 * 2 * 1.965e9 / 1e12  # fp32 FFMA at max SM clock
+    for name in ("sgemm_ffma", "sgemm_3xtf32", "i8", "conv", "bf16"):
+        if name == skip:
+            continue
+        try:
+            wl = Workload(name, lib, torch, 0, 1)
+            ms, _, _ = time_steps(torch, wl.step, 5, 3)
+            lib.synchronize()
+            tf = wl.flops_total / (ms / 1e3) / 1e12
+            if name in ("sgemm_ffma", "conv"):
+                peak, pname = simt_peak, "fp32 SIMT at max SM clock (computed)"
+            elif name == "sgemm_3xtf32":
+                peak, pname = peaks["bf16_tflops"] / 2 / 3, "bf16 measured / 2 (tf32) / 3 (three MMAs per product)"
+            elif name == "i8":
+                peak, pname = peaks["bf16_tflops"] * 2, "2 x bf16 measured (nominal int8 ratio)"
+            else:
+                peak, pname = peaks["bf16_tflops"], "bf16 measured"
+            out[name] = {"tflops": tf, "ms": ms, "peak": peak, "frac": tf / peak, "peak_is": pname,
+                         "launches_per_step": wl.launches_per_step}
+            del wl
+            torch.cuda.empty_cache()
+        except Exception as e:  # a failing side workload must not lose the headline line
+            out[name] = {"error": str(e)[:200]}
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="bf16", choices=["bf16", "sgemm_ffma", "sgemm_3xtf32", "i8"])
+    ap.add_argument("--no-sweep", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

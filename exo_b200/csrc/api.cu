@@ -1,0 +1,309 @@
+// The C-ABI entry points: argument checks, host/device operand staging, and
+// the choice of kernel.  Every computation runs on the GPU; an entry point that
+// cannot reach a device reports an error through exo_b200_last_error() and
+// leaves its output untouched -- there is no CPU path.
+#include <cstdlib>
+#include <cstring>
+
+#include "common.cuh"
+#include "kernels.cuh"
+
+using namespace exob200;
+
+namespace {
+
+bool bad_args(const char* fn, bool cond, const char* what) {
+  if (!cond) return false;
+  set_error(EXO_B200_ERR_INVALID_ARGUMENT, std::string(fn) + ": " + what);
+  return true;
+}
+
+// ---------------------------------------------------------------- SGEMM
+void sgemm_dispatch(const char* fn, void* ctxt, int path, int_fast32_t M, int_fast32_t N, int_fast32_t K,
+                    const float* A, const float* B, float* C) {
+  clear_error();
+  if (bad_args(fn, M < 1 || N < 1 || K < 1, "M, N, K must be >= 1")) return;
+  if (bad_args(fn, !A || !B || !C, "NULL tensor")) return;
+  exo_b200_Context* c = resolve_context(ctxt);
+  if (!c) return;
+  if (path < 0) path = c->sgemm_path;
+  Operand a, b, cc;
+  if (!stage_in(c, 0, A, sizeof(float) * (size_t)M * K, true, &a)) return;
+  if (!stage_in(c, 1, B, sizeof(float) * (size_t)K * N, true, &b)) return;
+  if (!stage_in(c, 2, C, sizeof(float) * (size_t)M * N, true, &cc)) return;  // C is read: +=
+  const float* dA = static_cast<const float*>(a.dev);
+  const float* dB = static_cast<const float*>(b.dev);
+  float* dC = static_cast<float*>(cc.dev);
+  cudaError_t e;
+  if (path == EXO_B200_SGEMM_3XTF32 && tc_supported_tf32(M, N, K, dA, dB, dC))
+    e = launch_sgemm_3xtf32_tc(c, M, N, K, dA, dB, dC);
+  else
+    e = launch_sgemm_ffma(c->stream, M, N, K, dA, dB, dC);
+  if (!check_cuda(e, fn)) return;
+  if (!stage_out(c, cc)) return;
+  finish(c, a.staged || b.staged || cc.staged);
+}
+
+// ----------------------------------------------------------------- conv
+void conv_dispatch(const char* fn, void* ctxt, const ConvShape& s, const float* inp, float* output,
+                   const float* weights, const float* bias) {
+  clear_error();
+  if (bad_args(fn, s.batch < 1 || s.in_h < 1 || s.in_w < 1 || s.in_c < 1 || s.out_c < 1 || s.kdim < 1 ||
+                       s.pad < 0 || s.out_h < 1 || s.out_w < 1,
+               "sizes must be >= 1 (pad >= 0) and the kernel must fit the padded input"))
+    return;
+  if (bad_args(fn, !inp || !output || !weights, "NULL tensor")) return;
+  exo_b200_Context* c = resolve_context(ctxt);
+  if (!c) return;
+  Operand i, o, w, b;
+  const size_t in_elems = (size_t)s.batch * s.in_h * s.in_w * s.in_c;
+  const size_t out_elems = (size_t)s.batch * s.out_h * s.out_w * s.out_c;
+  const size_t w_elems = (size_t)s.kdim * s.kdim * s.in_c * s.out_c;
+  if (!stage_in(c, 0, inp, sizeof(float) * in_elems, true, &i)) return;
+  if (!stage_in(c, 1, weights, sizeof(float) * w_elems, true, &w)) return;
+  if (!stage_in(c, 2, output, sizeof(float) * out_elems, false, &o)) return;
+  b.dev = nullptr;
+  b.staged = false;
+  if (bias && !stage_in(c, 3, bias, sizeof(float) * (size_t)s.out_c, true, &b)) return;
+  cudaError_t e = launch_conv_ffma(c->stream, s, static_cast<const float*>(i.dev), static_cast<float*>(o.dev),
+                                   static_cast<const float*>(w.dev), static_cast<const float*>(b.dev));
+  if (!check_cuda(e, fn)) return;
+  if (!stage_out(c, o)) return;
+  finish(c, i.staged || w.staged || o.staged || b.staged);
+}
+
+ConvShape x86_conv_shape(int_fast32_t out_h, int_fast32_t out_w, int_fast32_t out_channel, int_fast32_t in_h,
+                         int_fast32_t in_w, int_fast32_t in_channel, int_fast32_t kernel_dim,
+                         int_fast32_t batch_size) {
+  ConvShape s;
+  s.batch = (int)batch_size;
+  s.in_h = (int)in_h;
+  s.in_w = (int)in_w;
+  s.in_c = (int)in_channel;
+  s.out_h = (int)out_h;
+  s.out_w = (int)out_w;
+  s.out_c = (int)out_channel;
+  s.kdim = (int)kernel_dim;
+  s.pad = 0;
+  // weights f32[in_channel, kernel_dim, kernel_dim, out_channel] (apps/x86/conv/conv.py:22)
+  s.w_stride_kx = out_channel;
+  s.w_stride_ky = kernel_dim * out_channel;
+  s.w_stride_ci = kernel_dim * kernel_dim * out_channel;
+  s.relu = true;
+  return s;
+}
+
+// ----------------------------------------------------------- int8 matmul
+void matmul_i8_dispatch(const char* fn, int_fast32_t N, int_fast32_t M, int_fast32_t K, const float* scale,
+                        bool act, const int8_t* A, const int8_t* B, int8_t* C) {
+  clear_error();
+  if (bad_args(fn, N < 1 || M < 1 || K < 1, "N, M, K must be >= 1")) return;
+  if (bad_args(fn, !A || !B || !C || !scale, "NULL tensor or scale")) return;
+  exo_b200_Context* c = default_context();  // ctxt may be an uninitialised pointer: never read it
+  if (!c) return;
+  float s;
+  if (is_device_pointer(scale)) {
+    if (!check_cuda(cudaMemcpyAsync(&s, scale, sizeof(float), cudaMemcpyDeviceToHost, c->stream), fn)) return;
+    if (!check_cuda(cudaStreamSynchronize(c->stream), fn)) return;
+  } else {
+    s = *scale;
+  }
+  Operand a, b, cc;
+  if (!stage_in(c, 0, A, (size_t)N * K, true, &a)) return;
+  if (!stage_in(c, 1, B, (size_t)K * M, true, &b)) return;
+  if (!stage_in(c, 2, C, (size_t)N * M, false, &cc)) return;
+  const int8_t* dA = static_cast<const int8_t*>(a.dev);
+  const int8_t* dB = static_cast<const int8_t*>(b.dev);
+  int8_t* dC = static_cast<int8_t*>(cc.dev);
+  cudaError_t e;
+  if (tc_supported_i8(N, M, K, dA, dB, dC))
+    e = launch_matmul_i8_tc(c, N, M, K, s, act, dA, dB, dC);
+  else
+    e = launch_matmul_i8_simt(c->stream, N, M, K, s, act, dA, dB, dC);
+  if (!check_cuda(e, fn)) return;
+  if (!stage_out(c, cc)) return;
+  finish(c, a.staged || b.staged || cc.staged);
+}
+
+// ------------------------------------------------------------- int8 conv
+void conv_i8_dispatch(const char* fn, int_fast32_t batch_size, int_fast32_t out_dim, int_fast32_t out_channel,
+                      int_fast32_t kernel_dim, int_fast32_t in_channel, int_fast32_t in_dim, int8_t* output,
+                      const int32_t* bias, const int8_t* inp, const int8_t* weights, bool act,
+                      const float* scale) {
+  clear_error();
+  if (bad_args(fn, batch_size < 1 || out_dim < 1 || out_channel < 1 || kernel_dim < 1 || in_channel < 1 ||
+                       in_dim < 1,
+               "sizes must be >= 1"))
+    return;
+  if (bad_args(fn, out_dim != in_dim - kernel_dim + 1, "out_dim must equal in_dim - kernel_dim + 1")) return;
+  if (bad_args(fn, !output || !bias || !inp || !weights || !scale, "NULL tensor or scale")) return;
+  exo_b200_Context* c = default_context();
+  if (!c) return;
+  float sc;
+  if (is_device_pointer(scale)) {
+    if (!check_cuda(cudaMemcpyAsync(&sc, scale, sizeof(float), cudaMemcpyDeviceToHost, c->stream), fn)) return;
+    if (!check_cuda(cudaStreamSynchronize(c->stream), fn)) return;
+  } else {
+    sc = *scale;
+  }
+  ConvShape s;
+  s.batch = (int)batch_size;
+  s.in_h = s.in_w = (int)in_dim;
+  s.in_c = (int)in_channel;
+  s.out_h = s.out_w = (int)out_dim;
+  s.out_c = (int)out_channel;
+  s.kdim = (int)kernel_dim;
+  s.pad = 0;
+  // weights i8[kernel_dim, kernel_dim, in_channel, out_channel] (apps/gemmini/src/exo/conv.py:17)
+  s.w_stride_ci = out_channel;
+  s.w_stride_kx = in_channel * out_channel;
+  s.w_stride_ky = kernel_dim * in_channel * out_channel;
+  s.relu = act;
+  Operand i, o, w, b;
+  if (!stage_in(c, 0, inp, (size_t)batch_size * in_dim * in_dim * in_channel, true, &i)) return;
+  if (!stage_in(c, 1, weights, (size_t)kernel_dim * kernel_dim * in_channel * out_channel, true, &w)) return;
+  if (!stage_in(c, 2, output, (size_t)batch_size * out_dim * out_dim * out_channel, false, &o)) return;
+  if (!stage_in(c, 3, bias, sizeof(int32_t) * (size_t)out_channel, true, &b)) return;
+  cudaError_t e = launch_conv_i8_simt(c->stream, s, sc, act, static_cast<const int8_t*>(i.dev),
+                                      static_cast<int8_t*>(o.dev), static_cast<const int8_t*>(w.dev),
+                                      static_cast<const int32_t*>(b.dev));
+  if (!check_cuda(e, fn)) return;
+  if (!stage_out(c, o)) return;
+  finish(c, i.staged || w.staged || o.staged || b.staged);
+}
+
+}  // namespace
+
+extern "C" {
+
+void sgemm_exo(void* ctxt, int_fast32_t M, int_fast32_t N, int_fast32_t K, const float* A, const float* B,
+               float* C) {
+  sgemm_dispatch("sgemm_exo", ctxt, -1, M, N, K, A, B, C);
+}
+void sgemm_exo_ffma(void* ctxt, int_fast32_t M, int_fast32_t N, int_fast32_t K, const float* A, const float* B,
+                    float* C) {
+  sgemm_dispatch("sgemm_exo_ffma", ctxt, EXO_B200_SGEMM_FFMA, M, N, K, A, B, C);
+}
+void sgemm_exo_3xtf32(void* ctxt, int_fast32_t M, int_fast32_t N, int_fast32_t K, const float* A,
+                      const float* B, float* C) {
+  sgemm_dispatch("sgemm_exo_3xtf32", ctxt, EXO_B200_SGEMM_3XTF32, M, N, K, A, B, C);
+}
+
+void conv_specialized(void* ctxt, const float* inp, float* output, const float* weights, const float* bias) {
+  // inp f32[5,82,102,128], output f32[5,80,100,128], weights f32[128,3,3,128], bias f32[128]
+  clear_error();
+  if (bad_args("conv_specialized", !bias, "NULL bias")) return;
+  conv_dispatch("conv_specialized", ctxt, x86_conv_shape(80, 100, 128, 82, 102, 128, 3, 5), inp, output,
+                weights, bias);
+}
+
+void conv(void* ctxt, int_fast32_t out_h, int_fast32_t out_w, int_fast32_t out_channel, int_fast32_t in_h,
+          int_fast32_t in_w, int_fast32_t in_channel, int_fast32_t kernel_dim, int_fast32_t batch_size,
+          const float* inp, float* output, const float* weights, const float* bias) {
+  clear_error();
+  // assert out_h == in_h - kernel_dim + 1, out_w == in_w - kernel_dim + 1 (apps/x86/conv/conv.py:26-27)
+  if (bad_args("conv", out_h != in_h - kernel_dim + 1 || out_w != in_w - kernel_dim + 1,
+               "out_h/out_w must equal in - kernel_dim + 1"))
+    return;
+  if (bad_args("conv", !bias, "NULL bias")) return;
+  conv_dispatch("conv", ctxt,
+                x86_conv_shape(out_h, out_w, out_channel, in_h, in_w, in_channel, kernel_dim, batch_size), inp,
+                output, weights, bias);
+}
+
+void conv_nhwc_exo(void* ctxt, int_fast32_t batch_size, int_fast32_t in_h, int_fast32_t in_w,
+                   int_fast32_t in_channel, int_fast32_t out_channel, int_fast32_t kernel_dim, int_fast32_t pad,
+                   bool relu, const float* inp, float* output, const float* weights, const float* bias) {
+  ConvShape s;
+  s.batch = (int)batch_size;
+  s.in_h = (int)in_h;
+  s.in_w = (int)in_w;
+  s.in_c = (int)in_channel;
+  s.out_c = (int)out_channel;
+  s.kdim = (int)kernel_dim;
+  s.pad = (int)pad;
+  s.out_h = (int)(in_h + 2 * pad - kernel_dim + 1);
+  s.out_w = (int)(in_w + 2 * pad - kernel_dim + 1);
+  s.w_stride_ci = out_channel;
+  s.w_stride_kx = in_channel * out_channel;
+  s.w_stride_ky = kernel_dim * in_channel * out_channel;
+  s.relu = relu;
+  conv_dispatch("conv_nhwc_exo", ctxt, s, inp, output, weights, bias);
+}
+
+void matmul_on_cpu(void* ctxt, int_fast32_t N, int_fast32_t M, int_fast32_t K, const float* scale, bool act,
+                   const int8_t* A, const int8_t* B, int8_t* C) {
+  (void)ctxt;
+  matmul_i8_dispatch("matmul_on_cpu", N, M, K, scale, act, A, B, C);
+}
+
+#define EXOB200_MATMUL_INSTANCE(NAME, N_, M_, K_)                                                          \
+  void cpu_matmul_##NAME(void* ctxt, const float* scale, bool act, const int8_t* A, const int8_t* B,       \
+                         int8_t* C) {                                                                      \
+    (void)ctxt;                                                                                            \
+    matmul_i8_dispatch("cpu_matmul_" #NAME, N_, M_, K_, scale, act, A, B, C);                              \
+  }                                                                                                        \
+  void matmul_##NAME(void* ctxt, const float* scale, bool act, const int8_t* A, const int8_t* B, int8_t* C) { \
+    (void)ctxt;                                                                                            \
+    matmul_i8_dispatch("matmul_" #NAME, N_, M_, K_, scale, act, A, B, C);                                  \
+  }
+// shapes: apps/gemmini/src/exo/matmul.py:166-170,228-232,284-288,349-353,414-418,487-507
+EXOB200_MATMUL_INSTANCE(512x512x512, 512, 512, 512)
+EXOB200_MATMUL_INSTANCE(4, 12544, 256, 64)
+EXOB200_MATMUL_INSTANCE(6, 12544, 64, 256)
+EXOB200_MATMUL_INSTANCE(14, 3136, 512, 128)
+EXOB200_MATMUL_INSTANCE(16, 3136, 128, 512)
+EXOB200_MATMUL_INSTANCE(27, 784, 1024, 256)
+#undef EXOB200_MATMUL_INSTANCE
+
+void conv_on_cpu_stride_1(void* ctxt, int_fast32_t batch_size, int_fast32_t out_dim, int_fast32_t out_channel,
+                          int_fast32_t kernel_dim, int_fast32_t in_channel, int_fast32_t in_dim, int8_t* output,
+                          const int32_t* bias, const int8_t* inp, const int8_t* weights, bool act,
+                          const float* scale) {
+  (void)ctxt;
+  conv_i8_dispatch("conv_on_cpu_stride_1", batch_size, out_dim, out_channel, kernel_dim, in_channel, in_dim,
+                   output, bias, inp, weights, act, scale);
+}
+
+#define EXOB200_CONV_INSTANCE(NAME, B_, OD_, OC_, KD_, IC_, ID_)                                           \
+  void conv_##NAME##_cpu(void* ctxt, int8_t* output, const int32_t* bias, const int8_t* inp,               \
+                         const int8_t* weights, bool act, const float* scale) {                            \
+    (void)ctxt;                                                                                            \
+    conv_i8_dispatch("conv_" #NAME "_cpu", B_, OD_, OC_, KD_, IC_, ID_, output, bias, inp, weights, act,   \
+                     scale);                                                                               \
+  }                                                                                                        \
+  void conv_##NAME(void* ctxt, int8_t* output, const int32_t* bias, const int8_t* inp,                     \
+                   const int8_t* weights, bool act, const float* scale) {                                  \
+    (void)ctxt;                                                                                            \
+    conv_i8_dispatch("conv_" #NAME, B_, OD_, OC_, KD_, IC_, ID_, output, bias, inp, weights, act, scale);  \
+  }
+// shapes: apps/gemmini/src/exo/conv.py (conv_3 / conv_17 / conv_30 schedules)
+EXOB200_CONV_INSTANCE(3, 4, 56, 64, 3, 64, 58)
+EXOB200_CONV_INSTANCE(17, 4, 28, 128, 3, 128, 30)
+EXOB200_CONV_INSTANCE(30, 4, 14, 256, 3, 256, 16)
+#undef EXOB200_CONV_INSTANCE
+
+void gemm_bf16_exo(void* ctxt, int_fast32_t M, int_fast32_t N, int_fast32_t K, const uint16_t* A,
+                   const uint16_t* B, uint16_t* C) {
+  const char* fn = "gemm_bf16_exo";
+  clear_error();
+  if (bad_args(fn, M < 1 || N < 1 || K < 1, "M, N, K must be >= 1")) return;
+  if (bad_args(fn, !A || !B || !C, "NULL tensor")) return;
+  exo_b200_Context* c = resolve_context(ctxt);
+  if (!c) return;
+  Operand a, b, cc;
+  if (!stage_in(c, 0, A, sizeof(uint16_t) * (size_t)M * K, true, &a)) return;
+  if (!stage_in(c, 1, B, sizeof(uint16_t) * (size_t)K * N, true, &b)) return;
+  if (!stage_in(c, 2, C, sizeof(uint16_t) * (size_t)M * N, false, &cc)) return;
+  if (!tc_supported_bf16(M, N, K, a.dev, b.dev, cc.dev)) {
+    set_error(EXO_B200_ERR_UNSUPPORTED, "gemm_bf16_exo: K must be a multiple of 8 and bases 16-byte aligned");
+    return;
+  }
+  cudaError_t e = launch_gemm_bf16_tc(c, M, N, K, static_cast<const uint16_t*>(a.dev),
+                                      static_cast<const uint16_t*>(b.dev), static_cast<uint16_t*>(cc.dev));
+  if (!check_cuda(e, fn)) return;
+  if (!stage_out(c, cc)) return;
+  finish(c, a.staged || b.staged || cc.staged);
+}
+
+}  // extern "C"

@@ -1,0 +1,223 @@
+// Context management, thread-local error state and host<->device staging.
+#include "common.cuh"
+
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <map>
+#include <mutex>
+
+namespace exob200 {
+
+namespace {
+thread_local int tl_code = EXO_B200_OK;
+thread_local std::string tl_msg;
+std::mutex g_mutex;
+std::map<int, exo_b200_Context*> g_default;  // one default context per device
+thread_local cudaStream_t tl_default_stream = nullptr;
+}  // namespace
+
+void set_error(int code, const std::string& msg) {
+  tl_code = code;
+  tl_msg = msg;
+  if (getenv("EXOB200_VERBOSE")) fprintf(stderr, "[exo_b200] error %d: %s\n", code, msg.c_str());
+}
+void clear_error() {
+  tl_code = EXO_B200_OK;
+  tl_msg.clear();
+}
+int last_error_code() { return tl_code; }
+const char* last_error_msg() { return tl_msg.c_str(); }
+
+bool check_cuda(cudaError_t e, const char* what) {
+  if (e == cudaSuccess) return true;
+  set_error(EXO_B200_ERR_CUDA, std::string(what) + ": " + cudaGetErrorString(e));
+  return false;
+}
+
+static exo_b200_Context* make_context(int device, cudaStream_t stream) {
+  cudaDeviceProp prop;
+  if (!check_cuda(cudaGetDeviceProperties(&prop, device), "cudaGetDeviceProperties")) return nullptr;
+  if (prop.major != 10) {
+    set_error(EXO_B200_ERR_UNSUPPORTED,
+              std::string("device '") + prop.name + "' is sm_" + std::to_string(prop.major) +
+                  std::to_string(prop.minor) + "; this library contains sm_100a code only");
+    return nullptr;
+  }
+  exo_b200_Context* c = new exo_b200_Context();
+  memset(c, 0, sizeof(*c));
+  c->magic = kContextMagic;
+  c->device = device;
+  c->stream = stream;
+  c->sm_count = prop.multiProcessorCount;
+  c->sgemm_path = EXO_B200_SGEMM_FFMA;
+  if (const char* p = getenv("EXOB200_SGEMM_PATH")) {
+    if (!strcmp(p, "3xtf32")) c->sgemm_path = EXO_B200_SGEMM_3XTF32;
+  }
+  int cur = 0;
+  cudaGetDevice(&cur);
+  cudaSetDevice(device);
+  void* host = nullptr;
+  cudaError_t e = cudaHostAlloc(&host, sizeof(DeviceStatus), cudaHostAllocMapped);
+  if (e == cudaSuccess) {
+    memset(host, 0, sizeof(DeviceStatus));
+    c->status_host = static_cast<DeviceStatus*>(host);
+    void* dev = nullptr;
+    e = cudaHostGetDevicePointer(&dev, host, 0);
+    c->status_dev = static_cast<DeviceStatus*>(dev);
+  }
+  cudaSetDevice(cur);
+  if (!check_cuda(e, "status word allocation")) {
+    delete c;
+    return nullptr;
+  }
+  return c;
+}
+
+exo_b200_Context* default_context() {
+  int device = 0;
+  if (!check_cuda(cudaGetDevice(&device), "cudaGetDevice")) return nullptr;
+  std::lock_guard<std::mutex> lock(g_mutex);
+  auto it = g_default.find(device);
+  if (it == g_default.end()) {
+    exo_b200_Context* c = make_context(device, nullptr);
+    if (!c) return nullptr;
+    it = g_default.emplace(device, c).first;
+  }
+  it->second->stream = tl_default_stream;
+  return it->second;
+}
+
+exo_b200_Context* resolve_context(void* ctxt) {
+  if (ctxt == nullptr) return default_context();
+  exo_b200_Context* c = static_cast<exo_b200_Context*>(ctxt);
+  if (c->magic != kContextMagic) {
+    set_error(EXO_B200_ERR_INVALID_ARGUMENT, "ctxt is neither NULL nor an exo_b200_Context");
+    return nullptr;
+  }
+  return c;
+}
+
+bool is_device_pointer(const void* p) {
+  cudaPointerAttributes attr;
+  cudaError_t e = cudaPointerGetAttributes(&attr, p);
+  if (e != cudaSuccess) {
+    cudaGetLastError();  // unregistered host memory on old drivers: clear and treat as host
+    return false;
+  }
+  return attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged;
+}
+
+bool stage_in(exo_b200_Context* c, int slot, const void* user, size_t bytes, bool copy_in, Operand* op) {
+  op->user = user;
+  op->bytes = bytes;
+  if (is_device_pointer(user)) {
+    op->dev = const_cast<void*>(user);
+    op->staged = false;
+    return true;
+  }
+  if (c->stage_bytes[slot] < bytes) {
+    if (c->stage[slot]) {
+      if (!check_cuda(cudaStreamSynchronize(c->stream), "cudaStreamSynchronize")) return false;
+      cudaFree(c->stage[slot]);
+      c->stage[slot] = nullptr;
+      c->stage_bytes[slot] = 0;
+    }
+    size_t want = bytes + bytes / 8 + 256;
+    if (!check_cuda(cudaMalloc(&c->stage[slot], want), "cudaMalloc(staging)")) return false;
+    c->stage_bytes[slot] = want;
+  }
+  op->dev = c->stage[slot];
+  op->staged = true;
+  if (copy_in &&
+      !check_cuda(cudaMemcpyAsync(op->dev, user, bytes, cudaMemcpyHostToDevice, c->stream), "H2D copy"))
+    return false;
+  return true;
+}
+
+bool stage_out(exo_b200_Context* c, const Operand& op) {
+  if (!op.staged) return true;
+  return check_cuda(cudaMemcpyAsync(const_cast<void*>(op.user), op.dev, op.bytes, cudaMemcpyDeviceToHost,
+                                    c->stream),
+                    "D2H copy");
+}
+
+static bool read_status(exo_b200_Context* c) {
+  if (c->status_host && c->status_host->code != 0) {
+    DeviceStatus s = *c->status_host;
+    memset(c->status_host, 0, sizeof(DeviceStatus));
+    char buf[160];
+    snprintf(buf, sizeof(buf), "device-side wait ran out (kernel location %d, block %d, detail %d)",
+             s.where, s.block, s.detail);
+    set_error(s.code, buf);
+    return false;
+  }
+  return true;
+}
+
+bool finish(exo_b200_Context* c, bool any_staged) {
+  if (!any_staged) return true;
+  if (!check_cuda(cudaStreamSynchronize(c->stream), "cudaStreamSynchronize")) return false;
+  return read_status(c);
+}
+
+bool ensure_scratch(exo_b200_Context* c, int slot, size_t bytes) {
+  if (c->scratch_bytes[slot] >= bytes) return true;
+  if (c->scratch[slot]) {
+    if (!check_cuda(cudaStreamSynchronize(c->stream), "cudaStreamSynchronize")) return false;
+    cudaFree(c->scratch[slot]);
+    c->scratch[slot] = nullptr;
+    c->scratch_bytes[slot] = 0;
+  }
+  if (!check_cuda(cudaMalloc(&c->scratch[slot], bytes), "cudaMalloc(scratch)")) return false;
+  c->scratch_bytes[slot] = bytes;
+  return true;
+}
+
+}  // namespace exob200
+
+using namespace exob200;
+
+extern "C" {
+
+exo_b200_Context* exo_b200_context_create(int device, void* stream) {
+  clear_error();
+  if (device < 0 && !check_cuda(cudaGetDevice(&device), "cudaGetDevice")) return nullptr;
+  return make_context(device, static_cast<cudaStream_t>(stream));
+}
+
+void exo_b200_context_destroy(exo_b200_Context* c) {
+  if (!c || c->magic != kContextMagic) return;
+  cudaStreamSynchronize(c->stream);
+  for (int i = 0; i < 4; i++)
+    if (c->stage[i]) cudaFree(c->stage[i]);
+  for (int i = 0; i < 2; i++)
+    if (c->scratch[i]) cudaFree(c->scratch[i]);
+  if (c->status_host) cudaFreeHost(c->status_host);
+  c->magic = 0;
+  delete c;
+}
+
+void exo_b200_context_set_stream(exo_b200_Context* c, void* stream) {
+  if (c && c->magic == kContextMagic) c->stream = static_cast<cudaStream_t>(stream);
+}
+
+void exo_b200_context_set_sgemm_path(exo_b200_Context* c, int path) {
+  if (c && c->magic == kContextMagic) c->sgemm_path = path;
+}
+
+void exo_b200_set_default_stream(void* stream) { tl_default_stream = static_cast<cudaStream_t>(stream); }
+
+int exo_b200_synchronize(exo_b200_Context* ctxt) {
+  clear_error();
+  exo_b200_Context* c = resolve_context(ctxt);
+  if (!c) return exo_b200_last_error();
+  if (check_cuda(cudaStreamSynchronize(c->stream), "cudaStreamSynchronize")) read_status(c);
+  return exo_b200_last_error();
+}
+
+int exo_b200_last_error(void) { return last_error_code(); }
+const char* exo_b200_last_error_string(void) { return last_error_msg(); }
+const char* exo_b200_version(void) { return "exo_b200 0.1 (sm_100a)"; }
+
+}  // extern "C"

@@ -1,0 +1,176 @@
+// The exact-fp32 SIMT tile engine shared by the SGEMM and the implicit-GEMM
+// convolution.  It computes, for a logical row-major problem
+//     D[m, n] = finish( chain_k  fmaf(A(m, k), B(k, n), .) starting at init(m, n) )
+// where each output element is owned by one thread for the whole reduction, so
+// the reduction is one fused-multiply-add chain in increasing k -- the order
+// the reference's generated microkernels use
+// (tests/golden/test_apps/test_x86_sgemm.txt:437-454, test_x86_conv.txt:85-101).
+// No split-K, and no padded steps along K (fmaf(0,0,c) would turn c = -0.0
+// into +0.0), so results are bit-identical to the reference.
+//
+// Tiling: CTA tile 128x128, K step 16, 256 threads, each thread an 8x8
+// register tile laid out as 2x2 quadrants of 4x4 so that every shared-memory
+// read is a conflict-free 128-bit load.  A is stored k-major in shared memory
+// so that the per-k A fragment is contiguous.  The next K tile is fetched into
+// registers while the current one is multiplied (two shared-memory buffers, one
+// barrier per tile).
+//
+// A Policy supplies the operand addressing:
+//   int  M, N, K                       logical extents
+//   RowCtx row_ctx(int m)              per-row state for the A loader (computed once)
+//   float4 load_a(const RowCtx&, int m, int k)   A(m, k..k+3), zero outside
+//   void copy_b(float* smem, int k, int n)   cp.async of B(k, n..n+3) into smem, zero outside
+//   float4 init(int m, int n)          chain start for (m, n..n+3)
+//   void store(int m, int n, float4)   applies the epilogue and writes (bounds-checked)
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace exob200 {
+namespace ffma {
+
+constexpr int BM = 128, BN = 128, BK = 16;
+constexpr int THREADS = 256;
+constexpr int AS_PITCH = BM + 4;  // floats; keeps 16-byte alignment, spreads the transposing stores
+
+__device__ __forceinline__ float4 ldg4(const float* p) {
+  return __ldg(reinterpret_cast<const float4*>(p));
+}
+__device__ __forceinline__ float4 zero4() { return make_float4(0.f, 0.f, 0.f, 0.f); }
+
+// Asynchronous global -> shared copies; `valid` false zero-fills the destination.
+__device__ __forceinline__ void cp_async16(float* smem, const float* g, bool valid) {
+  const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+  const int n = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(s), "l"(g), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async4(float* smem, const float* g, bool valid) {
+  const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+  const int n = valid ? 4 : 0;
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(s), "l"(g), "r"(n) : "memory");
+}
+
+template <class Policy>
+__global__ void __launch_bounds__(THREADS, 2) tile_kernel(const Policy P, int tiles_m, int tiles_n) {
+  __shared__ __align__(16) float As[2][BK][AS_PITCH];
+  __shared__ __align__(16) float Bs[2][BK][BN];
+
+  // CTA -> tile, grouped 8 tile-rows at a time so that CTAs resident together
+  // share A rows and B columns in L2.
+  constexpr int GM = 8;
+  const int bid = blockIdx.x;
+  const int per_group = GM * tiles_n;
+  const int group = bid / per_group;
+  const int first_m = group * GM;
+  const int gm = min(GM, tiles_m - first_m);
+  const int in_group = bid - group * per_group;
+  const int tm = first_m + in_group % gm;
+  const int tn = in_group / gm;
+  const int m0 = tm * BM, n0 = tn * BN;
+  const int K = P.K;
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5, lane = tid & 31;
+  const int ty = (warp >> 1) * 4 + (lane >> 3);  // 0..15
+  const int tx = (warp & 1) * 8 + (lane & 7);    // 0..15
+
+  // global -> register staging coordinates
+  // A tile: 128 rows x 16 k.  thread -> rows tid/4 and tid/4 + 64, k quad (tid%4)*4
+  const int a_row = tid >> 2, a_kq = (tid & 3) * 4;
+  // B tile: 16 k x 128 cols.  thread -> k rows tid/32 and tid/32 + 8, col quad (tid%32)*4
+  const int b_k = tid >> 5, b_c4 = (tid & 31) * 4;
+
+  const typename Policy::RowCtx rc0 = P.row_ctx(m0 + a_row);
+  const typename Policy::RowCtx rc1 = P.row_ctx(m0 + a_row + 64);
+
+  // A goes through registers (it is transposed on the way into shared memory);
+  // B is copied global -> shared asynchronously, 16 bytes (or 4 x 4) per thread.
+  float4 pa[2];
+  auto load_tile = [&](int k0, int buf) {
+    pa[0] = P.load_a(rc0, m0 + a_row, k0 + a_kq);
+    pa[1] = P.load_a(rc1, m0 + a_row + 64, k0 + a_kq);
+    P.copy_b(&Bs[buf][b_k][b_c4], k0 + b_k, n0 + b_c4);
+    P.copy_b(&Bs[buf][b_k + 8][b_c4], k0 + b_k + 8, n0 + b_c4);
+  };
+  auto store_tile = [&](int buf) {
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+      const int r = a_row + h * 64;
+      As[buf][a_kq + 0][r] = pa[h].x;
+      As[buf][a_kq + 1][r] = pa[h].y;
+      As[buf][a_kq + 2][r] = pa[h].z;
+      As[buf][a_kq + 3][r] = pa[h].w;
+    }
+    asm volatile("cp.async.wait_all;" ::: "memory");
+  };
+
+  // accumulators start at the chain's first operand
+  float acc[8][8];
+#pragma unroll
+  for (int i = 0; i < 8; i++) {
+    const int row = m0 + (i >> 2) * 64 + ty * 4 + (i & 3);
+#pragma unroll
+    for (int jq = 0; jq < 2; jq++) {
+      const float4 v = P.init(row, n0 + jq * 64 + tx * 4);
+      acc[i][jq * 4 + 0] = v.x;
+      acc[i][jq * 4 + 1] = v.y;
+      acc[i][jq * 4 + 2] = v.z;
+      acc[i][jq * 4 + 3] = v.w;
+    }
+  }
+
+  const int ktiles = (K + BK - 1) / BK;
+  load_tile(0, 0);
+  store_tile(0);
+  __syncthreads();
+
+  for (int t = 0; t < ktiles; t++) {
+    const int buf = t & 1;
+    if (t + 1 < ktiles) load_tile((t + 1) * BK, buf ^ 1);
+
+    const int kmax = min(BK, K - t * BK);
+    auto step = [&](int kk) {
+      const float4 a0 = *reinterpret_cast<const float4*>(&As[buf][kk][ty * 4]);
+      const float4 a1 = *reinterpret_cast<const float4*>(&As[buf][kk][64 + ty * 4]);
+      const float4 b0 = *reinterpret_cast<const float4*>(&Bs[buf][kk][tx * 4]);
+      const float4 b1 = *reinterpret_cast<const float4*>(&Bs[buf][kk][64 + tx * 4]);
+      const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+      const float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+      for (int i = 0; i < 8; i++)
+#pragma unroll
+        for (int j = 0; j < 8; j++) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    };
+    if (kmax == BK) {
+#pragma unroll
+      for (int kk = 0; kk < BK; kk++) step(kk);
+    } else {
+      for (int kk = 0; kk < kmax; kk++) step(kk);  // ragged K tail: no padded steps
+    }
+
+    if (t + 1 < ktiles) store_tile(buf ^ 1);
+    __syncthreads();
+  }
+
+#pragma unroll
+  for (int i = 0; i < 8; i++) {
+    const int row = m0 + (i >> 2) * 64 + ty * 4 + (i & 3);
+#pragma unroll
+    for (int jq = 0; jq < 2; jq++)
+      P.store(row, n0 + jq * 64 + tx * 4,
+              make_float4(acc[i][jq * 4], acc[i][jq * 4 + 1], acc[i][jq * 4 + 2], acc[i][jq * 4 + 3]));
+  }
+}
+
+template <class Policy>
+cudaError_t launch_tiles(cudaStream_t stream, const Policy& P) {
+  const int64_t tiles_m = (P.M + BM - 1) / BM, tiles_n = (P.N + BN - 1) / BN;
+  if (tiles_m * tiles_n > INT32_MAX) return cudaErrorInvalidValue;
+  tile_kernel<Policy><<<(unsigned)(tiles_m * tiles_n), THREADS, 0, stream>>>(P, (int)tiles_m, (int)tiles_n);
+  return cudaGetLastError();
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace ffma
+}  // namespace exob200

@@ -1,0 +1,45 @@
+// Device-pointer launchers of every kernel in the library.  All pointers are
+// device memory; launches are asynchronous on `stream`.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "common.cuh"
+
+namespace exob200 {
+
+// ---- exact fp32 SIMT kernels (sgemm_ffma.cu, conv_ffma.cu)
+cudaError_t launch_sgemm_ffma(cudaStream_t stream, int64_t M, int64_t N, int64_t K, const float* A,
+                              const float* B, float* C);
+
+struct ConvShape {
+  int batch, in_h, in_w, in_c, out_h, out_w, out_c, kdim, pad;
+  // element strides of the weight tensor for (ky, kx, ci); co is contiguous
+  int64_t w_stride_ky, w_stride_kx, w_stride_ci;
+  bool relu;
+};
+cudaError_t launch_conv_ffma(cudaStream_t stream, const ConvShape& s, const float* inp, float* out,
+                             const float* weights, const float* bias);
+
+// ---- exact int8 SIMT kernels for shapes the tensor path cannot address (i8_simt.cu)
+cudaError_t launch_matmul_i8_simt(cudaStream_t stream, int64_t N, int64_t M, int64_t K, float scale,
+                                  bool act, const int8_t* A, const int8_t* B, int8_t* C);
+cudaError_t launch_conv_i8_simt(cudaStream_t stream, const ConvShape& s, float scale, bool act,
+                                const int8_t* inp, int8_t* out, const int8_t* weights,
+                                const int32_t* bias);
+
+// ---- tcgen05 / TMEM / TMA kernels (tc_gemm.cu)
+// Each returns cudaErrorNotSupported when the operands do not meet TMA's
+// address rules (16-byte aligned base and row pitch); callers then repack or
+// use the SIMT kernel.
+bool tc_supported_bf16(int64_t M, int64_t N, int64_t K, const void* A, const void* B, const void* C);
+cudaError_t launch_gemm_bf16_tc(exo_b200_Context* ctx, int64_t M, int64_t N, int64_t K,
+                                const uint16_t* A, const uint16_t* B, uint16_t* C);
+bool tc_supported_i8(int64_t N, int64_t M, int64_t K, const void* A, const void* B, const void* C);
+cudaError_t launch_matmul_i8_tc(exo_b200_Context* ctx, int64_t N, int64_t M, int64_t K, float scale,
+                                bool act, const int8_t* A, const int8_t* B, int8_t* C);
+bool tc_supported_tf32(int64_t M, int64_t N, int64_t K, const void* A, const void* B, const void* C);
+cudaError_t launch_sgemm_3xtf32_tc(exo_b200_Context* ctx, int64_t M, int64_t N, int64_t K,
+                                   const float* A, const float* B, float* C);
+
+}  // namespace exob200

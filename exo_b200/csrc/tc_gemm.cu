@@ -1,0 +1,597 @@
+// Tensor-core GEMMs on tcgen05 / tensor memory, fed by TMA.
+//
+// One persistent, warp-specialised kernel template serves three arithmetic
+// modes; all operands reach it K-major (rows of K-contiguous elements):
+//   BF16    C(bf16) = A(bf16) * B(bf16), fp32 accumulation      -> gemm_bf16_exo
+//   I8      int8 x int8 -> int32 in tensor memory, then the Gemmini output
+//           stage (scale, round-half-even, clamp, ReLU) fused in the epilogue
+//           (apps/gemmini/src/exo/matmul.py:18-43)                -> matmul_on_cpu & co
+//   TF32X3  fp32 operands pre-split into TF32 hi + lo terms; per product three
+//           MMAs (lo*hi, hi*lo, hi*hi) into one fp32 accumulator; C += result
+//           (apps/x86/sgemm/sgemm.py:20-23)                       -> sgemm_exo_3xtf32
+//
+// CTA = 6 warps: warp 0 issues TMA loads into a ring of shared-memory stages
+// (mbarrier full/empty pairs), one thread of warp 1 issues tcgen05.mma into one
+// of two 128 x 256 fp32/int32 accumulators in tensor memory (512 columns) and
+// commits stage releases, warps 2-5 drain the other accumulator with tcgen05.ld
+// and write C, so the epilogue of tile i overlaps the main loop of tile i+1.
+// Grid = one CTA per SM; tiles are handed out round-robin in an order that keeps
+// 16 tile-rows of A and the matching B columns hot in L2.  Ragged M / N / K:
+// TMA zero-fills out-of-range rows and K, stores are bounds-checked.
+//
+// Every wait is bounded: on expiry the role records EXO_B200_ERR_TIMEOUT in the
+// status word, raises the CTA's abort flag so the other roles leave their loops
+// too, the producer waits (bounded) for its TMA copies in flight, and the CTA
+// frees its tensor memory and returns.
+//
+// Operand layouts that are not K-major in the caller's memory (B of the int8
+// matmul and of the SGEMM are row-major K x N) are transposed into a scratch
+// buffer by a bandwidth-bound pre-pass, which for TF32X3 also performs the
+// hi/lo split and pads the row pitch to TMA's 16-byte rule, so ragged K and N
+// need no special case.
+#include <cuda.h>
+#include <cuda_bf16.h>
+
+#include <mutex>
+
+#include "i8_epilogue.cuh"
+#include "kernels.cuh"
+#include "umma.cuh"
+
+namespace exob200 {
+namespace {
+
+using namespace umma;
+
+enum Mode { MODE_BF16 = 0, MODE_I8 = 1, MODE_TF32X3 = 2 };
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int ROW_BYTES = 128;            // one swizzle row: the K extent of a stage
+constexpr int KSTEPS = ROW_BYTES / 32;    // every tcgen05.mma consumes 32 bytes of K
+constexpr int TMEM_COLS = 512;            // two BN-column accumulators
+constexpr int NUM_THREADS = 192;
+constexpr uint64_t WAIT_LIMIT_NS = 1000ull * 1000ull * 1000ull;  // 1 s per wait
+constexpr uint64_t DRAIN_LIMIT_NS = 1000ull * 1000ull;           // 1 ms per stage on the error path
+
+template <int MODE>
+struct Cfg;
+template <>
+struct Cfg<MODE_BF16> {
+  static constexpr int ELEM = 2, NA = 1, NB = 1, NPROD = 1, STAGES = 4, KIND = KIND_F16;
+  static constexpr uint32_t IDESC = make_idesc(1, 1, 1, BM, BN);
+};
+template <>
+struct Cfg<MODE_I8> {
+  static constexpr int ELEM = 1, NA = 1, NB = 1, NPROD = 1, STAGES = 4, KIND = KIND_I8;
+  static constexpr uint32_t IDESC = make_idesc(2, 1, 1, BM, BN);
+};
+template <>
+struct Cfg<MODE_TF32X3> {
+  static constexpr int ELEM = 4, NA = 2, NB = 2, NPROD = 3, STAGES = 2, KIND = KIND_TF32;
+  static constexpr uint32_t IDESC = make_idesc(1, 2, 2, BM, BN);
+};
+
+constexpr int A_TILE_BYTES = BM * ROW_BYTES;  // 16 KiB
+constexpr int B_TILE_BYTES = BN * ROW_BYTES;  // 32 KiB
+
+template <int MODE>
+__host__ __device__ constexpr int stage_bytes() {
+  return Cfg<MODE>::NA * A_TILE_BYTES + Cfg<MODE>::NB * B_TILE_BYTES;
+}
+template <int MODE>
+__host__ __device__ constexpr int smem_bytes() {
+  return Cfg<MODE>::STAGES * stage_bytes<MODE>() + 1024 /* alignment slack */ + 256 /* barriers */;
+}
+
+struct EpiParams {
+  void* C;
+  int64_t ldc;   // elements
+  float scale;   // I8
+  int act;       // I8
+  int vec_ok;    // 16-byte stores allowed
+};
+
+__device__ __forceinline__ void report_timeout(DeviceStatus* st, volatile int* abort, int where) {
+  *abort = 1;
+  if (st != nullptr && st->code == 0) {
+    st->where = where;
+    st->block = (int)blockIdx.x;
+    st->code = EXO_B200_ERR_TIMEOUT;
+  }
+}
+
+// ------------------------------------------------------------- epilogues
+template <int MODE>
+__device__ __forceinline__ void store_chunk(const EpiParams& ep, const uint32_t (&r)[32], int row, int col,
+                                            int M, int N) {
+  if (row >= M || col >= N) return;
+  if (MODE == MODE_BF16) {
+    __nv_bfloat16* p = static_cast<__nv_bfloat16*>(ep.C) + (int64_t)row * ep.ldc + col;
+    if (ep.vec_ok) {
+#pragma unroll
+      for (int v = 0; v < 4; v++) {
+        if (col + v * 8 + 8 > N) break;
+        uint32_t w[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+          const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + 2 * j]),
+                                                         __uint_as_float(r[v * 8 + 2 * j + 1]));
+          w[j] = *reinterpret_cast<const uint32_t*>(&h);
+        }
+        *reinterpret_cast<uint4*>(p + v * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; j++)
+        if (col + j < N) p[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
+    }
+  } else if (MODE == MODE_I8) {
+    int8_t* p = static_cast<int8_t*>(ep.C) + (int64_t)row * ep.ldc + col;
+    if (ep.vec_ok) {
+#pragma unroll
+      for (int v = 0; v < 2; v++) {
+        if (col + v * 16 + 16 > N) break;
+        uint32_t w[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+          uint32_t x = 0;
+#pragma unroll
+          for (int b = 0; b < 4; b++) {
+            const int8_t q = i8_epilogue((int32_t)r[v * 16 + j * 4 + b], ep.scale, ep.act != 0);
+            x |= (uint32_t)(uint8_t)q << (8 * b);
+          }
+          w[j] = x;
+        }
+        *reinterpret_cast<uint4*>(p + v * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; j++)
+        if (col + j < N) p[j] = i8_epilogue((int32_t)r[j], ep.scale, ep.act != 0);
+    }
+  } else {  // MODE_TF32X3: C += acc
+    float* p = static_cast<float*>(ep.C) + (int64_t)row * ep.ldc + col;
+    if (ep.vec_ok) {
+#pragma unroll
+      for (int v = 0; v < 8; v++) {
+        if (col + v * 4 + 4 > N) break;
+        float4 c = *reinterpret_cast<const float4*>(p + v * 4);
+        c.x += __uint_as_float(r[v * 4 + 0]);
+        c.y += __uint_as_float(r[v * 4 + 1]);
+        c.z += __uint_as_float(r[v * 4 + 2]);
+        c.w += __uint_as_float(r[v * 4 + 3]);
+        *reinterpret_cast<float4*>(p + v * 4) = c;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; j++)
+        if (col + j < N) p[j] += __uint_as_float(r[j]);
+    }
+  }
+}
+
+// ------------------------------------------------------------ the kernel
+template <int MODE>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmA1,
+               const __grid_constant__ CUtensorMap tmB0, const __grid_constant__ CUtensorMap tmB1, int M, int N,
+               int K, EpiParams ep, DeviceStatus* status, int tiles_m, int tiles_n) {
+  using C = Cfg<MODE>;
+  constexpr int STAGES = C::STAGES;
+  constexpr int STAGE_BYTES = stage_bytes<MODE>();
+  constexpr int BK = ROW_BYTES / C::ELEM;  // elements of K per stage
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t tiles = (raw + 1023u) & ~1023u;  // swizzled tiles need 1024-byte alignment
+  uint8_t* ctrl = smem_raw + (tiles - raw) + STAGES * STAGE_BYTES;
+  const uint32_t bars = tiles + STAGES * STAGE_BYTES;
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int b) { return bars + 8u * (2 * STAGES + b); };
+  auto tempty_bar = [&](int b) { return bars + 8u * (2 * STAGES + 2 + b); };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(ctrl + 8 * (2 * STAGES + 4));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(ctrl + 8 * (2 * STAGES + 4) + 4);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; s++) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 2; b++) {
+      mbar_init(tfull_bar(b), 1);
+      mbar_init(tempty_bar(b), 4);  // one arrival per epilogue warp
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    fence_proxy_async();
+    prefetch_tensormap(&tmA0);
+    prefetch_tensormap(&tmB0);
+    if (C::NA > 1) prefetch_tensormap(&tmA1);
+    if (C::NB > 1) prefetch_tensormap(&tmB1);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int num_tiles = tiles_m * tiles_n;
+  const int num_kb = (K + BK - 1) / BK;
+  constexpr int GM = 16;
+  auto tile_coord = [&](int t, int& tm, int& tn) {
+    const int per_group = GM * tiles_n;
+    const int group = t / per_group;
+    const int first_m = group * GM;
+    const int gm = min(GM, tiles_m - first_m);
+    const int in_group = t - group * per_group;
+    tm = first_m + in_group % gm;
+    tn = in_group / gm;
+  };
+
+  if (warp == 0) {
+    // ------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t armed = 0, armed_parity = 0;  // per-stage: has a load in flight / its phase parity
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        int tm, tn;
+        tile_coord(t, tm, tn);
+        const int m0 = tm * BM, n0 = tn * BN;
+        for (int kb = 0; kb < num_kb; kb++) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, WAIT_LIMIT_NS)) {
+            report_timeout(status, abort_flag, 1);
+            ok = false;
+            break;
+          }
+          const uint32_t bar = full_bar(stage);
+          const uint32_t dst = tiles + stage * STAGE_BYTES;
+          mbar_arrive_expect_tx(bar, STAGE_BYTES);
+          armed |= 1u << stage;
+          armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
+          const int k0 = kb * BK;
+          tma_load_2d(dst, &tmA0, bar, k0, m0);
+          if (C::NA > 1) tma_load_2d(dst + A_TILE_BYTES, &tmA1, bar, k0, m0);
+          tma_load_2d(dst + C::NA * A_TILE_BYTES, &tmB0, bar, k0, n0);
+          if (C::NB > 1) tma_load_2d(dst + C::NA * A_TILE_BYTES + B_TILE_BYTES, &tmB1, bar, k0, n0);
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      if (!ok || *abort_flag) {
+        // error path: let the copies already issued land before the CTA exits
+        volatile int never = 0;
+        for (int s = 0; s < STAGES; s++)
+          if (armed & (1u << s)) mbar_wait(full_bar(s), (armed_parity >> s) & 1u, &never, DRAIN_LIMIT_NS);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, WAIT_LIMIT_NS)) {
+          report_timeout(status, abort_flag, 2);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d = tmem_base + (uint32_t)(acc * BN);
+        for (int kb = 0; kb < num_kb; kb++) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag, WAIT_LIMIT_NS)) {
+            report_timeout(status, abort_flag, 3);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a0 = tiles + stage * STAGE_BYTES;
+          const uint32_t b0 = a0 + C::NA * A_TILE_BYTES;
+          const uint64_t da_hi = smem_desc_k_sw128(a0);
+          const uint64_t db_hi = smem_desc_k_sw128(b0);
+#pragma unroll
+          for (int ks = 0; ks < KSTEPS; ks++) {
+            const uint64_t adv = (uint64_t)(ks * 2);  // 32 bytes, in 16-byte units
+            if (C::NPROD == 1) {
+              tc_mma<C::KIND>(d, da_hi + adv, db_hi + adv, C::IDESC, (kb | ks) != 0);
+            } else {
+              const uint64_t da_lo = smem_desc_k_sw128(a0 + A_TILE_BYTES);
+              const uint64_t db_lo = smem_desc_k_sw128(b0 + B_TILE_BYTES);
+              // small terms first, then the leading term
+              tc_mma<C::KIND>(d, da_lo + adv, db_hi + adv, C::IDESC, (kb | ks) != 0);
+              tc_mma<C::KIND>(d, da_hi + adv, db_lo + adv, C::IDESC, 1);
+              tc_mma<C::KIND>(d, da_hi + adv, db_hi + adv, C::IDESC, 1);
+            }
+          }
+          tc_commit(empty_bar(stage));  // stage reusable once these MMAs have read it
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        tc_commit(tfull_bar(acc));  // accumulator complete
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------ epilogue warps 2..5
+    const int q = warp & 3;  // tensor-memory lane quarter this warp may read
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+      int tm, tn;
+      tile_coord(t, tm, tn);
+      const int m0 = tm * BM, n0 = tn * BN;
+      if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, WAIT_LIMIT_NS)) {
+        if (lane == 0) report_timeout(status, abort_flag, 4);
+        break;
+      }
+      tc_fence_after();
+      const int row = m0 + q * 32 + lane;
+#pragma unroll 1
+      for (int ch = 0; ch < BN / 32; ch++) {
+        const int col = n0 + ch * 32;
+        if (col >= N) break;  // warp-uniform
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + ch * 32), r);
+        tmem_ld_wait();
+        store_chunk<MODE>(ep, r, row, col, M, N);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar(acc));
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ----------------------------------------------------- pre-pass kernels
+// TF32 split of one fp32 value: hi = rna_tf32(x), lo = rna_tf32(x - hi).
+// x - hi is exact in fp32.  Non-finite x keeps lo = 0 so inf stays inf.
+__device__ __forceinline__ void split_tf32(float x, float& hi, float& lo) {
+  uint32_t h;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(x));
+  hi = __uint_as_float(h);
+  const float d = x - hi;
+  uint32_t l;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(l) : "f"(d));
+  lo = (fabsf(hi) <= 3.402823466e38f) ? __uint_as_float(l) : 0.f;
+}
+
+// A (M x K row-major) -> hi, lo (M x Kp), zero in the pad columns.
+__global__ void split_rows_kernel(const float* __restrict__ A, int64_t M, int K, int Kp, float* __restrict__ hi,
+                                  float* __restrict__ lo) {
+  const int64_t total = M * Kp;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t row = i / Kp;
+    const int k = (int)(i - row * Kp);
+    float h = 0.f, l = 0.f;
+    if (k < K) split_tf32(__ldg(A + row * K + k), h, l);
+    hi[i] = h;
+    lo[i] = l;
+  }
+}
+
+// B (K x N row-major) -> hi^T, lo^T (N x Kp): 32 x 32 tiles through shared memory.
+__global__ void split_transpose_kernel(const float* __restrict__ B, int K, int N, int Kp, float* __restrict__ hi,
+                                       float* __restrict__ lo) {
+  __shared__ float th[32][33], tl[32][33];
+  const int k0 = blockIdx.x * 32, n0 = blockIdx.y * 32;
+  const int tx = threadIdx.x, ty = threadIdx.y;  // 32 x 8
+  for (int r = ty; r < 32; r += 8) {
+    const int k = k0 + r, n = n0 + tx;
+    float h = 0.f, l = 0.f;
+    if (k < K && n < N) split_tf32(__ldg(B + (int64_t)k * N + n), h, l);
+    th[r][tx] = h;
+    tl[r][tx] = l;
+  }
+  __syncthreads();
+  for (int r = ty; r < 32; r += 8) {
+    const int n = n0 + r, k = k0 + tx;
+    if (n < N && k < Kp) {
+      hi[(int64_t)n * Kp + k] = th[tx][r];
+      lo[(int64_t)n * Kp + k] = tl[tx][r];
+    }
+  }
+}
+
+// int8 B (K x N row-major) -> B^T (N x Kp), zero pad.  128 x 128 byte tiles,
+// 32-bit global accesses on both sides.
+__global__ void __launch_bounds__(256) transpose_i8_kernel(const int8_t* __restrict__ B, int K, int N, int Kp,
+                                                           int8_t* __restrict__ Bt, int vec_in) {
+  __shared__ int8_t t[128][128 + 4];
+  const int k0 = blockIdx.x * 128, n0 = blockIdx.y * 128;
+  const int tid = threadIdx.x;
+  // read: 128 k rows x 32 words
+  for (int e = tid; e < 128 * 32; e += 256) {
+    const int r = e >> 5, w = e & 31;
+    const int k = k0 + r, n = n0 + w * 4;
+    uint32_t v = 0;
+    if (k < K) {
+      const int8_t* p = B + (int64_t)k * N + n;
+      if (vec_in && n + 4 <= N) {
+        v = __ldg(reinterpret_cast<const uint32_t*>(p));
+      } else {
+#pragma unroll
+        for (int b = 0; b < 4; b++)
+          if (n + b < N) v |= (uint32_t)(uint8_t)__ldg(p + b) << (8 * b);
+      }
+    }
+    *reinterpret_cast<uint32_t*>(&t[r][w * 4]) = v;
+  }
+  __syncthreads();
+  // write: 128 n rows x 32 words of k
+  for (int e = tid; e < 128 * 32; e += 256) {
+    const int r = e >> 5, w = e & 31;
+    const int n = n0 + r, k = k0 + w * 4;
+    if (n < N && k < Kp) {  // Kp % 16 == 0, so a word is entirely inside
+      const uint32_t v = (uint32_t)(uint8_t)t[w * 4 + 0][r] | ((uint32_t)(uint8_t)t[w * 4 + 1][r] << 8) |
+                         ((uint32_t)(uint8_t)t[w * 4 + 2][r] << 16) | ((uint32_t)(uint8_t)t[w * 4 + 3][r] << 24);
+      *reinterpret_cast<uint32_t*>(Bt + (int64_t)n * Kp + k) = v;
+    }
+  }
+}
+
+// ------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+// K-major operand: `rows` rows of `k_elems` elements, row pitch `pitch_bytes`;
+// box = 128 bytes of K x box_rows rows, 128-byte swizzle, zero fill outside.
+bool make_kmajor_map(CUtensorMap* m, CUtensorMapDataType dt, int elem, const void* base, int64_t rows,
+                     int64_t k_elems, int64_t pitch_bytes, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) {
+    set_error(EXO_B200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    return false;
+  }
+  cuuint64_t dims[2] = {(cuuint64_t)k_elems, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)pitch_bytes};
+  cuuint32_t box[2] = {(cuuint32_t)(ROW_BYTES / elem), (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(m, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error(EXO_B200_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult " + std::to_string((int)r));
+    return false;
+  }
+  return true;
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+template <int MODE>
+cudaError_t launch_tc(exo_b200_Context* ctx, const CUtensorMap& a0, const CUtensorMap& a1, const CUtensorMap& b0,
+                      const CUtensorMap& b1, int64_t M, int64_t N, int64_t K, const EpiParams& ep) {
+  {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         smem_bytes<MODE>());
+    if (e != cudaSuccess) return e;
+  }
+  const int64_t tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
+  if (tiles_m * tiles_n > INT32_MAX || M > INT32_MAX || N > INT32_MAX || K > INT32_MAX)
+    return cudaErrorInvalidValue;
+  const int grid = (int)std::min<int64_t>(tiles_m * tiles_n, ctx->sm_count);
+  gemm_tc_kernel<MODE><<<grid, NUM_THREADS, smem_bytes<MODE>(), ctx->stream>>>(
+      a0, a1, b0, b1, (int)M, (int)N, (int)K, ep, ctx->status_dev, (int)tiles_m, (int)tiles_n);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------- bf16
+bool tc_supported_bf16(int64_t, int64_t, int64_t K, const void* A, const void* B, const void*) {
+  return K % 8 == 0 && aligned16(A) && aligned16(B);
+}
+
+cudaError_t launch_gemm_bf16_tc(exo_b200_Context* ctx, int64_t M, int64_t N, int64_t K, const uint16_t* A,
+                                const uint16_t* B, uint16_t* C) {
+  CUtensorMap ma, mb;
+  if (!make_kmajor_map(&ma, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, A, M, K, K * 2, BM)) return cudaErrorUnknown;
+  if (!make_kmajor_map(&mb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, B, N, K, K * 2, BN)) return cudaErrorUnknown;
+  EpiParams ep{C, N, 0.f, 0, (N % 8 == 0 && aligned16(C)) ? 1 : 0};
+  return launch_tc<MODE_BF16>(ctx, ma, ma, mb, mb, M, N, K, ep);
+}
+
+// ---------------------------------------------------------------- int8
+bool tc_supported_i8(int64_t, int64_t, int64_t K, const void* A, const void*, const void*) {
+  return K % 16 == 0 && aligned16(A);
+}
+
+cudaError_t launch_matmul_i8_tc(exo_b200_Context* ctx, int64_t N, int64_t M, int64_t K, float scale, bool act,
+                                const int8_t* A, const int8_t* B, int8_t* C) {
+  // Exo's names: A is N x K (rows N), B is K x M, C is N x M.  GEMM view: rows = N, cols = M.
+  const int64_t rows = N, cols = M;
+  const int64_t Kp = K;  // K % 16 == 0 already
+  if (!ensure_scratch(ctx, 1, (size_t)(cols * Kp))) return cudaErrorMemoryAllocation;
+  int8_t* Bt = static_cast<int8_t*>(ctx->scratch[1]);
+  {
+    dim3 grid((unsigned)((K + 127) / 128), (unsigned)((cols + 127) / 128));
+    if (grid.y > 65535) return cudaErrorInvalidValue;
+    const int vec_in = (cols % 4 == 0 && (reinterpret_cast<uintptr_t>(B) & 3u) == 0) ? 1 : 0;
+    transpose_i8_kernel<<<grid, 256, 0, ctx->stream>>>(B, (int)K, (int)cols, (int)Kp, Bt, vec_in);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+  }
+  CUtensorMap ma, mb;
+  if (!make_kmajor_map(&ma, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, A, rows, K, K, BM)) return cudaErrorUnknown;
+  if (!make_kmajor_map(&mb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, Bt, cols, K, Kp, BN)) return cudaErrorUnknown;
+  EpiParams ep{C, cols, scale, act ? 1 : 0, (cols % 16 == 0 && aligned16(C)) ? 1 : 0};
+  return launch_tc<MODE_I8>(ctx, ma, ma, mb, mb, rows, cols, K, ep);
+}
+
+// -------------------------------------------------------------- 3xTF32
+bool tc_supported_tf32(int64_t, int64_t, int64_t, const void*, const void*, const void*) { return true; }
+
+cudaError_t launch_sgemm_3xtf32_tc(exo_b200_Context* ctx, int64_t M, int64_t N, int64_t K, const float* A,
+                                   const float* B, float* C) {
+  if (M > INT32_MAX || N > INT32_MAX || K > INT32_MAX - 64) return cudaErrorInvalidValue;
+  const int64_t Kp = (K + 3) / 4 * 4;  // pitch multiple of 16 bytes
+  const size_t a_elems = (size_t)(M * Kp), b_elems = (size_t)(N * Kp);
+  if (!ensure_scratch(ctx, 0, 2 * a_elems * sizeof(float))) return cudaErrorMemoryAllocation;
+  if (!ensure_scratch(ctx, 1, 2 * b_elems * sizeof(float))) return cudaErrorMemoryAllocation;
+  float* a_hi = static_cast<float*>(ctx->scratch[0]);
+  float* a_lo = a_hi + a_elems;
+  float* b_hi = static_cast<float*>(ctx->scratch[1]);
+  float* b_lo = b_hi + b_elems;
+  {
+    const int64_t total = M * Kp;
+    const int blocks = (int)std::min<int64_t>((total + 255) / 256, (int64_t)ctx->sm_count * 16);
+    split_rows_kernel<<<blocks, 256, 0, ctx->stream>>>(A, M, (int)K, (int)Kp, a_hi, a_lo);
+    dim3 grid((unsigned)((Kp + 31) / 32), (unsigned)((N + 31) / 32));
+    if (grid.y > 65535) return cudaErrorInvalidValue;
+    split_transpose_kernel<<<grid, dim3(32, 8), 0, ctx->stream>>>(B, (int)K, (int)N, (int)Kp, b_hi, b_lo);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+  }
+  CUtensorMap ma0, ma1, mb0, mb1;
+  const CUtensorMapDataType dt = CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  if (!make_kmajor_map(&ma0, dt, 4, a_hi, M, Kp, Kp * 4, BM)) return cudaErrorUnknown;
+  if (!make_kmajor_map(&ma1, dt, 4, a_lo, M, Kp, Kp * 4, BM)) return cudaErrorUnknown;
+  if (!make_kmajor_map(&mb0, dt, 4, b_hi, N, Kp, Kp * 4, BN)) return cudaErrorUnknown;
+  if (!make_kmajor_map(&mb1, dt, 4, b_lo, N, Kp, Kp * 4, BN)) return cudaErrorUnknown;
+  EpiParams ep{C, N, 0.f, 0, (N % 4 == 0 && aligned16(C)) ? 1 : 0};
+  return launch_tc<MODE_TF32X3>(ctx, ma0, ma1, mb0, mb1, M, N, Kp, ep);
+}
+
+}  // namespace exob200

@@ -1,0 +1,178 @@
+/*
+ * exo_b200 -- B200 (sm_100a) GEMM / convolution kernels behind the C ABI that
+ * Exo's compiler `exocc` writes into its generated headers.
+ *
+ * Every "reference-identical" prototype below is character-for-character the
+ * one exocc emits for the corresponding Exo procedure, so this library links
+ * wherever the generated C was linked (the `add_exo_library` CMake target,
+ * src/exo/cmake/AddExoLibrary.cmake:29-31).  ABI rules, from
+ * src/exo/backend/LoopIR_compiler.py:524-619 and src/exo/core/LoopIR.py:436-466:
+ *   - first parameter `ctxt`; sizes are int_fast32_t by value; bool by value;
+ *   - numeric scalars (e.g. `scale : f32`) are passed BY POINTER;
+ *   - tensors are raw pointers to dense row-major data; the callee allocates
+ *     nothing the caller has to free; arguments must not alias;
+ *   - return type is void: there is no error channel in the reference.  This
+ *     library adds one that existing callers may ignore: exo_b200_last_error().
+ *
+ * Pointers may be host memory (as in the reference; data is staged to the GPU
+ * and back inside the call, which returns when the result is in place) or
+ * CUDA device memory (used in place; the kernel is enqueued on the context's
+ * stream and the call returns without synchronising).  All work is done on the
+ * GPU; there is no CPU code path.
+ *
+ * `ctxt`: the `void *ctxt` functions accept NULL (process default context) or
+ * an exo_b200_Context* made by exo_b200_context_create().  The Gemmini-typed
+ * functions receive an UNINITIALISED pointer from their reference callers
+ * (apps/gemmini/test/run_matmul.c:49-52), so they never look at ctxt.
+ *
+ * Thread safety: calls that share a context are serialised by the caller (the
+ * reference's sgemm_exo is not reentrant either: it keeps tiles in function
+ * statics, tests/golden/test_apps/test_x86_sgemm.txt:797,804).
+ */
+#pragma once
+#ifndef EXO_B200_H
+#define EXO_B200_H
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#include <stdbool.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#pragma GCC visibility push(default) /* the library itself is built with hidden visibility */
+#endif
+
+/* ------------------------------------------------------------------------
+ * Reference-identical entry points
+ * --------------------------------------------------------------------- */
+
+/* sgemm_exo(M, N, K : size, A : f32[M,K], B : f32[K,N], C : f32[M,N]):  C += A * B
+ * Replaces tests/golden/test_apps/test_x86_sgemm.txt:69 (apps/x86/sgemm/sgemm.py:11-23,194).
+ * Default arithmetic: exact fp32 FFMA, one fused-multiply-add chain per output
+ * in increasing k starting from the incoming C -- bit-identical to the
+ * generated AVX-512 code.  EXOB200_SGEMM_PATH=3xtf32 (or the context setting)
+ * selects the tensor-core path instead. */
+void sgemm_exo( void *ctxt, int_fast32_t M, int_fast32_t N, int_fast32_t K, const float* A, const float* B, float* C );
+
+/* conv_specialized(inp : f32[5,82,102,128], output : f32[5,80,100,128],
+ *                  weights : f32[128,3,3,128], bias : f32[128])
+ * Replaces tests/golden/test_apps/test_x86_conv.txt:53 (apps/x86/conv/conv.py:53-119). */
+void conv_specialized( void *ctxt, const float* inp, float* output, const float* weights, const float* bias );
+
+/* conv: the unspecialised procedure of apps/x86/conv/conv.py:10-45 (argument
+ * order :11-24; call shape at apps/x86/conv/exo_conv.cpp:12-14).  NHWC input,
+ * weights f32[in_channel, kernel_dim, kernel_dim, out_channel], stride 1, no
+ * padding, bias, ReLU.  Requires out_h == in_h - kernel_dim + 1 (same for w). */
+void conv( void *ctxt, int_fast32_t out_h, int_fast32_t out_w, int_fast32_t out_channel, int_fast32_t in_h, int_fast32_t in_w, int_fast32_t in_channel, int_fast32_t kernel_dim, int_fast32_t batch_size, const float* inp, float* output, const float* weights, const float* bias );
+
+/* Gemmini-style int8 matmul (apps/gemmini/src/exo/matmul.py:7-43):
+ *   acc = sum_k (i32)A[i,k] * (i32)B[k,j];  t = round_half_even((f32)acc * *scale);
+ *   q = (int8)clamp(t, -128, 127);  if (act) q = max(q, 0);  C[i,j] = q
+ * A : i8[N,K], B : i8[K,M], C : i8[N,M] (Exo names the rows N and the columns M).
+ * Generic sizes; prototype shape confirmed by
+ * tests/golden/asplos25/test_gemmini_matmul_old/test_matmul.txt:92. */
+void matmul_on_cpu( void *ctxt, int_fast32_t N, int_fast32_t M, int_fast32_t K, const float* scale, bool act, const int8_t* A, const int8_t* B, int8_t* C );
+
+/* The size-specialised instances the Gemmini app exports
+ * (tests/golden/test_apps/test_gemmini_matmul.txt:99-198): `cpu_matmul_*` is the
+ * plain-C twin, `matmul_*` the accelerator version; both compute the same
+ * result (apps/gemmini/test/run_matmul.c:63 asserts equality) and both map to
+ * the same GPU kernel here.  ctxt is never dereferenced. */
+void cpu_matmul_512x512x512( void *ctxt, const float* scale, bool act, const int8_t* A, const int8_t* B, int8_t* C );
+void matmul_512x512x512( void *ctxt, const float* scale, bool act, const int8_t* A, const int8_t* B, int8_t* C );
+void cpu_matmul_4( void *ctxt, const float* scale, bool act, const int8_t* A, const int8_t* B, int8_t* C );   /* 12544 x 256, K = 64 */
+void matmul_4( void *ctxt, const float* scale, bool act, const int8_t* A, const int8_t* B, int8_t* C );
+void cpu_matmul_6( void *ctxt, const float* scale, bool act, const int8_t* A, const int8_t* B, int8_t* C );   /* 12544 x 64, K = 256 */
+void matmul_6( void *ctxt, const float* scale, bool act, const int8_t* A, const int8_t* B, int8_t* C );
+void cpu_matmul_14( void *ctxt, const float* scale, bool act, const int8_t* A, const int8_t* B, int8_t* C );  /* 3136 x 512, K = 128 */
+void matmul_14( void *ctxt, const float* scale, bool act, const int8_t* A, const int8_t* B, int8_t* C );
+void cpu_matmul_16( void *ctxt, const float* scale, bool act, const int8_t* A, const int8_t* B, int8_t* C );  /* 3136 x 128, K = 512 */
+void matmul_16( void *ctxt, const float* scale, bool act, const int8_t* A, const int8_t* B, int8_t* C );
+void cpu_matmul_27( void *ctxt, const float* scale, bool act, const int8_t* A, const int8_t* B, int8_t* C );  /* 784 x 1024, K = 256 */
+void matmul_27( void *ctxt, const float* scale, bool act, const int8_t* A, const int8_t* B, int8_t* C );
+
+/* Gemmini-style int8 NHWC convolution (apps/gemmini/src/exo/conv.py:6-55):
+ * weights i8[kernel_dim,kernel_dim,in_channel,out_channel], bias i32[1,out_channel]
+ * is the accumulator's start value, stride 1, caller-padded input
+ * (out_dim == in_dim - kernel_dim + 1), same epilogue as the matmul. */
+void conv_on_cpu_stride_1( void *ctxt, int_fast32_t batch_size, int_fast32_t out_dim, int_fast32_t out_channel, int_fast32_t kernel_dim, int_fast32_t in_channel, int_fast32_t in_dim, int8_t* output, const int32_t* bias, const int8_t* inp, const int8_t* weights, bool act, const float* scale );
+
+/* Size-specialised instances, tests/golden/test_apps/test_gemmini_conv.txt:96-146:
+ * conv_3: batch 4, 58->56, 64->64, 3x3;  conv_17: batch 4, 30->28, 128->128;
+ * conv_30: batch 4, 16->14, 256->256. */
+void conv_3_cpu( void *ctxt, int8_t* output, const int32_t* bias, const int8_t* inp, const int8_t* weights, bool act, const float* scale );
+void conv_3( void *ctxt, int8_t* output, const int32_t* bias, const int8_t* inp, const int8_t* weights, bool act, const float* scale );
+void conv_17_cpu( void *ctxt, int8_t* output, const int32_t* bias, const int8_t* inp, const int8_t* weights, bool act, const float* scale );
+void conv_17( void *ctxt, int8_t* output, const int32_t* bias, const int8_t* inp, const int8_t* weights, bool act, const float* scale );
+void conv_30_cpu( void *ctxt, int8_t* output, const int32_t* bias, const int8_t* inp, const int8_t* weights, bool act, const float* scale );
+void conv_30( void *ctxt, int8_t* output, const int32_t* bias, const int8_t* inp, const int8_t* weights, bool act, const float* scale );
+
+/* ------------------------------------------------------------------------
+ * Entry points with no generated counterpart, same conventions
+ * --------------------------------------------------------------------- */
+
+/* sgemm_exo with the arithmetic path fixed by name (same contract as
+ * tests/golden/test_apps/test_x86_sgemm.txt:69).  _ffma: exact fp32 chain.
+ * _3xtf32: tcgen05 tensor cores, each fp32 operand split into two TF32 terms,
+ * three MMAs per product, fp32 accumulation in tensor memory; not bit-identical,
+ * error comparable to fp32 accumulation in a different order. */
+void sgemm_exo_ffma( void *ctxt, int_fast32_t M, int_fast32_t N, int_fast32_t K, const float* A, const float* B, float* C );
+void sgemm_exo_3xtf32( void *ctxt, int_fast32_t M, int_fast32_t N, int_fast32_t K, const float* A, const float* B, float* C );
+
+/* gemm_bf16_exo(M, N, K, A : ui16[M,K] row-major, B : ui16 column-major KxN
+ * (element (k,j) at B[j*K + k]), C : ui16[M,N] row-major):  C = A * B.
+ * Exo has no bf16 type (src/exo/core/LoopIR.py:446-462 maps ui16 -> uint16_t), so
+ * bf16 bit patterns travel as uint16_t.  fp32 accumulation, one round-to-
+ * nearest-even to bf16 on output. */
+void gemm_bf16_exo( void *ctxt, int_fast32_t M, int_fast32_t N, int_fast32_t K, const uint16_t* A, const uint16_t* B, uint16_t* C );
+
+/* conv_nhwc_exo: apps/x86/conv/conv.py:10-45 generalised the way the
+ * convolution workload needs it: weights f32[kernel_dim,kernel_dim,in_channel,out_channel]
+ * (the layout of apps/gemmini/src/exo/conv.py:17), symmetric zero padding `pad`,
+ * stride 1, bias (may be NULL = zeros), optional ReLU.  Output is
+ * f32[batch, in_h + 2 pad - kernel_dim + 1, in_w + 2 pad - kernel_dim + 1, out_channel].
+ * Exact fp32: bias-initialised FMA chain in ky -> kx -> ci order. */
+void conv_nhwc_exo( void *ctxt, int_fast32_t batch_size, int_fast32_t in_h, int_fast32_t in_w, int_fast32_t in_channel, int_fast32_t out_channel, int_fast32_t kernel_dim, int_fast32_t pad, bool relu, const float* inp, float* output, const float* weights, const float* bias );
+
+/* ------------------------------------------------------------------------
+ * Context and error side channel (additions; the reference has neither)
+ * --------------------------------------------------------------------- */
+
+typedef struct exo_b200_Context exo_b200_Context;
+
+enum {
+  EXO_B200_OK = 0,
+  EXO_B200_ERR_INVALID_ARGUMENT = 1, /* size < 1, NULL tensor, broken size relation */
+  EXO_B200_ERR_CUDA = 2,             /* a CUDA runtime / driver call failed */
+  EXO_B200_ERR_TIMEOUT = 3,          /* a bounded device-side wait ran out */
+  EXO_B200_ERR_UNSUPPORTED = 4       /* no sm_100 device / shape not supported by this path */
+};
+
+enum { EXO_B200_SGEMM_FFMA = 0, EXO_B200_SGEMM_3XTF32 = 1 };
+
+/* device < 0: the current CUDA device.  stream: a cudaStream_t (NULL = the
+ * legacy default stream).  Returns NULL on failure (see last_error). */
+exo_b200_Context* exo_b200_context_create( int device, void* stream );
+void exo_b200_context_destroy( exo_b200_Context* ctxt );
+void exo_b200_context_set_stream( exo_b200_Context* ctxt, void* stream );
+void exo_b200_context_set_sgemm_path( exo_b200_Context* ctxt, int path );
+/* Stream used by calls that pass ctxt == NULL (and by the Gemmini-typed calls). */
+void exo_b200_set_default_stream( void* stream );
+/* Wait for the context's stream (NULL: default context) and collect device-side status. */
+int exo_b200_synchronize( exo_b200_Context* ctxt );
+
+/* Error of the most recent call on this thread (EXO_B200_OK if it succeeded). */
+int exo_b200_last_error( void );
+const char* exo_b200_last_error_string( void );
+const char* exo_b200_version( void );
+
+#if defined(__GNUC__)
+#pragma GCC visibility pop
+#endif
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* EXO_B200_H */

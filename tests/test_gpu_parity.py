@@ -1,0 +1,344 @@
+"""GPU parity tests: every kernel, called through the C ABI (ctypes), against
+the CPU oracle and the committed fixtures on the same seeded inputs.
+
+Bars: bit-exact for the fp32 FFMA paths (SGEMM, conv) and all int8 work;
+stated tolerances for 3xTF32 and bf16."""
+import os
+
+import numpy as np
+import pytest
+
+import oracle
+from tests import cases, inputs
+
+pytestmark = pytest.mark.gpu
+
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "reference_vectors.npz")
+
+
+@pytest.fixture(scope="module")
+def golden():
+    return np.load(GOLDEN)
+
+
+@pytest.fixture(scope="module")
+def lib():
+    import exo_b200
+
+    return exo_b200.library()
+
+
+@pytest.fixture(scope="module")
+def torch():
+    import torch
+
+    return torch
+
+
+def bits(a):
+    a = np.ascontiguousarray(a)
+    return a.view(np.uint32) if a.dtype == np.float32 else a
+
+
+def dev(torch, a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+# ------------------------------------------------------------- SGEMM (FFMA)
+@pytest.mark.parametrize("shape", cases.SGEMM_CASES)
+def test_sgemm_ffma_host_pointers_bit_exact(lib, port, golden, shape):
+    M, N, K = shape
+    A, B, C0 = cases.sgemm_inputs(M, N, K)
+    C = C0.copy()
+    lib.sgemm_exo(None, M, N, K, A, B, C)
+    assert np.array_equal(bits(C), bits(golden[f"sgemm_{M}x{N}x{K}"]))
+    assert np.array_equal(bits(C), bits(port.sgemm(A, B, C0.copy())))
+
+
+@pytest.mark.parametrize("shape", cases.SGEMM_DIGEST_CASES + [(129, 257, 40), (33, 128, 16), (32, 8192, 300)])
+def test_sgemm_ffma_device_pointers_bit_exact(lib, port, torch, golden, shape):
+    M, N, K = shape
+    A, B, C0 = cases.sgemm_inputs(M, N, K)
+    dA, dB, dC = dev(torch, A), dev(torch, B), dev(torch, C0)
+    lib.sgemm_exo_ffma(None, M, N, K, dA, dB, dC)
+    torch.cuda.synchronize()
+    C = dC.cpu().numpy()
+    key = f"sgemm_{M}x{N}x{K}_sha256"
+    if key in golden:
+        assert cases.digest(C) == str(golden[key])
+    else:
+        assert np.array_equal(bits(C), bits(port.sgemm(A, B, C0.copy())))
+
+
+def test_sgemm_ffma_signed_zero_and_specials(lib, port):
+    """-0.0 in C must survive a ragged K tail; inf/nan propagate like the chain."""
+    M, N, K = 9, 70, 19
+    A, B, C0 = cases.sgemm_inputs(M, N, K, seed=5)
+    A[3, :] = 0.0
+    C0[3, :] = -0.0
+    B[:, 5] = np.abs(B[:, 5])
+    A[4, 2] = np.inf
+    A[5, 1] = np.nan
+    C = C0.copy()
+    lib.sgemm_exo(None, M, N, K, A, B, C)
+    want = port.sgemm(A, B, C0.copy(), naive=True)
+    assert np.array_equal(bits(C), bits(want))
+
+
+def test_sgemm_ffma_full_size_rows_against_oracle(lib, port, torch):
+    """8192^3 is beyond what the CPU oracle finishes in seconds; because every
+    output row depends only on its own row of A, a sample of rows run through
+    the oracle at full N and K checks the full-size launch bit for bit."""
+    M = N = K = 4096
+    g = torch.Generator(device="cuda").manual_seed(7)
+    dA = torch.rand((M, K), generator=g, device="cuda") * 2 - 1
+    dB = torch.rand((K, N), generator=g, device="cuda") * 2 - 1
+    dC = torch.rand((M, N), generator=g, device="cuda") * 2 - 1
+    rows = [0, 1, 127, 128, 2049, 4095]
+    C0 = dC[rows].cpu().numpy()
+    lib.sgemm_exo(None, M, N, K, dA, dB, dC)
+    torch.cuda.synchronize()
+    port.set_threads(os.cpu_count() or 1)
+    try:
+        want = port.sgemm(dA[rows].cpu().numpy(), dB.cpu().numpy(), C0.copy())
+    finally:
+        port.set_threads(1)
+    assert np.array_equal(bits(dC[rows].cpu().numpy()), bits(want))
+
+
+# ------------------------------------------------------------ SGEMM (3xTF32)
+# Tolerance, stated: |C_gpu - C_fp64| <= 2e-6 * (|C0| + sum_k |a_ik| |b_kj|) per element.
+# Each product carries a relative error of about 2^-21 from the dropped lo*lo
+# term and the TF32 rounding of lo; accumulation is fp32 in tensor memory.
+TF32X3_REL = 2e-6
+
+
+@pytest.mark.parametrize("shape", [(128, 256, 32), (256, 512, 1024), (1000, 1000, 1000), (17, 4099, 513),
+                                   (4096, 64, 4096), (1, 8192, 2048), (300, 77, 129)])
+def test_sgemm_3xtf32_within_tolerance(lib, torch, shape):
+    M, N, K = shape
+    A, B, C0 = cases.sgemm_inputs(M, N, K)
+    dA, dB, dC = dev(torch, A), dev(torch, B), dev(torch, C0)
+    lib.sgemm_exo_3xtf32(None, M, N, K, dA, dB, dC)
+    torch.cuda.synchronize()
+    C = dC.cpu().numpy().astype(np.float64)
+    ref = C0.astype(np.float64) + A.astype(np.float64) @ B.astype(np.float64)
+    bound = TF32X3_REL * (np.abs(C0).astype(np.float64) + np.abs(A).astype(np.float64) @ np.abs(B).astype(np.float64))
+    err = np.abs(C - ref)
+    assert (err <= bound + 1e-30).all(), f"max err {err.max():.3e}, worst ratio {(err / bound).max():.3f}"
+
+
+# --------------------------------------------------------------------- conv
+def test_conv_specialized_fixture(lib, golden):
+    src = inputs.uniform_f32(11, (5, 82, 102, 128))
+    wts = inputs.uniform_f32(12, (128, 3, 3, 128))
+    bias = inputs.uniform_f32(13, (128,))
+    out = np.empty((5, 80, 100, 128), np.float32)
+    lib.conv_specialized(None, src, out, wts, bias)
+    assert cases.digest(out) == str(golden["conv_specialized_uniform_sha256"])
+
+
+def test_conv_specialized_reference_fill(lib, port, golden):
+    src, wts, bias = inputs.conv_instance_fill(5, 82, 102, 128, 128, 3)
+    out = np.empty((5, 80, 100, 128), np.float32)
+    lib.conv_specialized(None, src, out, wts, bias)
+    if cases.digest(src) + cases.digest(wts) + cases.digest(bias) == str(golden["conv_specialized_inputs_sha256"]):
+        assert cases.digest(out) == str(golden["conv_specialized_sha256"])
+    else:
+        port.set_threads(os.cpu_count() or 1)
+        try:
+            assert np.array_equal(bits(out), bits(port.conv(src, wts, bias)))
+        finally:
+            port.set_threads(1)
+
+
+@pytest.mark.parametrize("cfg", [
+    # batch, h, w, ci, co, k, pad, relu
+    (4, 56, 56, 64, 64, 3, 1, True),     # the 3x3 workload
+    (8, 28, 28, 256, 512, 1, 0, True),   # the 1x1 workload
+    (2, 9, 11, 8, 16, 3, 1, True),
+    (1, 7, 5, 3, 5, 3, 0, False),        # ragged channels: scalar loads
+    (3, 6, 6, 4, 130, 5, 2, True),
+])
+def test_conv_nhwc_bit_exact(lib, port, torch, cfg):
+    b, h, w, ci, co, k, pad, relu = cfg
+    inp = inputs.uniform_f32(101, (b, h, w, ci))
+    wts = inputs.uniform_f32(102, (k, k, ci, co))
+    bias = inputs.uniform_f32(103, (co,))
+    oh, ow = h + 2 * pad - k + 1, w + 2 * pad - k + 1
+    out = torch.empty((b, oh, ow, co), dtype=torch.float32, device="cuda")
+    lib.conv_nhwc_exo(None, b, h, w, ci, co, k, pad, relu, dev(torch, inp), out, dev(torch, wts), dev(torch, bias))
+    torch.cuda.synchronize()
+    port.set_threads(os.cpu_count() or 1)
+    try:
+        want = port.conv_nhwc(inp, wts, bias, pad, relu)
+    finally:
+        port.set_threads(1)
+    assert np.array_equal(bits(out.cpu().numpy()), bits(want))
+
+
+def test_conv_equals_im2col_plus_sgemm(lib, port):
+    """The decomposition of tests/test_im2col.py: marshal, then SGEMM into a
+    bias-initialised C, then ReLU -- done with the GPU SGEMM -- equals the
+    implicit-GEMM convolution bit for bit."""
+    b, h, w, ci, co, k, pad = 4, 56, 56, 64, 64, 3, 1
+    inp = inputs.uniform_f32(201, (b, h, w, ci))
+    wts = inputs.uniform_f32(202, (k, k, ci, co))
+    bias = inputs.uniform_f32(203, (co,))
+    out = np.empty((b, h, w, co), np.float32)
+    lib.conv_nhwc_exo(None, b, h, w, ci, co, k, pad, True, inp, out, wts, bias)
+    col = port.im2col_nhwc(inp, k, pad)
+    C = np.tile(bias, (col.shape[0], 1)).astype(np.float32)
+    lib.sgemm_exo(None, col.shape[0], co, col.shape[1], col, np.ascontiguousarray(wts.reshape(-1, co)), C)
+    C = np.where(C > 0, C, np.float32(0)).astype(np.float32)
+    assert np.array_equal(bits(out), bits(C.reshape(out.shape)))
+
+
+def test_conv_generic_entry_matches_specialized_layout(lib, port):
+    inp = inputs.uniform_f32(301, (2, 10, 12, 16))
+    wts = inputs.uniform_f32(302, (16, 3, 3, 32))  # [Ci, Kh, Kw, Co]
+    bias = inputs.uniform_f32(303, (32,))
+    out = np.empty((2, 8, 10, 32), np.float32)
+    lib.conv(None, 8, 10, 32, 10, 12, 16, 3, 2, inp, out, wts, bias)
+    assert np.array_equal(bits(out), bits(port.conv(inp, wts, bias)))
+
+
+# --------------------------------------------------------------------- int8
+@pytest.mark.parametrize("name", list(cases.I8_CASES))
+def test_i8_matmul_512_fixture(lib, golden, name):
+    A, B, scale, act = cases.i8_inputs(name)
+    C = np.empty((512, 512), np.int8)
+    s = np.array([scale], np.float32)
+    lib.cpu_matmul_512x512x512(None, s, act, A, B, C)
+    assert np.array_equal(C, golden[f"i8_{name}"])
+    C2 = np.empty_like(C)
+    lib.matmul_512x512x512(None, s, act, A, B, C2)
+    assert np.array_equal(C2, C)
+
+
+def test_i8_ties_and_uninitialised_ctxt(lib, golden):
+    import ctypes
+
+    A, B = cases.i8_tie_inputs()
+    C = np.empty((512, 512), np.int8)
+    # the reference runner passes an uninitialised context pointer (run_matmul.c:49-52)
+    garbage = ctypes.c_void_p(0xDEADBEEF0)
+    fn = lib.dll.cpu_matmul_512x512x512
+    s = np.array([1.0 / 256], np.float32)
+    fn(garbage, s.ctypes.data, False, A.ctypes.data, B.ctypes.data, C.ctypes.data)
+    assert lib.dll.exo_b200_last_error() == 0
+    assert np.array_equal(C, golden["i8_ties_s256"])
+    lib.matmul_on_cpu(None, 512, 512, 512, 1.0 / 512, True, A, B, C)
+    assert np.array_equal(C, golden["i8_ties_s512_relu"])
+
+
+@pytest.mark.parametrize("name", list(oracle.REF_MATMUL_SHAPES))
+def test_i8_reference_shapes(lib, golden, name):
+    N, M, K = oracle.REF_MATMUL_SHAPES[name]
+    x, y = inputs.gemmini_matmul_fill(N, M, K)
+    C = np.empty((N, M), np.int8)
+    getattr(lib, f"cpu_matmul_{name}")(None, np.array([2.0], np.float32), False, x, y, C)
+    assert cases.digest(C) == str(golden[f"i8_runner_{name}_sha256"])
+    A = inputs.int8(700 + N % 97, (N, K), -16, 15)
+    B = inputs.int8(701 + M % 89, (K, M), -16, 15)
+    getattr(lib, f"matmul_{name}")(None, np.array([1.0 / 64], np.float32), True, A, B, C)
+    assert cases.digest(C) == str(golden[f"i8_shape_{name}_sha256"])
+
+
+@pytest.mark.parametrize("shape", [(1, 1, 1), (5, 7, 17), (64, 48, 16), (130, 300, 256), (257, 129, 4096),
+                                   (128, 256, 128), (1000, 520, 272)])
+@pytest.mark.parametrize("scale,act", [(1.0 / 256, False), (0.3, True), (2.0 ** -7, True)])
+def test_i8_generic_shapes(lib, port, torch, shape, scale, act):
+    N, M, K = shape
+    A = inputs.int8(N + K, (N, K), -20, 20)
+    B = inputs.int8(M + K + 1, (K, M), -20, 20)
+    dC = torch.empty((N, M), dtype=torch.int8, device="cuda")
+    lib.matmul_on_cpu(None, N, M, K, float(scale), act, dev(torch, A), dev(torch, B), dC)
+    torch.cuda.synchronize()
+    assert np.array_equal(dC.cpu().numpy(), port.matmul_i8(A, B, scale, act))
+
+
+def test_i8_large_accumulator_rounding(lib):
+    K = 4096
+    A = np.full((128, K), 127, np.int8)
+    B = np.full((K, 256), 127, np.int8)
+    B[:5, 1] = 126
+    B[:3, 2] = 125
+    A[1, :7] = 126
+    acc = A.astype(np.int64) @ B.astype(np.int64)
+    scale = np.float32(2.0 ** -19)
+    want = np.clip(np.rint(acc.astype(np.float32) * scale), -128, 127).astype(np.int8)
+    C = np.empty((128, 256), np.int8)
+    lib.matmul_on_cpu(None, 128, 256, K, float(scale), False, A, B, C)
+    assert np.array_equal(C, want)
+
+
+def test_i8_4096_cubed(lib, port, torch):
+    """The full-size int8 workload, bit-exact against the oracle on a row sample
+    (rows are independent), with the saturation rate the workload implies."""
+    n = 4096
+    A = inputs.int8(41, (n, n))
+    B = inputs.int8(42, (n, n))
+    dC = torch.empty((n, n), dtype=torch.int8, device="cuda")
+    for act in (False, True):
+        lib.matmul_on_cpu(None, n, n, n, 1.0 / 256, act, dev(torch, A), dev(torch, B), dC)
+        torch.cuda.synchronize()
+        C = dC.cpu().numpy()
+        rows = np.r_[0:8, 127:131, 2047:2050, 4088:4096]
+        port.set_threads(os.cpu_count() or 1)
+        try:
+            want = port.matmul_i8(np.ascontiguousarray(A[rows]), B, 1.0 / 256, act)
+        finally:
+            port.set_threads(1)
+        assert np.array_equal(C[rows], want)
+
+
+@pytest.mark.parametrize("name", list(oracle.REF_CONV_I8_SHAPES))
+def test_i8_conv_reference_shapes(lib, golden, name):
+    b, od, co, kd, ci, ind = oracle.REF_CONV_I8_SHAPES[name]
+    inp, w, bias = inputs.gemmini_conv_fill(b, ind, ci, co, kd)
+    out = np.empty((b, od, od, co), np.int8)
+    getattr(lib, f"conv_{name}_cpu")(None, out, bias, inp, w, False, np.array([1.0], np.float32))
+    assert cases.digest(out) == str(golden[f"i8conv_runner_{name}_sha256"])
+    inp = inputs.int8(800 + ci, (b, ind, ind, ci), -16, 15)
+    w = inputs.int8(801 + co, (kd, kd, ci, co), -16, 15)
+    bias = inputs.int32(802, (1, co), -5000, 5000)
+    getattr(lib, f"conv_{name}")(None, out, bias, inp, w, True, np.array([1.0 / 128], np.float32))
+    assert cases.digest(out) == str(golden[f"i8conv_seeded_{name}_sha256"])
+    lib.conv_on_cpu_stride_1(None, b, od, co, kd, ci, ind, out, bias, inp, w, True, 1.0 / 128)
+    assert cases.digest(out) == str(golden[f"i8conv_seeded_{name}_sha256"])
+
+
+# --------------------------------------------------------------------- bf16
+# Tolerance, stated: |C_gpu - C_ref| <= 2^-8 |C_ref| + 1e-3 * sqrt(K) * 4e-4 where C_ref is
+# the reference fp32 SGEMM chain on the widened inputs rounded once to bf16 (one bf16 ulp
+# of slack for a different fp32 accumulation order plus an absolute floor near zero).
+@pytest.mark.parametrize("shape", [(128, 256, 64), (256, 512, 512), (384, 300, 1000), (130, 70, 72), (2048, 2048, 2048)])
+def test_gemm_bf16_against_reference_sgemm(lib, port, torch, shape):
+    M, N, K = shape
+    A = inputs.normal_bf16(51, (M, K))
+    Bt = inputs.normal_bf16(52, (N, K))  # column-major K x N
+    dC = torch.empty((M, N), dtype=torch.int16, device="cuda")
+    lib.gemm_bf16_exo(None, M, N, K, dev(torch, A.view(np.int16)), dev(torch, Bt.view(np.int16)), dC)
+    torch.cuda.synchronize()
+    C = inputs.bf16_bits_to_f32(dC.cpu().numpy().view(np.uint16))
+    port.set_threads(os.cpu_count() or 1)
+    try:
+        ref = inputs.bf16_bits_to_f32(port.gemm_bf16(A, Bt))
+    finally:
+        port.set_threads(1)
+    tol = 2.0 ** -8 * np.abs(ref) + 1e-3 * np.sqrt(K) * 4e-4
+    err = np.abs(C - ref)
+    assert (err <= tol).all(), f"max err {err.max():.3e} at ref {ref.reshape(-1)[err.argmax()]:.3e}"
+    # and most outputs are bit-identical to the reference rounding
+    assert (C == ref).mean() > 0.9
+
+
+def test_error_side_channel_on_gpu(lib):
+    import exo_b200
+
+    A = np.zeros((8, 8), np.float32)
+    with pytest.raises(exo_b200.ExoB200Error):
+        lib.sgemm_exo(None, -1, 8, 8, A, A, A)
+    lib.sgemm_exo(None, 8, 8, 8, A, A, A)  # a good call clears the error
+    assert lib.dll.exo_b200_last_error() == 0
