@@ -310,7 +310,7 @@ def test_i8_conv_reference_shapes(lib, golden, name):
 
 
 # --------------------------------------------------------------------- bf16
-# Tolerance, stated: |C_gpu - C_ref| <= 2^-8 |C_ref| + 1e-3 * sqrt(K) * 4e-4 where C_ref is
+# Tolerance, stated: |C_gpu - C_ref| <= 2^-7 |C_ref| + 1e-3 * sqrt(K) * 4e-4 where C_ref is
 # the reference fp32 SGEMM chain on the widened inputs rounded once to bf16 (one bf16 ulp
 # of slack for a different fp32 accumulation order plus an absolute floor near zero).
 @pytest.mark.parametrize("shape", [(128, 256, 64), (256, 512, 512), (384, 300, 1000), (130, 70, 72), (2048, 2048, 2048)])
@@ -327,7 +327,7 @@ def test_gemm_bf16_against_reference_sgemm(lib, port, torch, shape):
         ref = inputs.bf16_bits_to_f32(port.gemm_bf16(A, Bt))
     finally:
         port.set_threads(1)
-    tol = 2.0 ** -8 * np.abs(ref) + 1e-3 * np.sqrt(K) * 4e-4
+    tol = 2.0 ** -7 * np.abs(ref) + 1e-3 * np.sqrt(K) * 4e-4
     err = np.abs(C - ref)
     assert (err <= tol).all(), f"max err {err.max():.3e} at ref {ref.reshape(-1)[err.argmax()]:.3e}"
     # and most outputs are bit-identical to the reference rounding
