@@ -215,7 +215,9 @@ def run_reference_arm(args):
 
 
 # ---------------------------------------------------------------- workloads
-def workload_config(name, gpus):
+def workload_config(name, gpus, shape=None):
+    if shape is not None:
+        return {"workload": f"{name} (profiling case, not the headline shape)", "shape": list(shape)}
     if name == "bf16":
         M, N, K = BF16_SHAPE
         return {"workload": f"bf16 GEMM M={M} N={N} K={K}, A row-major, B column-major, fp32 accumulate, bf16 out",
@@ -227,17 +229,22 @@ def workload_config(name, gpus):
 class Workload:
     """flops per step, a device-resident step, and a host-buffer (e2e) step."""
 
-    def __init__(self, name, lib, torch, rank, world):
+    def __init__(self, name, lib, torch, rank, world, shape=None, dist=None):
         self.name, self.lib, self.torch, self.rank, self.world = name, lib, torch, rank, world
         self.launches_per_step = 1
+        self.custom_shape = shape
+        self.dist = dist
         getattr(self, f"_setup_{name}")()
 
     # -- bf16 headline
     def _setup_bf16(self):
+        from exo_b200.shard import ShardedGemm
+
         t = self.torch
-        M, N, K = BF16_SHAPE
+        M, N, K = self.custom_shape or BF16_SHAPE
         self.dtype = "bf16"
-        rows = M // self.world
+        self.sharded = ShardedGemm(self.dist, M, N, K)  # row blocks on CTA-tile boundaries
+        rows = self.sharded.block.rows
         self.shape = (rows, N, K)
         g = t.Generator(device="cuda").manual_seed(1234 + self.rank)
         self.A = (t.randn((rows, K), generator=g, device="cuda") * 0.02).to(t.bfloat16)
@@ -249,10 +256,11 @@ class Workload:
         self.flops_total = 2.0 * M * N * K
         self.flops_local = 2.0 * rows * N * K
         self.bound = "tensor"
+        if self.custom_shape is None and self.world > 1 and any(b.rows != rows for b in self.sharded.blocks):
+            raise SystemExit("row blocks must be equal for the scaling run")
 
     def step_bf16(self):
-        r, N, K = self.shape
-        self.lib.gemm_bf16_exo(None, r, N, K, self.A, self.B, self.C)
+        self.sharded.step(self.A, self.B, self.C)
 
     def host_bf16(self):
         t = self.torch
@@ -262,12 +270,13 @@ class Workload:
         return (self.hA.numel() + self.hB.numel()) * 2, self.hC.numel() * 2
 
     def e2e_bf16(self):
-        r, N, K = self.shape
-        self.lib.gemm_bf16_exo(None, r, N, K, self.hA, self.hB, self.hC)
+        self.sharded.step(self.hA, self.hB, self.hC)
 
     # -- fp32 SGEMM 8192^3 (FFMA exact / 3xTF32)
     def _setup_sgemm(self, n=8192):
         t = self.torch
+        if self.custom_shape:
+            n = self.custom_shape[0]
         self.dtype = "f32"
         self.shape = (n, n, n)
         g = t.Generator(device="cuda").manual_seed(5)
@@ -311,6 +320,8 @@ class Workload:
     # -- int8 4096^3
     def _setup_i8(self, n=4096):
         t = self.torch
+        if self.custom_shape:
+            n = self.custom_shape[0]
         self.dtype = "i8"
         self.shape = (n, n, n)
         g = t.Generator(device="cuda").manual_seed(6)
@@ -413,7 +424,8 @@ def run_ours(args):
     lib = exo_b200.library()
     peaks = measured_peaks()
 
-    wl = Workload(args.workload, lib, torch, rank, world)
+    shape = tuple(int(x) for x in args.shape.split("x")) if args.shape else None
+    wl = Workload(args.workload, lib, torch, rank, world, shape=shape, dist=dist)
     bcast_ms = None
     if dist is not None:
         # the one exchange of the sharded GEMM: B from rank 0 to every GPU over NVLink
@@ -421,7 +433,7 @@ def run_ours(args):
         dist.barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        dist.broadcast(wl.B, src=0)
+        wl.sharded.broadcast_b(wl.B)
         e1.record()
         torch.cuda.synchronize()
         bcast_ms = e0.elapsed_time(e1)
@@ -436,10 +448,14 @@ def run_ours(args):
     value = wl.flops_total / (ms / 1e3) / 1e12
 
     # end to end: pinned host buffers through the C ABI, copies inside the timed region
-    h2d, d2h = wl.host()
-    e2e_steps = max(1, min(args.steps, 5))
-    e2e_ms, _, _ = time_steps(torch, wl.e2e_step, e2e_steps, 1, dist)
-    e2e_value = wl.flops_total / (e2e_ms / 1e3) / 1e12
+    if args.no_e2e:
+        h2d = d2h = 0
+        e2e_steps, e2e_ms, e2e_value = 0, None, None
+    else:
+        h2d, d2h = wl.host()
+        e2e_steps = max(1, min(args.steps, 5))
+        e2e_ms, _, _ = time_steps(torch, wl.e2e_step, e2e_steps, 1, dist)
+        e2e_value = wl.flops_total / (e2e_ms / 1e3) / 1e12
 
     if rank != 0:
         if dist is not None:
@@ -456,7 +472,7 @@ def run_ours(args):
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic",
-        "config": workload_config(args.workload, world), "clocks": clocks,
+        "config": workload_config(args.workload, world, shape), "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": d2h * world,
                 "ms_per_step": e2e_ms, "steps": e2e_steps},
         "gpu_launches": wl.launches_per_step * args.steps,
@@ -513,6 +529,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="bf16", choices=["bf16", "sgemm_ffma", "sgemm_3xtf32", "i8"])
+    ap.add_argument("--shape", default=None, help="MxNxK override for small profiling cases")
+    ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()

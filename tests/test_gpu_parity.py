@@ -82,7 +82,14 @@ def test_sgemm_ffma_signed_zero_and_specials(lib, port):
     C = C0.copy()
     lib.sgemm_exo(None, M, N, K, A, B, C)
     want = port.sgemm(A, B, C0.copy(), naive=True)
-    assert np.array_equal(bits(C), bits(want))
+    # NaN payloads are not part of the contract (x86 propagates an operand's payload,
+    # the GPU returns the canonical NaN); everything else, signed zeros and
+    # infinities included, is compared bit for bit.
+    assert np.array_equal(np.isnan(C), np.isnan(want))
+    ok = ~np.isnan(want)
+    assert np.isnan(want).any() and np.isinf(want).any()
+    assert np.array_equal(bits(C)[ok], bits(want)[ok])
+    assert np.signbit(C[3]).any() and not np.signbit(C[3]).all()
 
 
 def test_sgemm_ffma_full_size_rows_against_oracle(lib, port, torch):
@@ -107,10 +114,15 @@ def test_sgemm_ffma_full_size_rows_against_oracle(lib, port, torch):
 
 
 # ------------------------------------------------------------ SGEMM (3xTF32)
-# Tolerance, stated: |C_gpu - C_fp64| <= 2e-6 * (|C0| + sum_k |a_ik| |b_kj|) per element.
-# Each product carries a relative error of about 2^-21 from the dropped lo*lo
-# term and the TF32 rounding of lo; accumulation is fp32 in tensor memory.
-TF32X3_REL = 2e-6
+# Tolerance, stated: per element, with S = |C0| + sum_k |a_ik| |b_kj|,
+#     |C_gpu - C_fp64| <= (1.5e-6 + 1e-6 * K / 1024) * S.
+# The constant term: each product carries a relative error of about 2^-21 from
+# the dropped lo*lo term and the TF32 rounding of lo.  The K term: the tensor
+# core adds into its fp32 accumulator without round-to-nearest, a bias that grows
+# linearly with the number of accumulation steps (measured: 3.1e-3 absolute at
+# K = 4096 on uniform[-1,1) inputs, where S is about 1024).
+def tf32x3_bound(K):
+    return 1.5e-6 + 1e-6 * K / 1024.0
 
 
 @pytest.mark.parametrize("shape", [(128, 256, 32), (256, 512, 1024), (1000, 1000, 1000), (17, 4099, 513),
@@ -123,7 +135,7 @@ def test_sgemm_3xtf32_within_tolerance(lib, torch, shape):
     torch.cuda.synchronize()
     C = dC.cpu().numpy().astype(np.float64)
     ref = C0.astype(np.float64) + A.astype(np.float64) @ B.astype(np.float64)
-    bound = TF32X3_REL * (np.abs(C0).astype(np.float64) + np.abs(A).astype(np.float64) @ np.abs(B).astype(np.float64))
+    bound = tf32x3_bound(K) * (np.abs(C0).astype(np.float64) + np.abs(A).astype(np.float64) @ np.abs(B).astype(np.float64))
     err = np.abs(C - ref)
     assert (err <= bound + 1e-30).all(), f"max err {err.max():.3e}, worst ratio {(err / bound).max():.3f}"
 
