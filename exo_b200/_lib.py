@@ -28,6 +28,7 @@ PROTOTYPES = {
     "matmul_on_cpu": [vp, i64, i64, i64, vp, cbool, vp, vp, vp],
     "conv_on_cpu_stride_1": [vp] + [i64] * 6 + [vp] * 4 + [cbool, vp],
     "gemm_bf16_exo": [vp, i64, i64, i64, vp, vp, vp],
+    "matmul_on_cpu_static": [vp, i64, i64, i64, vp, cbool, vp, vp, vp],
 }
 for _n in _MM_INSTANCES:
     PROTOTYPES[f"cpu_matmul_{_n}"] = [vp, vp, cbool, vp, vp, vp]

@@ -594,4 +594,129 @@ cudaError_t launch_sgemm_3xtf32_tc(exo_b200_Context* ctx, int64_t M, int64_t N, 
   return launch_tc<MODE_TF32X3>(ctx, ma0, ma1, mb0, mb1, M, N, Kp, ep);
 }
 
+// --------------------------------------------------------------------------
+// matmul_on_cpu_static: the int8 matmul for callers that must not allocate.
+//
+// Some callers cannot call cudaMalloc at the point where they need a matmul:
+// code that runs between the begin and end of a stream capture, code that has
+// handed all device memory to its own arena and must never see the driver
+// allocator move under it, and latency-critical loops where an allocation's
+// implicit device synchronisation is not acceptable.  The regular entry points
+// keep a grow-only scratch buffer in their context (for the K-major copy of B
+// that the tensor-core kernel reads), so their first call with a new size
+// allocates.  This variant keeps that scratch in a fixed array inside the
+// library image instead: every GPU that loads the library holds
+// EXO_B200_STATIC_SCRATCH_BYTES of it until the process exits.
+//
+// The array's name is only a host-side handle for the symbol; the kernels need
+// its device address, which is looked up once per device (cudaGetSymbolAddress,
+// with that device current) on the first call made on that device.  That first
+// call also loads the kernels and sets their shared-memory attribute, so make
+// it before starting any stream capture.
+//
+// All calls share the one array: two calls whose kernels overlap on the GPU
+// (different streams, no dependency) race on it.  Nothing in it has to start at
+// zero -- the transpose pre-pass overwrites every byte the GEMM then reads.
+constexpr size_t kStaticScratchBytes = 4u << 20;  // K * M <= 4 Mi int8 elements
+static __device__ __align__(256) int8_t g_static_bt_scratch[kStaticScratchBytes];
+
+namespace {
+
+struct StaticDeviceState {
+  bool ready = false;
+  int8_t* scratch = nullptr;  // device address of g_static_bt_scratch on this device
+  int sm_count = 0;
+};
+constexpr int kMaxDevices = 64;
+StaticDeviceState g_static_state[kMaxDevices];
+std::mutex g_static_mutex;
+
+// Once per device, with that device current.  Allocates nothing.
+StaticDeviceState* static_state_for_current_device() {
+  int dev = 0;
+  if (!check_cuda(cudaGetDevice(&dev), "cudaGetDevice")) return nullptr;
+  if (dev < 0 || dev >= kMaxDevices) {
+    set_error(EXO_B200_ERR_UNSUPPORTED, "matmul_on_cpu_static: device ordinal out of range");
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lock(g_static_mutex);
+  StaticDeviceState& st = g_static_state[dev];
+  if (st.ready) return &st;
+  int major = 0;
+  if (!check_cuda(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev), "cudaDeviceGetAttribute"))
+    return nullptr;
+  if (major != 10) {
+    set_error(EXO_B200_ERR_UNSUPPORTED, "matmul_on_cpu_static: this library contains sm_100a code only");
+    return nullptr;
+  }
+  if (!check_cuda(cudaDeviceGetAttribute(&st.sm_count, cudaDevAttrMultiProcessorCount, dev),
+                  "cudaDeviceGetAttribute"))
+    return nullptr;
+  void* ptr = nullptr;
+  if (!check_cuda(cudaGetSymbolAddress(&ptr, g_static_bt_scratch), "cudaGetSymbolAddress(static scratch)"))
+    return nullptr;
+  if (!check_cuda(cudaFuncSetAttribute(gemm_tc_kernel<MODE_I8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       smem_bytes<MODE_I8>()),
+                  "cudaFuncSetAttribute"))
+    return nullptr;
+  st.scratch = static_cast<int8_t*>(ptr);
+  st.ready = true;
+  return &st;
+}
+
+}  // namespace
 }  // namespace exob200
+
+extern "C" __attribute__((visibility("default"))) void matmul_on_cpu_static(
+    void* stream, int_fast32_t N, int_fast32_t M, int_fast32_t K, const float* scale, bool act, const int8_t* A,
+    const int8_t* B, int8_t* C) {
+  using namespace exob200;
+  const char* fn = "matmul_on_cpu_static";
+  clear_error();
+  if (N < 1 || M < 1 || K < 1 || !scale || !A || !B || !C) {
+    set_error(EXO_B200_ERR_INVALID_ARGUMENT, std::string(fn) + ": sizes must be >= 1 and pointers non-NULL");
+    return;
+  }
+  if (N > INT32_MAX || M > INT32_MAX || K > INT32_MAX) {
+    set_error(EXO_B200_ERR_INVALID_ARGUMENT, std::string(fn) + ": size out of range");
+    return;
+  }
+  if ((size_t)K * (size_t)M > kStaticScratchBytes) {
+    set_error(EXO_B200_ERR_UNSUPPORTED,
+              std::string(fn) + ": K * M = " + std::to_string((size_t)K * (size_t)M) + " exceeds the static scratch of " +
+                  std::to_string(kStaticScratchBytes) + " int8 elements; use matmul_on_cpu");
+    return;
+  }
+  if (!is_device_pointer(A) || !is_device_pointer(B) || !is_device_pointer(C) || is_device_pointer(scale)) {
+    set_error(EXO_B200_ERR_INVALID_ARGUMENT,
+              std::string(fn) + ": A, B, C must be device memory (host buffers would need staging allocations) "
+                                "and scale host memory (it is read when the call is made)");
+    return;
+  }
+  StaticDeviceState* st = static_state_for_current_device();
+  if (!st) return;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const float sc = *scale;
+  if (K % 16 != 0 || (reinterpret_cast<uintptr_t>(A) & 15u) != 0) {
+    // pitches TMA cannot express: the SIMT kernel needs no scratch at all
+    check_cuda(launch_matmul_i8_simt(s, N, M, K, sc, act, A, B, C), fn);
+    return;
+  }
+  const int64_t rows = N, cols = M;
+  dim3 tgrid((unsigned)((K + 127) / 128), (unsigned)((cols + 127) / 128));
+  const int vec_in = (cols % 4 == 0 && (reinterpret_cast<uintptr_t>(B) & 3u) == 0) ? 1 : 0;
+  transpose_i8_kernel<<<tgrid, 256, 0, s>>>(B, (int)K, (int)cols, (int)K, st->scratch, vec_in);
+  if (!check_cuda(cudaGetLastError(), fn)) return;
+  CUtensorMap ma, mb;
+  if (!make_kmajor_map(&ma, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, A, rows, K, K, BM)) return;
+  if (!make_kmajor_map(&mb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, st->scratch, cols, K, K, BN)) return;
+  EpiParams ep{C, cols, sc, act ? 1 : 0, (cols % 16 == 0 && (reinterpret_cast<uintptr_t>(C) & 15u) == 0) ? 1 : 0};
+  const int64_t tiles_m = (rows + BM - 1) / BM, tiles_n = (cols + BN - 1) / BN;
+  const int grid = (int)std::min<int64_t>(tiles_m * tiles_n, st->sm_count);
+  // no status word: a bounded device-side wait that runs out ends the kernel but is not reported here
+  gemm_tc_kernel<MODE_I8><<<grid, NUM_THREADS, smem_bytes<MODE_I8>(), s>>>(ma, ma, mb, mb, (int)rows, (int)cols,
+                                                                           (int)K, ep, nullptr, (int)tiles_m,
+                                                                           (int)tiles_n);
+  check_cuda(cudaGetLastError(), fn);
+}
+

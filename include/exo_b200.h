@@ -136,6 +136,26 @@ void gemm_bf16_exo( void *ctxt, int_fast32_t M, int_fast32_t N, int_fast32_t K, 
  * Exact fp32: bias-initialised FMA chain in ky -> kx -> ci order. */
 void conv_nhwc_exo( void *ctxt, int_fast32_t batch_size, int_fast32_t in_h, int_fast32_t in_w, int_fast32_t in_channel, int_fast32_t out_channel, int_fast32_t kernel_dim, int_fast32_t pad, bool relu, const float* inp, float* output, const float* weights, const float* bias );
 
+/* matmul_on_cpu_static: the int8 matmul of matmul_on_cpu for callers that cannot
+ * allocate device memory where they need the result -- inside a stream capture,
+ * under an arena that owns all device memory, or in a loop that must not meet an
+ * allocation's implicit synchronisation.  It has no counterpart in the reference
+ * (whose C code never allocates on a device); same arithmetic and same result
+ * as matmul_on_cpu.
+ *   - The first parameter is the cudaStream_t to launch on (NULL = default
+ *     stream), not a context: contexts own allocations.
+ *   - A, B, C must be device memory; scale is host memory, read during the call.
+ *   - Scratch for the K-major copy of B is a fixed array in the library image,
+ *     EXO_B200_STATIC_SCRATCH_BYTES per GPU for the life of the process;
+ *     K * M beyond it is rejected (EXO_B200_ERR_UNSUPPORTED, output untouched).
+ *   - The first call on each device looks up the array's device address and
+ *     loads the kernels: make that call before any stream capture begins.
+ *   - All calls share the array: calls whose kernels may overlap on the GPU
+ *     race; order them on one stream or with events.
+ *   - Calls no cudaMalloc / cudaFree / cudaHostAlloc and creates no context. */
+#define EXO_B200_STATIC_SCRATCH_BYTES (4u << 20)
+void matmul_on_cpu_static( void *stream, int_fast32_t N, int_fast32_t M, int_fast32_t K, const float* scale, bool act, const int8_t* A, const int8_t* B, int8_t* C );
+
 /* ------------------------------------------------------------------------
  * Context and error side channel (additions; the reference has neither)
  * --------------------------------------------------------------------- */
