@@ -76,7 +76,7 @@ def test_sgemm_ffma_signed_zero_and_specials(lib, port):
     A, B, C0 = cases.sgemm_inputs(M, N, K, seed=5)
     A[3, :] = 0.0
     C0[3, :] = -0.0
-    B[:, 5] = np.abs(B[:, 5])
+    B[:, 5] = -np.abs(B[:, 5])  # every product in column 5 of row 3 is -0: the -0 in C survives
     A[4, 2] = np.inf
     A[5, 1] = np.nan
     C = C0.copy()
@@ -89,7 +89,7 @@ def test_sgemm_ffma_signed_zero_and_specials(lib, port):
     ok = ~np.isnan(want)
     assert np.isnan(want).any() and np.isinf(want).any()
     assert np.array_equal(bits(C)[ok], bits(want)[ok])
-    assert np.signbit(C[3]).any() and not np.signbit(C[3]).all()
+    assert np.signbit(C[3, 5]) and C[3, 5] == 0 and not np.signbit(C[3]).all()
 
 
 def test_sgemm_ffma_full_size_rows_against_oracle(lib, port, torch):
