@@ -25,6 +25,7 @@
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 namespace exob200 {
 namespace ffma {
@@ -50,7 +51,26 @@ __device__ __forceinline__ void cp_async4(float* smem, const float* g, bool vali
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(s), "l"(g), "r"(n) : "memory");
 }
 
-template <class Policy>
+// Packed fp32 pairs: fma.rn.f32x2 performs two IEEE fused multiply-adds (one per
+// 32-bit half, round-to-nearest, denormals kept) in ONE issue slot.  The SIMT
+// SGEMM is issue-bound (one FFMA per slot, plus loads and address arithmetic),
+// so pairing adjacent output columns halves the slots the FMAs need while every
+// component still sees exactly fmaf(a, b, c).
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+
+template <class Policy, bool PACKED>
 __global__ void __launch_bounds__(THREADS, 2) tile_kernel(const Policy P, int tiles_m, int tiles_n) {
   __shared__ __align__(16) float As[2][BK][AS_PITCH];
   __shared__ __align__(16) float Bs[2][BK][BN];
@@ -105,17 +125,23 @@ __global__ void __launch_bounds__(THREADS, 2) tile_kernel(const Policy P, int ti
   };
 
   // accumulators start at the chain's first operand
-  float acc[8][8];
+  float acc[PACKED ? 1 : 8][PACKED ? 1 : 8];
+  uint64_t acc2[PACKED ? 8 : 1][PACKED ? 4 : 1];  // [row][column pair]
 #pragma unroll
   for (int i = 0; i < 8; i++) {
     const int row = m0 + (i >> 2) * 64 + ty * 4 + (i & 3);
 #pragma unroll
     for (int jq = 0; jq < 2; jq++) {
       const float4 v = P.init(row, n0 + jq * 64 + tx * 4);
-      acc[i][jq * 4 + 0] = v.x;
-      acc[i][jq * 4 + 1] = v.y;
-      acc[i][jq * 4 + 2] = v.z;
-      acc[i][jq * 4 + 3] = v.w;
+      if (PACKED) {
+        acc2[i][jq * 2 + 0] = pack2(v.x, v.y);
+        acc2[i][jq * 2 + 1] = pack2(v.z, v.w);
+      } else {
+        acc[i][jq * 4 + 0] = v.x;
+        acc[i][jq * 4 + 1] = v.y;
+        acc[i][jq * 4 + 2] = v.z;
+        acc[i][jq * 4 + 3] = v.w;
+      }
     }
   }
 
@@ -132,14 +158,26 @@ __global__ void __launch_bounds__(THREADS, 2) tile_kernel(const Policy P, int ti
     auto step = [&](int kk) {
       const float4 a0 = *reinterpret_cast<const float4*>(&As[buf][kk][ty * 4]);
       const float4 a1 = *reinterpret_cast<const float4*>(&As[buf][kk][64 + ty * 4]);
-      const float4 b0 = *reinterpret_cast<const float4*>(&Bs[buf][kk][tx * 4]);
-      const float4 b1 = *reinterpret_cast<const float4*>(&Bs[buf][kk][64 + tx * 4]);
       const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-      const float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+      if (PACKED) {
+        const ulonglong2 b0 = *reinterpret_cast<const ulonglong2*>(&Bs[buf][kk][tx * 4]);
+        const ulonglong2 b1 = *reinterpret_cast<const ulonglong2*>(&Bs[buf][kk][64 + tx * 4]);
+        const uint64_t b[4] = {b0.x, b0.y, b1.x, b1.y};
 #pragma unroll
-      for (int i = 0; i < 8; i++)
+        for (int i = 0; i < 8; i++) {
+          const uint64_t aa = pack2(a[i], a[i]);
 #pragma unroll
-        for (int j = 0; j < 8; j++) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+          for (int j = 0; j < 4; j++) acc2[i][j] = fma2(aa, b[j], acc2[i][j]);
+        }
+      } else {
+        const float4 b0 = *reinterpret_cast<const float4*>(&Bs[buf][kk][tx * 4]);
+        const float4 b1 = *reinterpret_cast<const float4*>(&Bs[buf][kk][64 + tx * 4]);
+        const float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+        for (int i = 0; i < 8; i++)
+#pragma unroll
+          for (int j = 0; j < 8; j++) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+      }
     };
     if (kmax == BK) {
 #pragma unroll
@@ -156,17 +194,37 @@ __global__ void __launch_bounds__(THREADS, 2) tile_kernel(const Policy P, int ti
   for (int i = 0; i < 8; i++) {
     const int row = m0 + (i >> 2) * 64 + ty * 4 + (i & 3);
 #pragma unroll
-    for (int jq = 0; jq < 2; jq++)
-      P.store(row, n0 + jq * 64 + tx * 4,
-              make_float4(acc[i][jq * 4], acc[i][jq * 4 + 1], acc[i][jq * 4 + 2], acc[i][jq * 4 + 3]));
+    for (int jq = 0; jq < 2; jq++) {
+      float4 v;
+      if (PACKED) {
+        unpack2(acc2[i][jq * 2 + 0], v.x, v.y);
+        unpack2(acc2[i][jq * 2 + 1], v.z, v.w);
+      } else {
+        v = make_float4(acc[i][jq * 4], acc[i][jq * 4 + 1], acc[i][jq * 4 + 2], acc[i][jq * 4 + 3]);
+      }
+      P.store(row, n0 + jq * 64 + tx * 4, v);
+    }
   }
+}
+
+// EXOB200_FFMA_SCALAR=1 selects the one-FMA-per-instruction variant (for A/B timing).
+inline bool use_packed() {
+  static const bool packed = [] {
+    const char* e = getenv("EXOB200_FFMA_SCALAR");
+    return !(e && e[0] == '1');
+  }();
+  return packed;
 }
 
 template <class Policy>
 cudaError_t launch_tiles(cudaStream_t stream, const Policy& P) {
   const int64_t tiles_m = (P.M + BM - 1) / BM, tiles_n = (P.N + BN - 1) / BN;
   if (tiles_m * tiles_n > INT32_MAX) return cudaErrorInvalidValue;
-  tile_kernel<Policy><<<(unsigned)(tiles_m * tiles_n), THREADS, 0, stream>>>(P, (int)tiles_m, (int)tiles_n);
+  const unsigned grid = (unsigned)(tiles_m * tiles_n);
+  if (use_packed())
+    tile_kernel<Policy, true><<<grid, THREADS, 0, stream>>>(P, (int)tiles_m, (int)tiles_n);
+  else
+    tile_kernel<Policy, false><<<grid, THREADS, 0, stream>>>(P, (int)tiles_m, (int)tiles_n);
   return cudaGetLastError();
 }
 
