@@ -32,6 +32,7 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 
+#include <cstdlib>
 #include <mutex>
 
 #include "i8_epilogue.cuh"
@@ -172,7 +173,10 @@ __device__ __forceinline__ void store_chunk(const EpiParams& ep, const uint32_t 
 }
 
 // ------------------------------------------------------------ the kernel
-template <int MODE>
+// BMN: B is read MN-major straight from the caller's row-major K x N array (no
+// transposing pre-pass): per stage BN*ELEM/128 TMA boxes {128 bytes of N, BK rows
+// of K}, and the B descriptor / instruction descriptor say "MN-major".
+template <int MODE, bool BMN = false>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmA1,
                const __grid_constant__ CUtensorMap tmB0, const __grid_constant__ CUtensorMap tmB1, int M, int N,
@@ -260,8 +264,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
           const int k0 = kb * BK;
           tma_load_2d(dst, &tmA0, bar, k0, m0);
           if (C::NA > 1) tma_load_2d(dst + A_TILE_BYTES, &tmA1, bar, k0, m0);
-          tma_load_2d(dst + C::NA * A_TILE_BYTES, &tmB0, bar, k0, n0);
-          if (C::NB > 1) tma_load_2d(dst + C::NA * A_TILE_BYTES + B_TILE_BYTES, &tmB1, bar, k0, n0);
+          if (BMN) {
+            constexpr int NBOX = BN * C::ELEM / ROW_BYTES;  // 128-byte chunks of N per tile
+            constexpr int BOX_BYTES = BK * ROW_BYTES;
+#pragma unroll
+            for (int j = 0; j < NBOX; j++)
+              tma_load_2d(dst + C::NA * A_TILE_BYTES + j * BOX_BYTES, &tmB0, bar, n0 + j * (ROW_BYTES / C::ELEM), k0);
+          } else {
+            tma_load_2d(dst + C::NA * A_TILE_BYTES, &tmB0, bar, k0, n0);
+            if (C::NB > 1) tma_load_2d(dst + C::NA * A_TILE_BYTES + B_TILE_BYTES, &tmB1, bar, k0, n0);
+          }
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1u;
@@ -301,12 +313,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
           const uint32_t a0 = tiles + stage * STAGE_BYTES;
           const uint32_t b0 = a0 + C::NA * A_TILE_BYTES;
           const uint64_t da_hi = smem_desc_k_sw128(a0);
-          const uint64_t db_hi = smem_desc_k_sw128(b0);
+          const uint64_t db_hi = BMN ? smem_desc_mn_sw128(b0, BK) : smem_desc_k_sw128(b0);
+          constexpr uint32_t IDESC = C::IDESC | (BMN ? IDESC_B_MN_MAJOR : 0u);
+          // one MMA consumes 32 bytes of K: K-major that is 32 bytes along the row;
+          // MN-major it is (32 / ELEM) K-rows of 128 bytes
+          constexpr uint64_t B_ADV = BMN ? (uint64_t)((32 / C::ELEM) * ROW_BYTES / 16) : 2u;
 #pragma unroll
           for (int ks = 0; ks < KSTEPS; ks++) {
             const uint64_t adv = (uint64_t)(ks * 2);  // 32 bytes, in 16-byte units
             if (C::NPROD == 1) {
-              tc_mma<C::KIND>(d, da_hi + adv, db_hi + adv, C::IDESC, (kb | ks) != 0);
+              tc_mma<C::KIND>(d, da_hi + adv, db_hi + ks * B_ADV, IDESC, (kb | ks) != 0);
             } else {
               const uint64_t da_lo = smem_desc_k_sw128(a0 + A_TILE_BYTES);
               const uint64_t db_lo = smem_desc_k_sw128(b0 + B_TILE_BYTES);
@@ -498,13 +514,36 @@ bool make_kmajor_map(CUtensorMap* m, CUtensorMapDataType dt, int elem, const voi
   return true;
 }
 
+// MN-major operand: a row-major `k_rows` x `n_elems` array, row pitch
+// `pitch_bytes`; box = 128 bytes of N x box_k rows of K.
+bool make_mnmajor_map(CUtensorMap* m, CUtensorMapDataType dt, int elem, const void* base, int64_t k_rows,
+                      int64_t n_elems, int64_t pitch_bytes, int box_k) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) {
+    set_error(EXO_B200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    return false;
+  }
+  cuuint64_t dims[2] = {(cuuint64_t)n_elems, (cuuint64_t)k_rows};
+  cuuint64_t strides[1] = {(cuuint64_t)pitch_bytes};
+  cuuint32_t box[2] = {(cuuint32_t)(ROW_BYTES / elem), (cuuint32_t)box_k};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(m, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error(EXO_B200_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult " + std::to_string((int)r));
+    return false;
+  }
+  return true;
+}
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-template <int MODE>
+template <int MODE, bool BMN = false>
 cudaError_t launch_tc(exo_b200_Context* ctx, const CUtensorMap& a0, const CUtensorMap& a1, const CUtensorMap& b0,
                       const CUtensorMap& b1, int64_t M, int64_t N, int64_t K, const EpiParams& ep) {
   {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<MODE, BMN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          smem_bytes<MODE>());
     if (e != cudaSuccess) return e;
   }
@@ -512,7 +551,7 @@ cudaError_t launch_tc(exo_b200_Context* ctx, const CUtensorMap& a0, const CUtens
   if (tiles_m * tiles_n > INT32_MAX || M > INT32_MAX || N > INT32_MAX || K > INT32_MAX)
     return cudaErrorInvalidValue;
   const int grid = (int)std::min<int64_t>(tiles_m * tiles_n, ctx->sm_count);
-  gemm_tc_kernel<MODE><<<grid, NUM_THREADS, smem_bytes<MODE>(), ctx->stream>>>(
+  gemm_tc_kernel<MODE, BMN><<<grid, NUM_THREADS, smem_bytes<MODE>(), ctx->stream>>>(
       a0, a1, b0, b1, (int)M, (int)N, (int)K, ep, ctx->status_dev, (int)tiles_m, (int)tiles_n);
   return cudaGetLastError();
 }
@@ -543,6 +582,18 @@ cudaError_t launch_matmul_i8_tc(exo_b200_Context* ctx, int64_t N, int64_t M, int
   // Exo's names: A is N x K (rows N), B is K x M, C is N x M.  GEMM view: rows = N, cols = M.
   const int64_t rows = N, cols = M;
   const int64_t Kp = K;  // K % 16 == 0 already
+  static const bool allow_mn = [] {
+    const char* e = getenv("EXOB200_I8_TRANSPOSE");  // =1 forces the transposing pre-pass (A/B timing)
+    return !(e && e[0] == '1');
+  }();
+  if (allow_mn && cols % 16 == 0 && aligned16(B)) {
+    // B's pitch satisfies TMA: read it MN-major in place, no pre-pass, no scratch
+    CUtensorMap ma, mb;
+    if (!make_kmajor_map(&ma, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, A, rows, K, K, BM)) return cudaErrorUnknown;
+    if (!make_mnmajor_map(&mb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, B, K, cols, cols, ROW_BYTES)) return cudaErrorUnknown;
+    EpiParams ep{C, cols, scale, act ? 1 : 0, (cols % 16 == 0 && aligned16(C)) ? 1 : 0};
+    return launch_tc<MODE_I8, true>(ctx, ma, ma, mb, mb, rows, cols, K, ep);
+  }
   if (!ensure_scratch(ctx, 1, (size_t)(cols * Kp))) return cudaErrorMemoryAllocation;
   int8_t* Bt = static_cast<int8_t*>(ctx->scratch[1]);
   {

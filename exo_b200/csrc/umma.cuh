@@ -165,6 +165,23 @@ __device__ __forceinline__ uint64_t smem_desc_k_sw128(uint32_t smem_addr) {
   return d;
 }
 
+// Shared-memory matrix descriptor for an MN-major operand tile (rows of K, each
+// row 128 bytes of consecutive M or N elements) stored by TMA boxes
+// {128 bytes of MN, box_k_rows rows of K} with the 128-byte swizzle.  The
+// canonical atom is 8 K-rows x 128 bytes (1024 bytes, rows 128 bytes apart):
+//   stride byte offset  = 1024: from one group of 8 K-rows to the next
+//   leading byte offset = box_k_rows * 128: from one 128-byte chunk of MN to the next box
+__device__ __forceinline__ uint64_t smem_desc_mn_sw128(uint32_t smem_addr, uint32_t box_k_rows) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
+  d |= (uint64_t)(((box_k_rows * 128u) >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+constexpr uint32_t IDESC_B_MN_MAJOR = 1u << 16;
+
 // Instruction descriptor (kind::f16 / tf32 / i8), dense, no negate, both
 // operands K-major:
 //   bits 4-5 D format (1 = f32, 2 = s32)   bits 7-9 A format   bits 10-12 B format
