@@ -348,22 +348,59 @@ class Workload:
         self.lib.matmul_on_cpu(None, n, n, n, 1.0 / 256, False, self.hA, self.hB, self.hC)
 
     # -- fp32 conv: batch 4, 56x56, 64->64, 3x3, pad 1 (implicit GEMM, exact)
-    def _setup_conv(self):
+    def _setup_conv(self, cv=(4, 56, 56, 64, 64, 3, 1)):
         t = self.torch
         self.dtype = "f32"
         g = t.Generator(device="cuda").manual_seed(8)
-        self.cv = (4, 56, 56, 64, 64, 3, 1)
+        self.cv = cv
         b, h, w, ci, co, k, pad = self.cv
         self.A = t.rand((b, h, w, ci), generator=g, device="cuda") * 2 - 1
         self.B = t.rand((k, k, ci, co), generator=g, device="cuda") * 2 - 1
         self.bias = t.rand((co,), generator=g, device="cuda") * 2 - 1
-        self.C = t.empty((b, h, w, co), device="cuda")
-        self.flops_total = self.flops_local = 2.0 * b * h * w * co * k * k * ci
+        oh, ow = h + 2 * pad - k + 1, w + 2 * pad - k + 1
+        self.C = t.empty((b, oh, ow, co), device="cuda")
+        self.flops_total = self.flops_local = 2.0 * b * oh * ow * co * k * k * ci
         self.bound = "tensor"
 
     def step_conv(self):
         b, h, w, ci, co, k, pad = self.cv
         self.lib.conv_nhwc_exo(None, b, h, w, ci, co, k, pad, True, self.A, self.C, self.B, self.bias)
+
+    # -- the same conv on the tensor cores (TMA implicit im2col, 3xTF32)
+    def _setup_conv_3xtf32(self):
+        self._setup_conv()
+        self.launches_per_step = 3  # input split, weight split, conv kernel
+
+    def step_conv_3xtf32(self):
+        b, h, w, ci, co, k, pad = self.cv
+        self.lib.conv_nhwc_exo_3xtf32(None, b, h, w, ci, co, k, pad, True, self.A, self.C, self.B, self.bias)
+
+    # -- the 1x1 conv: batch 8, 28x28, 256 -> 512 (exact FFMA and 3xTF32)
+    def _setup_conv1x1(self):
+        self._setup_conv(cv=(8, 28, 28, 256, 512, 1, 0))
+
+    step_conv1x1 = step_conv
+
+    def _setup_conv1x1_3xtf32(self):
+        self._setup_conv(cv=(8, 28, 28, 256, 512, 1, 0))
+        self.launches_per_step = 3
+
+    step_conv1x1_3xtf32 = step_conv_3xtf32
+
+    # -- Gemmini int8 conv_3: batch 4, 58 -> 56, 64 -> 64, 3x3 (tensor cores, bit-exact)
+    def _setup_conv_i8(self):
+        t = self.torch
+        self.dtype = "i8"
+        g = t.Generator(device="cuda").manual_seed(9)
+        self.A = t.randint(-128, 128, (4, 58, 58, 64), generator=g, device="cuda", dtype=t.int8)
+        self.B = t.randint(-128, 128, (3, 3, 64, 64), generator=g, device="cuda", dtype=t.int8)
+        self.bias = t.randint(-1000, 1000, (1, 64), generator=g, device="cuda", dtype=t.int32)
+        self.C = t.empty((4, 56, 56, 64), dtype=t.int8, device="cuda")
+        self.flops_total = self.flops_local = 2.0 * 4 * 56 * 56 * 64 * 9 * 64
+        self.bound = "tensor"
+
+    def step_conv_i8(self):
+        self.lib.conv_3(None, self.C, self.bias, self.A, self.B, True, 1.0 / 256)
 
     def step(self):
         getattr(self, f"step_{self.name}")()
@@ -497,19 +534,20 @@ def run_sweep(lib, torch, peaks, skip):
     out = {}
     sm_count = torch.cuda.get_device_properties(0).multi_processor_count
     simt_peak = sm_count * 128 * 2 * 1.965e9 / 1e12  # fp32 FFMA at max SM clock
-    for name in ("sgemm_ffma", "sgemm_3xtf32", "i8", "conv", "bf16"):
+    for name in ("sgemm_ffma", "sgemm_3xtf32", "i8", "conv", "conv_3xtf32", "conv1x1", "conv1x1_3xtf32", "conv_i8",
+                 "bf16"):
         if name == skip:
             continue
         try:
             wl = Workload(name, lib, torch, 0, 1)
-            ms, _, _ = time_steps(torch, wl.step, 5, 3)
+            ms, _, _ = time_steps(torch, wl.step, 5 if wl.flops_total > 1e11 else 50, 3)
             lib.synchronize()
             tf = wl.flops_total / (ms / 1e3) / 1e12
-            if name in ("sgemm_ffma", "conv"):
+            if name in ("sgemm_ffma", "conv", "conv1x1"):
                 peak, pname = simt_peak, "fp32 SIMT at max SM clock (computed)"
-            elif name == "sgemm_3xtf32":
+            elif name in ("sgemm_3xtf32", "conv_3xtf32", "conv1x1_3xtf32"):
                 peak, pname = peaks["bf16_tflops"] / 2 / 3, "bf16 measured / 2 (tf32) / 3 (three MMAs per product)"
-            elif name == "i8":
+            elif name in ("i8", "conv_i8"):
                 peak, pname = peaks["bf16_tflops"] * 2, "2 x bf16 measured (nominal int8 ratio)"
             else:
                 peak, pname = peaks["bf16_tflops"], "bf16 measured"

@@ -46,7 +46,7 @@ void sgemm_dispatch(const char* fn, void* ctxt, int path, int_fast32_t M, int_fa
 
 // ----------------------------------------------------------------- conv
 void conv_dispatch(const char* fn, void* ctxt, const ConvShape& s, const float* inp, float* output,
-                   const float* weights, const float* bias) {
+                   const float* weights, const float* bias, int path = -1) {
   clear_error();
   if (bad_args(fn, s.batch < 1 || s.in_h < 1 || s.in_w < 1 || s.in_c < 1 || s.out_c < 1 || s.kdim < 1 ||
                        s.pad < 0 || s.out_h < 1 || s.out_w < 1,
@@ -65,8 +65,14 @@ void conv_dispatch(const char* fn, void* ctxt, const ConvShape& s, const float* 
   b.dev = nullptr;
   b.staged = false;
   if (bias && !stage_in(c, 3, bias, sizeof(float) * (size_t)s.out_c, true, &b)) return;
-  cudaError_t e = launch_conv_ffma(c->stream, s, static_cast<const float*>(i.dev), static_cast<float*>(o.dev),
-                                   static_cast<const float*>(w.dev), static_cast<const float*>(b.dev));
+  if (path < 0) path = c->sgemm_path;  // one switch selects exact FFMA or 3xTF32 for every fp32 kernel
+  cudaError_t e;
+  if (path == EXO_B200_SGEMM_3XTF32 && tc_supported_conv_tf32(s, i.dev))
+    e = launch_conv_3xtf32_tc(c, s, static_cast<const float*>(i.dev), static_cast<float*>(o.dev),
+                              static_cast<const float*>(w.dev), static_cast<const float*>(b.dev));
+  else
+    e = launch_conv_ffma(c->stream, s, static_cast<const float*>(i.dev), static_cast<float*>(o.dev),
+                         static_cast<const float*>(w.dev), static_cast<const float*>(b.dev));
   if (!check_cuda(e, fn)) return;
   if (!stage_out(c, o)) return;
   finish(c, i.staged || w.staged || o.staged || b.staged);
@@ -164,9 +170,14 @@ void conv_i8_dispatch(const char* fn, int_fast32_t batch_size, int_fast32_t out_
   if (!stage_in(c, 1, weights, (size_t)kernel_dim * kernel_dim * in_channel * out_channel, true, &w)) return;
   if (!stage_in(c, 2, output, (size_t)batch_size * out_dim * out_dim * out_channel, false, &o)) return;
   if (!stage_in(c, 3, bias, sizeof(int32_t) * (size_t)out_channel, true, &b)) return;
-  cudaError_t e = launch_conv_i8_simt(c->stream, s, sc, act, static_cast<const int8_t*>(i.dev),
-                                      static_cast<int8_t*>(o.dev), static_cast<const int8_t*>(w.dev),
-                                      static_cast<const int32_t*>(b.dev));
+  cudaError_t e;
+  if (tc_supported_conv_i8(s, i.dev, w.dev))
+    e = launch_conv_i8_tc(c, s, sc, act, static_cast<const int8_t*>(i.dev), static_cast<int8_t*>(o.dev),
+                          static_cast<const int8_t*>(w.dev), static_cast<const int32_t*>(b.dev));
+  else
+    e = launch_conv_i8_simt(c->stream, s, sc, act, static_cast<const int8_t*>(i.dev),
+                            static_cast<int8_t*>(o.dev), static_cast<const int8_t*>(w.dev),
+                            static_cast<const int32_t*>(b.dev));
   if (!check_cuda(e, fn)) return;
   if (!stage_out(c, o)) return;
   finish(c, i.staged || w.staged || o.staged || b.staged);
@@ -211,9 +222,9 @@ void conv(void* ctxt, int_fast32_t out_h, int_fast32_t out_w, int_fast32_t out_c
                 output, weights, bias);
 }
 
-void conv_nhwc_exo(void* ctxt, int_fast32_t batch_size, int_fast32_t in_h, int_fast32_t in_w,
-                   int_fast32_t in_channel, int_fast32_t out_channel, int_fast32_t kernel_dim, int_fast32_t pad,
-                   bool relu, const float* inp, float* output, const float* weights, const float* bias) {
+static ConvShape nhwc_conv_shape(int_fast32_t batch_size, int_fast32_t in_h, int_fast32_t in_w,
+                                 int_fast32_t in_channel, int_fast32_t out_channel, int_fast32_t kernel_dim,
+                                 int_fast32_t pad, bool relu) {
   ConvShape s;
   s.batch = (int)batch_size;
   s.in_h = (int)in_h;
@@ -228,7 +239,24 @@ void conv_nhwc_exo(void* ctxt, int_fast32_t batch_size, int_fast32_t in_h, int_f
   s.w_stride_kx = in_channel * out_channel;
   s.w_stride_ky = kernel_dim * in_channel * out_channel;
   s.relu = relu;
-  conv_dispatch("conv_nhwc_exo", ctxt, s, inp, output, weights, bias);
+  return s;
+}
+
+void conv_nhwc_exo(void* ctxt, int_fast32_t batch_size, int_fast32_t in_h, int_fast32_t in_w,
+                   int_fast32_t in_channel, int_fast32_t out_channel, int_fast32_t kernel_dim, int_fast32_t pad,
+                   bool relu, const float* inp, float* output, const float* weights, const float* bias) {
+  conv_dispatch("conv_nhwc_exo", ctxt,
+                nhwc_conv_shape(batch_size, in_h, in_w, in_channel, out_channel, kernel_dim, pad, relu), inp, output,
+                weights, bias);
+}
+
+void conv_nhwc_exo_3xtf32(void* ctxt, int_fast32_t batch_size, int_fast32_t in_h, int_fast32_t in_w,
+                          int_fast32_t in_channel, int_fast32_t out_channel, int_fast32_t kernel_dim,
+                          int_fast32_t pad, bool relu, const float* inp, float* output, const float* weights,
+                          const float* bias) {
+  conv_dispatch("conv_nhwc_exo_3xtf32", ctxt,
+                nhwc_conv_shape(batch_size, in_h, in_w, in_channel, out_channel, kernel_dim, pad, relu), inp, output,
+                weights, bias, EXO_B200_SGEMM_3XTF32);
 }
 
 void matmul_on_cpu(void* ctxt, int_fast32_t N, int_fast32_t M, int_fast32_t K, const float* scale, bool act,

@@ -42,4 +42,12 @@ bool tc_supported_tf32(int64_t M, int64_t N, int64_t K, const void* A, const voi
 cudaError_t launch_sgemm_3xtf32_tc(exo_b200_Context* ctx, int64_t M, int64_t N, int64_t K,
                                    const float* A, const float* B, float* C);
 
+// ---- implicit-GEMM convolution on tensor cores, im2col done by TMA (conv_tc.cu)
+bool tc_supported_conv_i8(const ConvShape& s, const void* inp, const void* weights);
+cudaError_t launch_conv_i8_tc(exo_b200_Context* ctx, const ConvShape& s, float scale, bool act, const int8_t* inp,
+                              int8_t* out, const int8_t* weights, const int32_t* bias);
+bool tc_supported_conv_tf32(const ConvShape& s, const void* inp);
+cudaError_t launch_conv_3xtf32_tc(exo_b200_Context* ctx, const ConvShape& s, const float* inp, float* out,
+                                  const float* weights, const float* bias);
+
 }  // namespace exob200

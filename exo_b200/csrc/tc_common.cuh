@@ -1,0 +1,87 @@
+// Pieces shared by the tensor-core kernels (tc_gemm.cu, conv_tc.cu): tile
+// constants, the bounded-wait bookkeeping, the TF32 split, and the host-side
+// tensor-map encoder.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <mutex>
+#include <string>
+
+#include "common.cuh"
+#include "umma.cuh"
+
+namespace exob200 {
+namespace tc {
+
+constexpr int BM = 128;                   // rows per CTA tile = tensor-memory lanes
+constexpr int ROW_BYTES = 128;            // one swizzle row: the K extent of a stage
+constexpr int KSTEPS = ROW_BYTES / 32;    // every tcgen05.mma consumes 32 bytes of K
+constexpr int NUM_THREADS = 192;          // warp 0 TMA, warp 1 MMA, warps 2-5 epilogue
+constexpr int A_TILE_BYTES = BM * ROW_BYTES;  // 16 KiB
+constexpr uint64_t WAIT_LIMIT_NS = 1000ull * 1000ull * 1000ull;  // 1 s per wait
+constexpr uint64_t DRAIN_LIMIT_NS = 1000ull * 1000ull;           // 1 ms per stage on the error path
+
+__device__ __forceinline__ void report_timeout(DeviceStatus* st, volatile int* abort, int where) {
+  *abort = 1;
+  if (st != nullptr && st->code == 0) {
+    st->where = where;
+    st->block = (int)blockIdx.x;
+    st->code = EXO_B200_ERR_TIMEOUT;
+  }
+}
+
+// TF32 split of one fp32 value: hi = rna_tf32(x), lo = rna_tf32(x - hi).
+// x - hi is exact in fp32.  Non-finite x keeps lo = 0 so inf stays inf.
+__device__ __forceinline__ void split_tf32(float x, float& hi, float& lo) {
+  uint32_t h;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(x));
+  hi = __uint_as_float(h);
+  const float d = x - hi;
+  uint32_t l;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(l) : "f"(d));
+  lo = (fabsf(hi) <= 3.402823466e38f) ? __uint_as_float(l) : 0.f;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+// Tiled tensor map, 128-byte swizzle, zero fill outside the tensor.  dims/box are
+// innermost first; strides (bytes) are for dimensions 1..rank-1.
+inline bool make_tiled_map(CUtensorMap* m, CUtensorMapDataType dt, int rank, const void* base,
+                           const cuuint64_t* dims, const cuuint64_t* strides, const cuuint32_t* box) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) {
+    set_error(EXO_B200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    return false;
+  }
+  cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  CUresult r = fn(m, dt, (cuuint32_t)rank, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error(EXO_B200_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult " + std::to_string((int)r));
+    return false;
+  }
+  return true;
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace tc
+}  // namespace exob200

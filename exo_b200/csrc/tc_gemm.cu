@@ -37,6 +37,7 @@
 
 #include "i8_epilogue.cuh"
 #include "kernels.cuh"
+#include "tc_common.cuh"
 #include "umma.cuh"
 
 namespace exob200 {
@@ -46,14 +47,9 @@ using namespace umma;
 
 enum Mode { MODE_BF16 = 0, MODE_I8 = 1, MODE_TF32X3 = 2 };
 
-constexpr int BM = 128;
+using namespace tc;
 constexpr int BN = 256;
-constexpr int ROW_BYTES = 128;            // one swizzle row: the K extent of a stage
-constexpr int KSTEPS = ROW_BYTES / 32;    // every tcgen05.mma consumes 32 bytes of K
 constexpr int TMEM_COLS = 512;            // two BN-column accumulators
-constexpr int NUM_THREADS = 192;
-constexpr uint64_t WAIT_LIMIT_NS = 1000ull * 1000ull * 1000ull;  // 1 s per wait
-constexpr uint64_t DRAIN_LIMIT_NS = 1000ull * 1000ull;           // 1 ms per stage on the error path
 
 template <int MODE>
 struct Cfg;
@@ -73,7 +69,6 @@ struct Cfg<MODE_TF32X3> {
   static constexpr uint32_t IDESC = make_idesc(1, 2, 2, BM, BN);
 };
 
-constexpr int A_TILE_BYTES = BM * ROW_BYTES;  // 16 KiB
 constexpr int B_TILE_BYTES = BN * ROW_BYTES;  // 32 KiB
 
 template <int MODE>
@@ -92,15 +87,6 @@ struct EpiParams {
   int act;       // I8
   int vec_ok;    // 16-byte stores allowed
 };
-
-__device__ __forceinline__ void report_timeout(DeviceStatus* st, volatile int* abort, int where) {
-  *abort = 1;
-  if (st != nullptr && st->code == 0) {
-    st->where = where;
-    st->block = (int)blockIdx.x;
-    st->code = EXO_B200_ERR_TIMEOUT;
-  }
-}
 
 // ------------------------------------------------------------- epilogues
 template <int MODE>
@@ -386,18 +372,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
 }
 
 // ----------------------------------------------------- pre-pass kernels
-// TF32 split of one fp32 value: hi = rna_tf32(x), lo = rna_tf32(x - hi).
-// x - hi is exact in fp32.  Non-finite x keeps lo = 0 so inf stays inf.
-__device__ __forceinline__ void split_tf32(float x, float& hi, float& lo) {
-  uint32_t h;
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(x));
-  hi = __uint_as_float(h);
-  const float d = x - hi;
-  uint32_t l;
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(l) : "f"(d));
-  lo = (fabsf(hi) <= 3.402823466e38f) ? __uint_as_float(l) : 0.f;
-}
-
 // A (M x K row-major) -> hi, lo (M x Kp), zero in the pad columns.
 __global__ void split_rows_kernel(const float* __restrict__ A, int64_t M, int K, int Kp, float* __restrict__ hi,
                                   float* __restrict__ lo) {
@@ -474,70 +448,25 @@ __global__ void __launch_bounds__(256) transpose_i8_kernel(const int8_t* __restr
 }
 
 // ------------------------------------------------------------ host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(p);
-  });
-  return fn;
-}
-
 // K-major operand: `rows` rows of `k_elems` elements, row pitch `pitch_bytes`;
-// box = 128 bytes of K x box_rows rows, 128-byte swizzle, zero fill outside.
+// box = 128 bytes of K x box_rows rows.
 bool make_kmajor_map(CUtensorMap* m, CUtensorMapDataType dt, int elem, const void* base, int64_t rows,
                      int64_t k_elems, int64_t pitch_bytes, int box_rows) {
-  EncodeTiledFn fn = encode_fn();
-  if (!fn) {
-    set_error(EXO_B200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
-    return false;
-  }
   cuuint64_t dims[2] = {(cuuint64_t)k_elems, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)pitch_bytes};
   cuuint32_t box[2] = {(cuuint32_t)(ROW_BYTES / elem), (cuuint32_t)box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(m, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) {
-    set_error(EXO_B200_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult " + std::to_string((int)r));
-    return false;
-  }
-  return true;
+  return make_tiled_map(m, dt, 2, base, dims, strides, box);
 }
 
 // MN-major operand: a row-major `k_rows` x `n_elems` array, row pitch
 // `pitch_bytes`; box = 128 bytes of N x box_k rows of K.
 bool make_mnmajor_map(CUtensorMap* m, CUtensorMapDataType dt, int elem, const void* base, int64_t k_rows,
                       int64_t n_elems, int64_t pitch_bytes, int box_k) {
-  EncodeTiledFn fn = encode_fn();
-  if (!fn) {
-    set_error(EXO_B200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
-    return false;
-  }
   cuuint64_t dims[2] = {(cuuint64_t)n_elems, (cuuint64_t)k_rows};
   cuuint64_t strides[1] = {(cuuint64_t)pitch_bytes};
   cuuint32_t box[2] = {(cuuint32_t)(ROW_BYTES / elem), (cuuint32_t)box_k};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(m, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) {
-    set_error(EXO_B200_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult " + std::to_string((int)r));
-    return false;
-  }
-  return true;
+  return make_tiled_map(m, dt, 2, base, dims, strides, box);
 }
-
-inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 template <int MODE, bool BMN = false>
 cudaError_t launch_tc(exo_b200_Context* ctx, const CUtensorMap& a0, const CUtensorMap& a1, const CUtensorMap& b0,

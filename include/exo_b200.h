@@ -136,6 +136,13 @@ void gemm_bf16_exo( void *ctxt, int_fast32_t M, int_fast32_t N, int_fast32_t K, 
  * Exact fp32: bias-initialised FMA chain in ky -> kx -> ci order. */
 void conv_nhwc_exo( void *ctxt, int_fast32_t batch_size, int_fast32_t in_h, int_fast32_t in_w, int_fast32_t in_channel, int_fast32_t out_channel, int_fast32_t kernel_dim, int_fast32_t pad, bool relu, const float* inp, float* output, const float* weights, const float* bias );
 
+/* Same contract as conv_nhwc_exo on the tensor cores: implicit GEMM whose im2col
+ * addressing is done by TMA (the decomposition of tests/test_im2col.py:41-62),
+ * operands split into TF32 hi + lo terms, bias and ReLU in the epilogue.  Not
+ * bit-identical; error like sgemm_exo_3xtf32.  conv / conv_specialized /
+ * conv_nhwc_exo take this path too when the context's SGEMM path is 3xTF32. */
+void conv_nhwc_exo_3xtf32( void *ctxt, int_fast32_t batch_size, int_fast32_t in_h, int_fast32_t in_w, int_fast32_t in_channel, int_fast32_t out_channel, int_fast32_t kernel_dim, int_fast32_t pad, bool relu, const float* inp, float* output, const float* weights, const float* bias );
+
 /* matmul_on_cpu_static: the int8 matmul of matmul_on_cpu for callers that cannot
  * allocate device memory where they need the result -- inside a stream capture,
  * under an arena that owns all device memory, or in a loop that must not meet an

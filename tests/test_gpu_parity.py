@@ -321,6 +321,56 @@ def test_i8_conv_reference_shapes(lib, golden, name):
     assert cases.digest(out) == str(golden[f"i8conv_seeded_{name}_sha256"])
 
 
+@pytest.mark.parametrize("cfg", [
+    # batch, in_dim, ci, co, k     (tensor path: ci % 16 == 0 and co % 16 == 0; else SIMT)
+    (2, 19, 32, 48, 3), (1, 9, 16, 16, 5), (3, 12, 144, 272, 3), (2, 10, 64, 64, 1), (1, 130, 16, 32, 3),
+    (2, 11, 24, 40, 3),
+])
+def test_i8_conv_generic_shapes(lib, port, torch, cfg):
+    b, ind, ci, co, k = cfg
+    od = ind - k + 1
+    inp = inputs.int8(900 + ind, (b, ind, ind, ci), -20, 20)
+    w = inputs.int8(901 + co, (k, k, ci, co), -20, 20)
+    bias = inputs.int32(902, (1, co), -3000, 3000)
+    out = torch.empty((b, od, od, co), dtype=torch.int8, device="cuda")
+    for scale, act in [(1.0 / 64, True), (0.013, False)]:
+        lib.conv_on_cpu_stride_1(None, b, od, co, k, ci, ind, out, dev(torch, bias), dev(torch, inp), dev(torch, w),
+                                 act, float(scale))
+        torch.cuda.synchronize()
+        assert np.array_equal(out.cpu().numpy(), port.conv_i8(inp, w, bias, scale, act))
+
+
+# ------------------------------------------------------- conv on tensor cores
+@pytest.mark.parametrize("cfg", [
+    (4, 56, 56, 64, 64, 3, 1, True),     # the 3x3 workload
+    (8, 28, 28, 256, 512, 1, 0, True),   # the 1x1 workload
+    (2, 9, 11, 8, 16, 3, 1, True),
+    (1, 20, 150, 12, 36, 3, 2, False),   # rows wider than a tile, channels not a multiple of 32
+    (3, 6, 6, 4, 130, 5, 2, True),
+])
+def test_conv_3xtf32_within_tolerance(lib, port, torch, cfg):
+    """Same bound as the 3xTF32 SGEMM with K = kdim^2 * Ci and S = |bias| + sum |x||w|
+    (ReLU is 1-Lipschitz, so the bound carries through it)."""
+    b, h, w, ci, co, k, pad, relu = cfg
+    inp = inputs.uniform_f32(111, (b, h, w, ci))
+    wts = inputs.uniform_f32(112, (k, k, ci, co))
+    bias = inputs.uniform_f32(113, (co,))
+    oh, ow = h + 2 * pad - k + 1, w + 2 * pad - k + 1
+    out = torch.empty((b, oh, ow, co), dtype=torch.float32, device="cuda")
+    lib.conv_nhwc_exo_3xtf32(None, b, h, w, ci, co, k, pad, relu, dev(torch, inp), out, dev(torch, wts),
+                             dev(torch, bias))
+    torch.cuda.synchronize()
+    port.set_threads(os.cpu_count() or 1)
+    try:
+        want = port.conv_nhwc(inp, wts, bias, pad, relu)
+        S = port.conv_nhwc(np.abs(inp), np.abs(wts), np.abs(bias), pad, False)
+    finally:
+        port.set_threads(1)
+    err = np.abs(out.cpu().numpy().astype(np.float64) - want.astype(np.float64))
+    bound = (tf32x3_bound(k * k * ci) + 2e-7) * S.astype(np.float64)  # + the fp32 chain's own rounding
+    assert (err <= bound).all(), f"max err {err.max():.3e}, worst ratio {(err / bound).max():.3f}"
+
+
 # --------------------------------------------------------------------- bf16
 # Tolerance, stated: |C_gpu - C_ref| <= 2^-7 |C_ref| + 1e-3 * sqrt(K) * 4e-4 where C_ref is
 # the reference fp32 SGEMM chain on the widened inputs rounded once to bf16 (one bf16 ulp
