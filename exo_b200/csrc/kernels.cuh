@@ -42,6 +42,13 @@ bool tc_supported_tf32(int64_t M, int64_t N, int64_t K, const void* A, const voi
 cudaError_t launch_sgemm_3xtf32_tc(exo_b200_Context* ctx, int64_t M, int64_t N, int64_t K,
                                    const float* A, const float* B, float* C);
 
+// ---- CTA-pair (cta_group::2) variants of the bf16 and int8 GEMMs (tc_gemm2.cu)
+bool tc2_wanted(int64_t M, int64_t N);
+cudaError_t launch_gemm_bf16_tc2(exo_b200_Context* ctx, int64_t M, int64_t N, int64_t K, const uint16_t* A,
+                                 const uint16_t* B, uint16_t* C);
+cudaError_t launch_matmul_i8_tc2(exo_b200_Context* ctx, int64_t rows, int64_t cols, int64_t K, float scale, bool act,
+                                 const int8_t* A, const int8_t* B, int8_t* C);
+
 // ---- implicit-GEMM convolution on tensor cores, im2col done by TMA (conv_tc.cu)
 bool tc_supported_conv_i8(const ConvShape& s, const void* inp, const void* weights);
 cudaError_t launch_conv_i8_tc(exo_b200_Context* ctx, const ConvShape& s, float scale, bool act, const int8_t* inp,

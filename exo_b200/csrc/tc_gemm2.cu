@@ -1,0 +1,458 @@
+// Tensor-core GEMM with CTA pairs (tcgen05 cta_group::2).
+//
+// Same pipeline as tc_gemm.cu -- TMA -> mbarrier ring -> tcgen05.mma -> two
+// accumulators in tensor memory -> epilogue warps -- but two CTAs on neighbouring
+// SMs form a cluster and share one 256 x 256 output tile: CTA r of the pair loads
+// A rows [128 r, 128 r + 128) and B rows (columns of the product) [128 r, 128 r +
+// 128) of the tile, one thread of the even CTA issues a single 256 x 256 x (32
+// bytes of K) MMA that reads both CTAs' shared memory, and each CTA ends up with
+// its 128 x 256 half of the accumulator in its own tensor memory.  Per SM that
+// halves the B traffic into and out of shared memory (128 instead of 192 bytes
+// per tensor clock), which is what limits the single-CTA kernel, and leaves room
+// for a six-stage ring.
+//
+// Synchronisation inside the pair:
+//   full[s]    lives in the even CTA; armed by its producer for the bytes of BOTH
+//              CTAs; each CTA's TMA loads complete on it (cp.async.bulk.tensor
+//              with .cta_group::2, no multicast)
+//   empty[s], tfull[b]   one in each CTA, signalled together by the issuing
+//              thread's tcgen05.commit (multicast arrive to the pair)
+//   tempty[b]  lives in the even CTA; the eight epilogue warps of the pair arrive
+//              on it (the odd CTA's through a cluster-scope remote arrive)
+// Every wait is bounded as in tc_gemm.cu; a CTA that gives up also raises the
+// abort flag of its partner.  The pair leaves together (cluster barrier) so
+// neither CTA's shared memory disappears under the other.
+#include <cuda.h>
+#include <cuda_bf16.h>
+
+#include <algorithm>
+#include <cstdlib>
+
+#include "i8_epilogue.cuh"
+#include "kernels.cuh"
+#include "tc_common.cuh"
+#include "umma.cuh"
+
+namespace exob200 {
+namespace {
+
+using namespace tc;
+using namespace umma;
+
+enum Mode2 { M2_BF16 = 0, M2_I8 = 1 };
+
+template <int MODE>
+struct Cfg2;
+template <>
+struct Cfg2<M2_BF16> {
+  static constexpr int ELEM = 2, KIND = KIND_F16;
+  static constexpr bool BMN = false;
+  static constexpr uint32_t D_FMT = 1, AB_FMT = 1;
+};
+template <>
+struct Cfg2<M2_I8> {
+  static constexpr int ELEM = 1, KIND = KIND_I8;
+  static constexpr bool BMN = true;
+  static constexpr uint32_t D_FMT = 2, AB_FMT = 1;
+};
+
+constexpr int BN2 = 256;                          // columns of the pair's tile
+constexpr int BHALF = BN2 / 2;                    // B rows each CTA loads
+constexpr int STAGE2_BYTES = A_TILE_BYTES + BHALF * ROW_BYTES;  // 32 KiB per CTA
+constexpr int STAGES2 = 6;
+constexpr int SMEM2_BYTES = STAGES2 * STAGE2_BYTES + 1024 + 256;
+constexpr uint32_t TMEM2_COLS = 512;
+
+// ---- cluster / pair primitives
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of `local_addr` in CTA `rank` of this cluster
+__device__ __forceinline__ uint32_t mapa(uint32_t local_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void st_cluster_u32(uint32_t cluster_addr, uint32_t v) {
+  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
+// TMA load whose completion is signalled on a barrier of the even CTA of the pair
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* m, uint32_t bar_cluster, int x,
+                                                 int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc2(uint32_t smem_result, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_result), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish2() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc2(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// arrive on the barrier at this shared-memory offset in both CTAs of the pair
+// once all MMAs issued so far by this thread have completed
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
+  const uint16_t mask = 3;
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+      "h"(mask)
+      : "memory");
+}
+template <int KIND>
+__device__ __forceinline__ void tc_mma_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                            uint32_t accumulate) {
+  if (KIND == KIND_F16) {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(d_tmem),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n}\n" ::"r"(d_tmem),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }
+}
+
+struct Epi2 {
+  void* C;
+  int64_t ldc;
+  float scale;
+  int act;
+  int vec_ok;
+};
+
+template <int MODE>
+__device__ __forceinline__ void store_chunk2(const Epi2& ep, const uint32_t (&r)[32], int row, int col, int M,
+                                             int N) {
+  if (row >= M || col >= N) return;
+  if (MODE == M2_BF16) {
+    __nv_bfloat16* p = static_cast<__nv_bfloat16*>(ep.C) + (int64_t)row * ep.ldc + col;
+    if (ep.vec_ok) {
+#pragma unroll
+      for (int v = 0; v < 4; v++) {
+        if (col + v * 8 + 8 > N) break;
+        uint32_t w[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+          const __nv_bfloat162 h =
+              __floats2bfloat162_rn(__uint_as_float(r[v * 8 + 2 * j]), __uint_as_float(r[v * 8 + 2 * j + 1]));
+          w[j] = *reinterpret_cast<const uint32_t*>(&h);
+        }
+        *reinterpret_cast<uint4*>(p + v * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; j++)
+        if (col + j < N) p[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
+    }
+  } else {
+    int8_t* p = static_cast<int8_t*>(ep.C) + (int64_t)row * ep.ldc + col;
+    if (ep.vec_ok) {
+#pragma unroll
+      for (int v = 0; v < 2; v++) {
+        if (col + v * 16 + 16 > N) break;
+        uint32_t w[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+          uint32_t x = 0;
+#pragma unroll
+          for (int b = 0; b < 4; b++)
+            x |= (uint32_t)(uint8_t)i8_epilogue((int32_t)r[v * 16 + j * 4 + b], ep.scale, ep.act != 0) << (8 * b);
+          w[j] = x;
+        }
+        *reinterpret_cast<uint4*>(p + v * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; j++)
+        if (col + j < N) p[j] = i8_epilogue((int32_t)r[j], ep.scale, ep.act != 0);
+    }
+  }
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, int M, int N, int K,
+                Epi2 ep, DeviceStatus* status, int tiles_m, int tiles_n) {
+  using C = Cfg2<MODE>;
+  constexpr int BK = ROW_BYTES / C::ELEM;
+  constexpr uint32_t IDESC =
+      make_idesc(C::D_FMT, C::AB_FMT, C::AB_FMT, 2 * BM, BN2) | (C::BMN ? IDESC_B_MN_MAJOR : 0u);
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t tiles = (raw + 1023u) & ~1023u;
+  uint8_t* ctrl = smem_raw + (tiles - raw) + STAGES2 * STAGE2_BYTES;
+  const uint32_t bars = tiles + STAGES2 * STAGE2_BYTES;
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (STAGES2 + s); };
+  auto tfull_bar = [&](int b) { return bars + 8u * (2 * STAGES2 + b); };
+  auto tempty_bar = [&](int b) { return bars + 8u * (2 * STAGES2 + 2 + b); };
+  const uint32_t slot_addr = bars + 8u * (2 * STAGES2 + 4);
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(ctrl + 8 * (2 * STAGES2 + 4));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(ctrl + 8 * (2 * STAGES2 + 4) + 4);
+  const uint32_t abort_addr = slot_addr + 4;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();  // 0 = even CTA: owns full[] / tempty[] and issues the MMAs
+  const int pair = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES2; s++) {
+      mbar_init(full_bar(s), 1);   // the even CTA's producer; bytes of both CTAs ride on the tx count
+      mbar_init(empty_bar(s), 1);  // one multicast commit
+    }
+    for (int b = 0; b < 2; b++) {
+      mbar_init(tfull_bar(b), 1);
+      mbar_init(tempty_bar(b), 8);  // four epilogue warps in each CTA of the pair
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    fence_proxy_async();
+    prefetch_tensormap(&tmA);
+    prefetch_tensormap(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc2(smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM2_COLS);
+    tmem_relinquish2();
+  }
+  tc_fence_before();
+  cluster_sync_all();  // barriers of both CTAs initialised before anyone signals them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int num_tiles = tiles_m * tiles_n;  // 256 x 256 tiles
+  const int num_kb = (K + BK - 1) / BK;
+  constexpr int GM = 8;
+  auto tile_coord = [&](int t, int& tm, int& tn) {
+    const int per_group = GM * tiles_n;
+    const int group = t / per_group;
+    const int first_m = group * GM;
+    const int gm = min(GM, tiles_m - first_m);
+    const int in_group = t - group * per_group;
+    tm = first_m + in_group % gm;
+    tn = in_group / gm;
+  };
+  auto give_up = [&](int where) {
+    report_timeout(status, abort_flag, where);
+    st_cluster_u32(mapa(abort_addr, rank ^ 1u), 1u);  // take the partner down too
+  };
+
+  if (warp == 0) {
+    // ------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = pair; t < num_tiles && ok; t += num_pairs) {
+        int tm, tn;
+        tile_coord(t, tm, tn);
+        const int m0 = tm * 2 * BM + (int)rank * BM;      // this CTA's A rows
+        const int n0 = tn * BN2 + (int)rank * BHALF;       // this CTA's half of the tile's columns
+        for (int kb = 0; kb < num_kb; kb++) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, WAIT_LIMIT_NS)) {
+            give_up(21);
+            ok = false;
+            break;
+          }
+          const uint32_t bar0 = mapa(full_bar(stage), 0);  // the even CTA's barrier
+          const uint32_t dst = tiles + stage * STAGE2_BYTES;
+          if (rank == 0) mbar_arrive_expect_tx(full_bar(stage), 2 * STAGE2_BYTES);
+          const int k0 = kb * BK;
+          tma_load_2d_pair(dst, &tmA, bar0, k0, m0);
+          if (C::BMN)
+            tma_load_2d_pair(dst + A_TILE_BYTES, &tmB, bar0, n0, k0);  // {128 bytes of N, BK rows of K}
+          else
+            tma_load_2d_pair(dst + A_TILE_BYTES, &tmB, bar0, k0, n0);
+          if (++stage == STAGES2) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      if (!ok || *abort_flag) {
+        // error path: give copies in flight time to land (they complete on the even
+        // CTA's barrier, which this CTA may not be able to poll)
+        const uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 200000ull) {
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------------------------ MMA issuer (even CTA only)
+    if (lane == 0 && rank == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int t = pair; t < num_tiles && ok; t += num_pairs) {
+        if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, WAIT_LIMIT_NS)) {
+          give_up(22);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d = tmem_base + (uint32_t)(acc * BN2);
+        for (int kb = 0; kb < num_kb; kb++) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag, WAIT_LIMIT_NS)) {
+            give_up(23);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a0 = tiles + stage * STAGE2_BYTES;
+          const uint32_t b0 = a0 + A_TILE_BYTES;
+          const uint64_t da = smem_desc_k_sw128(a0);
+          const uint64_t db = C::BMN ? smem_desc_mn_sw128(b0, BK) : smem_desc_k_sw128(b0);
+          constexpr uint64_t B_ADV = C::BMN ? (uint64_t)((32 / C::ELEM) * ROW_BYTES / 16) : 2u;
+#pragma unroll
+          for (int ks = 0; ks < KSTEPS; ks++)
+            tc_mma_pair<C::KIND>(d, da + (uint64_t)(ks * 2), db + ks * B_ADV, IDESC, (kb | ks) != 0);
+          tc_commit_pair(empty_bar(stage));
+          if (++stage == STAGES2) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        tc_commit_pair(tfull_bar(acc));
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------ epilogue warps 2..5 (both CTAs)
+    const int q = warp & 3;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int t = pair; t < num_tiles; t += num_pairs) {
+      int tm, tn;
+      tile_coord(t, tm, tn);
+      const int m0 = tm * 2 * BM + (int)rank * BM, n0 = tn * BN2;
+      if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, WAIT_LIMIT_NS)) {
+        if (lane == 0) give_up(24);
+        break;
+      }
+      tc_fence_after();
+      const int row = m0 + q * 32 + lane;
+#pragma unroll 1
+      for (int ch = 0; ch < BN2 / 32; ch++) {
+        const int col = n0 + ch * 32;
+        if (col >= N) break;
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN2 + ch * 32), r);
+        tmem_ld_wait();
+        store_chunk2<MODE>(ep, r, row, col, M, N);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(mapa(tempty_bar(acc), 0));
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+  }
+
+  tc_fence_before();
+  cluster_sync_all();  // the pair leaves together
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc2(tmem_base, TMEM2_COLS);
+  }
+}
+
+template <int MODE>
+cudaError_t launch_tc2(exo_b200_Context* ctx, const CUtensorMap& ma, const CUtensorMap& mb, int64_t M, int64_t N,
+                       int64_t K, const Epi2& ep) {
+  cudaError_t e =
+      cudaFuncSetAttribute(gemm_tc2_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM2_BYTES);
+  if (e != cudaSuccess) return e;
+  const int64_t tiles_m = (M + 2 * BM - 1) / (2 * BM), tiles_n = (N + BN2 - 1) / BN2;
+  if (tiles_m * tiles_n > INT32_MAX || M > INT32_MAX || N > INT32_MAX || K > INT32_MAX) return cudaErrorInvalidValue;
+  // launched as clusters of two CTAs; size the grid to the number of pairs that
+  // can be resident at once (a pair needs two SMs of the same GPC)
+  cudaLaunchConfig_t cfg = {};
+  cfg.blockDim = dim3(NUM_THREADS);
+  cfg.dynamicSmemBytes = SMEM2_BYTES;
+  cfg.stream = ctx->stream;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = 2;
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  static int max_clusters = 0;
+  if (max_clusters == 0) {
+    cfg.gridDim = dim3(2 * ctx->sm_count);
+    int n = 0;
+    e = cudaOccupancyMaxActiveClusters(&n, gemm_tc2_kernel<MODE>, &cfg);
+    if (e != cudaSuccess) return e;
+    max_clusters = std::max(1, n);
+  }
+  const int pairs = (int)std::min<int64_t>(tiles_m * tiles_n, max_clusters);
+  cfg.gridDim = dim3(2 * pairs);
+  return cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<MODE>, ma, mb, (int)M, (int)N, (int)K, ep, ctx->status_dev,
+                            (int)tiles_m, (int)tiles_n);
+}
+
+}  // namespace
+
+// The pair kernel keeps the tensor pipe busier (96 % against 81 % active in ncu
+// captures of the bf16 GEMM) and is used once there are enough 256 x 256 tiles
+// to give every pair several; smaller problems quantise better on the 128 x 256
+// tiles of the single-CTA kernel.  EXOB200_TC2=0 switches it off, =1 forces it.
+bool tc2_wanted(int64_t M, int64_t N) {
+  static const int mode = [] {
+    const char* e = getenv("EXOB200_TC2");
+    return e ? atoi(e) : -1;
+  }();
+  if (mode == 0) return false;
+  if (mode == 1) return true;
+  const int64_t tiles = ((M + 255) / 256) * ((N + 255) / 256);
+  return tiles >= 4 * 74;
+}
+
+cudaError_t launch_gemm_bf16_tc2(exo_b200_Context* ctx, int64_t M, int64_t N, int64_t K, const uint16_t* A,
+                                 const uint16_t* B, uint16_t* C) {
+  CUtensorMap ma, mb;
+  cuuint64_t da[2] = {(cuuint64_t)K, (cuuint64_t)M}, db[2] = {(cuuint64_t)K, (cuuint64_t)N};
+  cuuint64_t st[1] = {(cuuint64_t)K * 2};
+  cuuint32_t boxa[2] = {64, (cuuint32_t)BM}, boxb[2] = {64, (cuuint32_t)BHALF};
+  if (!make_tiled_map(&ma, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, A, da, st, boxa)) return cudaErrorUnknown;
+  if (!make_tiled_map(&mb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, B, db, st, boxb)) return cudaErrorUnknown;
+  Epi2 ep{C, N, 0.f, 0, (N % 8 == 0 && aligned16(C)) ? 1 : 0};
+  return launch_tc2<M2_BF16>(ctx, ma, mb, M, N, K, ep);
+}
+
+cudaError_t launch_matmul_i8_tc2(exo_b200_Context* ctx, int64_t rows, int64_t cols, int64_t K, float scale, bool act,
+                                 const int8_t* A, const int8_t* B, int8_t* C) {
+  CUtensorMap ma, mb;
+  cuuint64_t da[2] = {(cuuint64_t)K, (cuuint64_t)rows}, db[2] = {(cuuint64_t)cols, (cuuint64_t)K};
+  cuuint64_t sa[1] = {(cuuint64_t)K}, sb[1] = {(cuuint64_t)cols};
+  cuuint32_t boxa[2] = {128, (cuuint32_t)BM}, boxb[2] = {128, 128};
+  if (!make_tiled_map(&ma, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, A, da, sa, boxa)) return cudaErrorUnknown;
+  if (!make_tiled_map(&mb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, B, db, sb, boxb)) return cudaErrorUnknown;
+  Epi2 ep{C, cols, scale, act ? 1 : 0, (cols % 16 == 0 && aligned16(C)) ? 1 : 0};
+  return launch_tc2<M2_I8>(ctx, ma, mb, rows, cols, K, ep);
+}
+
+}  // namespace exob200
