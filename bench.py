@@ -522,6 +522,10 @@ def run_ours(args):
         torch.cuda.empty_cache()
         if not args.no_sweep:
             line["sweep"] = run_sweep(lib, torch, peaks, args.workload)
+            try:
+                line["sgemm_shapes"] = run_shapes(lib, torch, peaks)
+            except Exception as e:
+                line["sgemm_shapes"] = {"error": str(e)[:200]}
         if not args.no_cpu:
             line["cpu_baseline"] = run_cpu_single_core()
     print(json.dumps(line), flush=True)
@@ -540,7 +544,7 @@ def run_sweep(lib, torch, peaks, skip):
             continue
         try:
             wl = Workload(name, lib, torch, 0, 1)
-            ms, _, _ = time_steps(torch, wl.step, 5 if wl.flops_total > 1e11 else 50, 3)
+            ms, _, _ = time_steps(torch, wl.step, 5 if wl.flops_total > 1e12 else 50, 3)
             lib.synchronize()
             tf = wl.flops_total / (ms / 1e3) / 1e12
             if name in ("sgemm_ffma", "conv", "conv1x1"):
@@ -557,6 +561,70 @@ def run_sweep(lib, torch, peaks, skip):
             torch.cuda.empty_cache()
         except Exception as e:  # a failing side workload must not lose the headline line
             out[name] = {"error": str(e)[:200]}
+    return out
+
+
+SGEMM_SHAPES = [(256, 256, 256), (512, 512, 512), (1024, 1024, 1024), (2048, 2048, 2048), (4096, 4096, 4096),
+                (1000, 1000, 1000), (17, 4099, 513), (4096, 64, 4096), (1, 8192, 8192)]
+
+
+def run_shapes(lib, torch, peaks):
+    """The SGEMM shape sweep (squares and ragged / skinny shapes) on both fp32
+    paths, device time per launch.  Small shapes finish faster than the host can
+    launch them, so launches are replayed from a CUDA graph: R x [L2 flush (a
+    256 MB write), GEMM], minus a graph of R flushes alone; median of 5 replays."""
+    sm_count = torch.cuda.get_device_properties(0).multi_processor_count
+    simt_peak = sm_count * 128 * 2 * 1.965e9 / 1e12
+    hbm = peaks["hbm_gbs"]
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    R = 10
+
+    def replay_ms(body):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for _ in range(R):
+                body()
+        g.replay()
+        torch.cuda.synchronize()
+        times = []
+        for _ in range(5):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            g.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1))
+        times.sort()
+        return times[len(times) // 2] / R
+
+    flush_ms = replay_ms(lambda: flush.fill_(1))
+    out = []
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    for (M, N, K) in SGEMM_SHAPES:
+        A = torch.rand((M, K), generator=gen, device="cuda") * 2 - 1
+        B = torch.rand((K, N), generator=gen, device="cuda") * 2 - 1
+        C = torch.zeros((M, N), device="cuda")
+        flops = 2.0 * M * N * K
+        nbytes = 4.0 * (M * K + K * N + 2 * M * N)
+        row = {"shape": [M, N, K], "flop_per_byte": flops / nbytes}
+        for path, fn in (("ffma", lib.sgemm_exo_ffma), ("3xtf32", lib.sgemm_exo_3xtf32)):
+            for _ in range(3):
+                fn(None, M, N, K, A, B, C)  # warm-up: also sizes the scratch before capture
+            torch.cuda.synchronize()
+
+            def body():
+                flush.fill_(1)
+                fn(None, M, N, K, A, B, C)
+
+            ms = max(replay_ms(body) - flush_ms, 1e-6)
+            tf, gbs = flops / ms / 1e9, nbytes / ms / 1e6
+            peak_tf = simt_peak if path == "ffma" else peaks["bf16_tflops"] / 6
+            # the roofline that binds: min(compute peak, bandwidth x arithmetic intensity)
+            ceiling = min(peak_tf, hbm * row["flop_per_byte"] / 1e3)
+            row[path] = {"us": ms * 1e3, "tflops": tf, "gbs": gbs, "bound": "hbm" if ceiling < peak_tf else "compute",
+                         "frac_of_roofline": tf / ceiling}
+        out.append(row)
+    lib.synchronize()
     return out
 
 

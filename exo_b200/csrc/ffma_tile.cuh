@@ -30,9 +30,12 @@
 namespace exob200 {
 namespace ffma {
 
-constexpr int BM = 128, BN = 128, BK = 16;
+constexpr int BK = 16;
 constexpr int THREADS = 256;
-constexpr int AS_PITCH = BM + 4;  // floats; keeps 16-byte alignment, spreads the transposing stores
+// Two tile sizes from one engine: H = 2 -> 128 x 128 (8 x 8 per thread), the
+// throughput configuration; H = 1 -> 64 x 64 (4 x 4 per thread) for problems with
+// too few 128 x 128 tiles to occupy the machine (without split-K, which the
+// reference's per-element chain order rules out, parallelism only comes from M x N).
 
 __device__ __forceinline__ float4 ldg4(const float* p) {
   return __ldg(reinterpret_cast<const float4*>(p));
@@ -70,8 +73,11 @@ __device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
   return d;
 }
 
-template <class Policy, bool PACKED>
+template <class Policy, bool PACKED, int H>
 __global__ void __launch_bounds__(THREADS, 2) tile_kernel(const Policy P, int tiles_m, int tiles_n) {
+  constexpr int BM = 64 * H, BN = 64 * H;
+  constexpr int AS_PITCH = BM + 4;  // floats; keeps 16-byte alignment, spreads the transposing stores
+  constexpr int R = 4 * H;          // rows (and columns) per thread
   __shared__ __align__(16) float As[2][BK][AS_PITCH];
   __shared__ __align__(16) float Bs[2][BK][BN];
 
@@ -95,26 +101,30 @@ __global__ void __launch_bounds__(THREADS, 2) tile_kernel(const Policy P, int ti
   const int tx = (warp & 1) * 8 + (lane & 7);    // 0..15
 
   // global -> register staging coordinates
-  // A tile: 128 rows x 16 k.  thread -> rows tid/4 and tid/4 + 64, k quad (tid%4)*4
+  // A tile: BM rows x 16 k.  thread -> rows tid/4 (+ 64), k quad (tid%4)*4
   const int a_row = tid >> 2, a_kq = (tid & 3) * 4;
-  // B tile: 16 k x 128 cols.  thread -> k rows tid/32 and tid/32 + 8, col quad (tid%32)*4
-  const int b_k = tid >> 5, b_c4 = (tid & 31) * 4;
+  // B tile: 16 k x BN cols = 256 H column quads, H per thread
+  constexpr int QPR = 16 * H;  // quads per k row
+  const int b_k = tid / QPR, b_c4 = (tid % QPR) * 4;
+  constexpr int B_KSTEP = THREADS / QPR;  // k rows covered per pass
 
-  const typename Policy::RowCtx rc0 = P.row_ctx(m0 + a_row);
-  const typename Policy::RowCtx rc1 = P.row_ctx(m0 + a_row + 64);
+  typename Policy::RowCtx rc[H];
+#pragma unroll
+  for (int h = 0; h < H; h++) rc[h] = P.row_ctx(m0 + a_row + h * 64);
 
   // A goes through registers (it is transposed on the way into shared memory);
   // B is copied global -> shared asynchronously, 16 bytes (or 4 x 4) per thread.
-  float4 pa[2];
+  float4 pa[H];
   auto load_tile = [&](int k0, int buf) {
-    pa[0] = P.load_a(rc0, m0 + a_row, k0 + a_kq);
-    pa[1] = P.load_a(rc1, m0 + a_row + 64, k0 + a_kq);
-    P.copy_b(&Bs[buf][b_k][b_c4], k0 + b_k, n0 + b_c4);
-    P.copy_b(&Bs[buf][b_k + 8][b_c4], k0 + b_k + 8, n0 + b_c4);
+#pragma unroll
+    for (int h = 0; h < H; h++) pa[h] = P.load_a(rc[h], m0 + a_row + h * 64, k0 + a_kq);
+#pragma unroll
+    for (int h = 0; h < H; h++)
+      P.copy_b(&Bs[buf][b_k + h * B_KSTEP][b_c4], k0 + b_k + h * B_KSTEP, n0 + b_c4);
   };
   auto store_tile = [&](int buf) {
 #pragma unroll
-    for (int h = 0; h < 2; h++) {
+    for (int h = 0; h < H; h++) {
       const int r = a_row + h * 64;
       As[buf][a_kq + 0][r] = pa[h].x;
       As[buf][a_kq + 1][r] = pa[h].y;
@@ -125,13 +135,13 @@ __global__ void __launch_bounds__(THREADS, 2) tile_kernel(const Policy P, int ti
   };
 
   // accumulators start at the chain's first operand
-  float acc[PACKED ? 1 : 8][PACKED ? 1 : 8];
-  uint64_t acc2[PACKED ? 8 : 1][PACKED ? 4 : 1];  // [row][column pair]
+  float acc[PACKED ? 1 : R][PACKED ? 1 : R];
+  uint64_t acc2[PACKED ? R : 1][PACKED ? R / 2 : 1];  // [row][column pair]
 #pragma unroll
-  for (int i = 0; i < 8; i++) {
+  for (int i = 0; i < R; i++) {
     const int row = m0 + (i >> 2) * 64 + ty * 4 + (i & 3);
 #pragma unroll
-    for (int jq = 0; jq < 2; jq++) {
+    for (int jq = 0; jq < H; jq++) {
       const float4 v = P.init(row, n0 + jq * 64 + tx * 4);
       if (PACKED) {
         acc2[i][jq * 2 + 0] = pack2(v.x, v.y);
@@ -156,27 +166,43 @@ __global__ void __launch_bounds__(THREADS, 2) tile_kernel(const Policy P, int ti
 
     const int kmax = min(BK, K - t * BK);
     auto step = [&](int kk) {
-      const float4 a0 = *reinterpret_cast<const float4*>(&As[buf][kk][ty * 4]);
-      const float4 a1 = *reinterpret_cast<const float4*>(&As[buf][kk][64 + ty * 4]);
-      const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-      if (PACKED) {
-        const ulonglong2 b0 = *reinterpret_cast<const ulonglong2*>(&Bs[buf][kk][tx * 4]);
-        const ulonglong2 b1 = *reinterpret_cast<const ulonglong2*>(&Bs[buf][kk][64 + tx * 4]);
-        const uint64_t b[4] = {b0.x, b0.y, b1.x, b1.y};
+      float a[R];
 #pragma unroll
-        for (int i = 0; i < 8; i++) {
+      for (int h = 0; h < H; h++) {
+        const float4 av = *reinterpret_cast<const float4*>(&As[buf][kk][h * 64 + ty * 4]);
+        a[h * 4 + 0] = av.x;
+        a[h * 4 + 1] = av.y;
+        a[h * 4 + 2] = av.z;
+        a[h * 4 + 3] = av.w;
+      }
+      if (PACKED) {
+        uint64_t b[R / 2];
+#pragma unroll
+        for (int h = 0; h < H; h++) {
+          const ulonglong2 bv = *reinterpret_cast<const ulonglong2*>(&Bs[buf][kk][h * 64 + tx * 4]);
+          b[h * 2 + 0] = bv.x;
+          b[h * 2 + 1] = bv.y;
+        }
+#pragma unroll
+        for (int i = 0; i < R; i++) {
           const uint64_t aa = pack2(a[i], a[i]);
 #pragma unroll
-          for (int j = 0; j < 4; j++) acc2[i][j] = fma2(aa, b[j], acc2[i][j]);
+          for (int j = 0; j < R / 2; j++) acc2[i][j] = fma2(aa, b[j], acc2[i][j]);
         }
       } else {
-        const float4 b0 = *reinterpret_cast<const float4*>(&Bs[buf][kk][tx * 4]);
-        const float4 b1 = *reinterpret_cast<const float4*>(&Bs[buf][kk][64 + tx * 4]);
-        const float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+        float b[R];
 #pragma unroll
-        for (int i = 0; i < 8; i++)
+        for (int h = 0; h < H; h++) {
+          const float4 bv = *reinterpret_cast<const float4*>(&Bs[buf][kk][h * 64 + tx * 4]);
+          b[h * 4 + 0] = bv.x;
+          b[h * 4 + 1] = bv.y;
+          b[h * 4 + 2] = bv.z;
+          b[h * 4 + 3] = bv.w;
+        }
 #pragma unroll
-          for (int j = 0; j < 8; j++) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        for (int i = 0; i < R; i++)
+#pragma unroll
+          for (int j = 0; j < R; j++) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
       }
     };
     if (kmax == BK) {
@@ -191,10 +217,10 @@ __global__ void __launch_bounds__(THREADS, 2) tile_kernel(const Policy P, int ti
   }
 
 #pragma unroll
-  for (int i = 0; i < 8; i++) {
+  for (int i = 0; i < R; i++) {
     const int row = m0 + (i >> 2) * 64 + ty * 4 + (i & 3);
 #pragma unroll
-    for (int jq = 0; jq < 2; jq++) {
+    for (int jq = 0; jq < H; jq++) {
       float4 v;
       if (PACKED) {
         unpack2(acc2[i][jq * 2 + 0], v.x, v.y);
@@ -216,16 +242,29 @@ inline bool use_packed() {
   return packed;
 }
 
-template <class Policy>
-cudaError_t launch_tiles(cudaStream_t stream, const Policy& P) {
-  const int64_t tiles_m = (P.M + BM - 1) / BM, tiles_n = (P.N + BN - 1) / BN;
+template <class Policy, int H>
+cudaError_t launch_tiles_h(cudaStream_t stream, const Policy& P) {
+  constexpr int T = 64 * H;
+  const int64_t tiles_m = (P.M + T - 1) / T, tiles_n = (P.N + T - 1) / T;
   if (tiles_m * tiles_n > INT32_MAX) return cudaErrorInvalidValue;
   const unsigned grid = (unsigned)(tiles_m * tiles_n);
   if (use_packed())
-    tile_kernel<Policy, true><<<grid, THREADS, 0, stream>>>(P, (int)tiles_m, (int)tiles_n);
+    tile_kernel<Policy, true, H><<<grid, THREADS, 0, stream>>>(P, (int)tiles_m, (int)tiles_n);
   else
-    tile_kernel<Policy, false><<<grid, THREADS, 0, stream>>>(P, (int)tiles_m, (int)tiles_n);
+    tile_kernel<Policy, false, H><<<grid, THREADS, 0, stream>>>(P, (int)tiles_m, (int)tiles_n);
   return cudaGetLastError();
+}
+
+// 128 x 128 tiles unless they would leave most SMs without work.
+template <class Policy>
+cudaError_t launch_tiles(cudaStream_t stream, const Policy& P) {
+  const int64_t big_tiles = ((int64_t)(P.M + 127) / 128) * ((P.N + 127) / 128);
+  static const int force = [] {
+    const char* e = getenv("EXOB200_FFMA_TILE");  // 64 or 128 forces a tile size (timing experiments)
+    return e ? atoi(e) : 0;
+  }();
+  const bool small = force == 64 || (force != 128 && big_tiles <= 148);
+  return small ? launch_tiles_h<Policy, 1>(stream, P) : launch_tiles_h<Policy, 2>(stream, P);
 }
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }

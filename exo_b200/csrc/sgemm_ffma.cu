@@ -88,96 +88,112 @@ struct SgemmPolicy {
 };
 
 // --------------------------------------------------------------------------
-// Skinny-M kernel (M <= 32): bandwidth bound, B is streamed exactly once.
-// One thread owns `ROWS` x 4 outputs (4 adjacent columns, all rows of a 4- or
-// 8-row slab) and walks K sequentially, so the chain order is unchanged.  A CTA
-// covers 128 columns x up to 32 rows; A's slab rows for the current K chunk sit
-// in shared memory and are read as broadcasts.  Loads of B for KU consecutive
-// k are issued before the dependent FMAs so each thread keeps KU x 16 bytes in
-// flight.
-constexpr int SK_THREADS = 128;  // 32 column quads x 4 row slabs
-constexpr int SK_KC = 64;        // K chunk staged in shared memory for A
-constexpr int SK_KU = 8;         // B loads in flight per thread
+// Skinny-M kernel (M <= 32): bandwidth bound -- B is streamed exactly once.
+//
+// A CTA owns a strip of 64 output columns (and up to 32 rows) for the whole K
+// loop, so every output is still one thread's sequential-k FMA chain.  B (and
+// the matching K chunk of A, stored k-major) flow through a deep ring of
+// shared-memory stages filled by cp.async: with 9 stages of 32 K-rows a CTA
+// keeps 64 KB of B loads in flight, and two CTAs fit per SM, which is what it
+// takes to cover HBM latency when the only parallelism is across N.
+// Thread (cq, rg): column quad cq (16 per strip) x row group rg (8 groups of 4
+// rows): 16 accumulators, per k one 128-bit load of B, one of A, 16 FMAs.
+constexpr int SK_W = 64;        // columns per CTA
+constexpr int SK_KS = 32;       // K rows per stage
+constexpr int SK_STAGES = 9;    // 108 KiB of shared memory: two CTAs per SM
+constexpr int SK_THREADS = 128;
+constexpr int SK_SMEM = SK_STAGES * (SK_KS * SK_W + SK_KS * 32) * (int)sizeof(float);  // 9 x 12 KiB
 
 template <bool VB>
 __global__ void __launch_bounds__(SK_THREADS)
 sgemm_skinny_kernel(int M, int N, int K, const float* __restrict__ A, const float* __restrict__ B,
                     float* __restrict__ C) {
-  __shared__ float As[32][SK_KC + 1];
-  const int tid = threadIdx.x;
-  const int cq = tid & 31;           // column quad within the CTA
-  const int slab = tid >> 5;         // 8-row slab (warp index): rows slab*8 .. +7
-  const int col = blockIdx.x * 128 + cq * 4;
-  const int r0 = blockIdx.y * 32 + slab * 8;
-  const int row_base = blockIdx.y * 32;
-  const bool slab_live = r0 < M;
+  extern __shared__ __align__(16) float sk_smem[];
+  float(*Bs)[SK_KS][SK_W] = reinterpret_cast<float(*)[SK_KS][SK_W]>(sk_smem);
+  float(*As)[SK_KS][32] = reinterpret_cast<float(*)[SK_KS][32]>(sk_smem + SK_STAGES * SK_KS * SK_W);
 
-  float acc[8][4];
+  const int tid = threadIdx.x;
+  const int cq = tid & 15, rg = tid >> 4;
+  const int n0 = blockIdx.x * SK_W, m0 = blockIdx.y * 32;
+  const int col = n0 + cq * 4;
+  const int rows_here = min(32, M - m0);
+  const bool live = rg * 4 < rows_here;
+
+  float acc[4][4];
 #pragma unroll
-  for (int i = 0; i < 8; i++)
+  for (int i = 0; i < 4; i++)
 #pragma unroll
     for (int j = 0; j < 4; j++) {
-      const int r = r0 + i, c = col + j;
+      const int r = m0 + rg * 4 + i, c = col + j;
       acc[i][j] = (r < M && c < N) ? C[(int64_t)r * N + c] : 0.f;
     }
 
-  for (int k0 = 0; k0 < K; k0 += SK_KC) {
-    const int kc = min(SK_KC, K - k0);
-    __syncthreads();
-    for (int e = tid; e < 32 * SK_KC; e += SK_THREADS) {
-      const int r = e / SK_KC, k = e % SK_KC;
-      As[r][k] = (row_base + r < M && k < kc) ? __ldg(A + (int64_t)(row_base + r) * K + k0 + k) : 0.f;
-    }
-    __syncthreads();
-    if (!slab_live) continue;
-    int k = 0;
-    for (; k + SK_KU <= kc; k += SK_KU) {
-      float4 b[SK_KU];
+  const int nstages = (K + SK_KS - 1) / SK_KS;
+  auto issue = [&](int st) {
+    if (st < nstages) {
+      const int buf = st % SK_STAGES, k0 = st * SK_KS;
+      // B: 32 k-rows x 16 quads = 512 quads, 4 per thread
 #pragma unroll
-      for (int u = 0; u < SK_KU; u++) {
-        const float* p = B + (int64_t)(k0 + k + u) * N + col;
+      for (int i = 0; i < 4; i++) {
+        const int e = tid + i * SK_THREADS;
+        const int kk = e >> 4, q = e & 15;
+        const int k = k0 + kk, c = n0 + q * 4;
+        const bool kin = k < K;
+        const float* src = B + (kin ? (int64_t)k * N : 0);
         if (VB) {
-          b[u] = col < N ? ldg4(p) : make_float4(0.f, 0.f, 0.f, 0.f);
+          const bool ok = kin && c < N;
+          ffma::cp_async16(&Bs[buf][kk][q * 4], src + (ok ? c : 0), ok);
         } else {
-          b[u].x = col + 0 < N ? __ldg(p + 0) : 0.f;
-          b[u].y = col + 1 < N ? __ldg(p + 1) : 0.f;
-          b[u].z = col + 2 < N ? __ldg(p + 2) : 0.f;
-          b[u].w = col + 3 < N ? __ldg(p + 3) : 0.f;
+#pragma unroll
+          for (int j = 0; j < 4; j++) {
+            const bool ok = kin && c + j < N;
+            ffma::cp_async4(&Bs[buf][kk][q * 4 + j], src + (ok ? c + j : 0), ok);
+          }
         }
       }
-#pragma unroll
-      for (int u = 0; u < SK_KU; u++)
-#pragma unroll
-        for (int i = 0; i < 8; i++) {
-          const float a = As[slab * 8 + i][k + u];
-          acc[i][0] = fmaf(a, b[u].x, acc[i][0]);
-          acc[i][1] = fmaf(a, b[u].y, acc[i][1]);
-          acc[i][2] = fmaf(a, b[u].z, acc[i][2]);
-          acc[i][3] = fmaf(a, b[u].w, acc[i][3]);
-        }
+      // A chunk, stored k-major: As[kk][row]; consecutive threads walk k within a row
+      for (int e = tid; e < rows_here * SK_KS; e += SK_THREADS) {
+        const int r = e / SK_KS, kk = e - r * SK_KS;
+        const bool ok = k0 + kk < K;
+        ffma::cp_async4(&As[buf][kk][r], A + (int64_t)(m0 + r) * K + (ok ? k0 + kk : 0), ok);
+      }
     }
-    for (; k < kc; k++) {
-      const float* p = B + (int64_t)(k0 + k) * N + col;
-      float4 b;
-      b.x = col + 0 < N ? __ldg(p + 0) : 0.f;
-      b.y = col + 1 < N ? __ldg(p + 1) : 0.f;
-      b.z = col + 2 < N ? __ldg(p + 2) : 0.f;
-      b.w = col + 3 < N ? __ldg(p + 3) : 0.f;
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+
+  for (int st = 0; st < SK_STAGES - 1; st++) issue(st);
+  for (int st = 0; st < nstages; st++) {
+    asm volatile("cp.async.wait_group %0;" ::"n"(SK_STAGES - 2) : "memory");
+    __syncthreads();               // stage st has landed for every thread; stage st-1 is free
+    issue(st + SK_STAGES - 1);     // refill the buffer that stage st-1 used
+    if (live) {
+      const int buf = st % SK_STAGES;
+      const int kmax = min(SK_KS, K - st * SK_KS);
+      auto step = [&](int kk) {
+        const float4 b = *reinterpret_cast<const float4*>(&Bs[buf][kk][cq * 4]);
+        const float4 a = *reinterpret_cast<const float4*>(&As[buf][kk][rg * 4]);
+        const float av[4] = {a.x, a.y, a.z, a.w};
 #pragma unroll
-      for (int i = 0; i < 8; i++) {
-        const float a = As[slab * 8 + i][k];
-        acc[i][0] = fmaf(a, b.x, acc[i][0]);
-        acc[i][1] = fmaf(a, b.y, acc[i][1]);
-        acc[i][2] = fmaf(a, b.z, acc[i][2]);
-        acc[i][3] = fmaf(a, b.w, acc[i][3]);
+        for (int i = 0; i < 4; i++) {
+          acc[i][0] = fmaf(av[i], b.x, acc[i][0]);
+          acc[i][1] = fmaf(av[i], b.y, acc[i][1]);
+          acc[i][2] = fmaf(av[i], b.z, acc[i][2]);
+          acc[i][3] = fmaf(av[i], b.w, acc[i][3]);
+        }
+      };
+      if (kmax == SK_KS) {
+#pragma unroll
+        for (int kk = 0; kk < SK_KS; kk++) step(kk);
+      } else {
+        for (int kk = 0; kk < kmax; kk++) step(kk);  // ragged K tail: no padded steps
       }
     }
   }
 #pragma unroll
-  for (int i = 0; i < 8; i++)
+  for (int i = 0; i < 4; i++)
 #pragma unroll
     for (int j = 0; j < 4; j++) {
-      const int r = r0 + i, c = col + j;
+      const int r = m0 + rg * 4 + i, c = col + j;
       if (r < M && c < N) C[(int64_t)r * N + c] = acc[i][j];
     }
 }
@@ -190,11 +206,17 @@ cudaError_t launch_sgemm_ffma(cudaStream_t stream, int64_t M, int64_t N, int64_t
   const bool va = (K % 4 == 0) && ffma::aligned16(A);
   const bool vb = (N % 4 == 0) && ffma::aligned16(B) && ffma::aligned16(C);
   if (M <= 32) {
-    dim3 grid((unsigned)((N + 127) / 128), (unsigned)((M + 31) / 32));
-    if (vb)
-      sgemm_skinny_kernel<true><<<grid, SK_THREADS, 0, stream>>>((int)M, (int)N, (int)K, A, B, C);
-    else
-      sgemm_skinny_kernel<false><<<grid, SK_THREADS, 0, stream>>>((int)M, (int)N, (int)K, A, B, C);
+    dim3 grid((unsigned)((N + SK_W - 1) / SK_W), (unsigned)((M + 31) / 32));
+    cudaError_t e;
+    if (vb) {
+      e = cudaFuncSetAttribute(sgemm_skinny_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SK_SMEM);
+      if (e != cudaSuccess) return e;
+      sgemm_skinny_kernel<true><<<grid, SK_THREADS, SK_SMEM, stream>>>((int)M, (int)N, (int)K, A, B, C);
+    } else {
+      e = cudaFuncSetAttribute(sgemm_skinny_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SK_SMEM);
+      if (e != cudaSuccess) return e;
+      sgemm_skinny_kernel<false><<<grid, SK_THREADS, SK_SMEM, stream>>>((int)M, (int)N, (int)K, A, B, C);
+    }
     return cudaGetLastError();
   }
 #define EXOB200_LAUNCH(VA_, VB_) \
