@@ -35,10 +35,14 @@ void sgemm_dispatch(const char* fn, void* ctxt, int path, int_fast32_t M, int_fa
   const float* dB = static_cast<const float*>(b.dev);
   float* dC = static_cast<float*>(cc.dev);
   cudaError_t e;
-  if (path == EXO_B200_SGEMM_3XTF32 && tc_supported_tf32(M, N, K, dA, dB, dC))
+  // The tensor path has fixed costs (two split pre-passes, 128 x 256 tiles); for
+  // skinny or small problems the exact FFMA kernels are faster and more accurate,
+  // so "3xTF32" only means "tensor cores where they pay".
+  const bool tensor_pays = M >= 128 && N >= 64 && 2.0 * (double)M * (double)N * (double)K >= 1.0e9;
+  if (path == EXO_B200_SGEMM_3XTF32 && tensor_pays && tc_supported_tf32(M, N, K, dA, dB, dC))
     e = launch_sgemm_3xtf32_tc(c, M, N, K, dA, dB, dC);
   else
-    e = launch_sgemm_ffma(c->stream, M, N, K, dA, dB, dC);
+    e = launch_sgemm_ffma(c, M, N, K, dA, dB, dC);
   if (!check_cuda(e, fn)) return;
   if (!stage_out(c, cc)) return;
   finish(c, a.staged || b.staged || cc.staged);
@@ -310,6 +314,19 @@ EXOB200_CONV_INSTANCE(3, 4, 56, 64, 3, 64, 58)
 EXOB200_CONV_INSTANCE(17, 4, 28, 128, 3, 128, 30)
 EXOB200_CONV_INSTANCE(30, 4, 14, 256, 3, 256, 16)
 #undef EXOB200_CONV_INSTANCE
+
+int exo_b200_selftest_bounded_wait(exo_b200_Context* ctxt, int limit_us) {
+  clear_error();
+  exo_b200_Context* c = resolve_context(ctxt);
+  if (!c) return exo_b200_last_error();
+  if (limit_us < 1 || limit_us > 2000000) {
+    set_error(EXO_B200_ERR_INVALID_ARGUMENT, "exo_b200_selftest_bounded_wait: limit_us must be in [1, 2000000]");
+    return exo_b200_last_error();
+  }
+  if (check_cuda(launch_bounded_wait_selftest(c, (uint64_t)limit_us * 1000ull), "selftest launch"))
+    exo_b200_synchronize(ctxt);  // reads the status word: expected to report the timeout
+  return exo_b200_last_error();
+}
 
 void gemm_bf16_exo(void* ctxt, int_fast32_t M, int_fast32_t N, int_fast32_t K, const uint16_t* A,
                    const uint16_t* B, uint16_t* C) {

@@ -9,7 +9,7 @@
 namespace exob200 {
 
 // ---- exact fp32 SIMT kernels (sgemm_ffma.cu, conv_ffma.cu)
-cudaError_t launch_sgemm_ffma(cudaStream_t stream, int64_t M, int64_t N, int64_t K, const float* A,
+cudaError_t launch_sgemm_ffma(exo_b200_Context* ctx, int64_t M, int64_t N, int64_t K, const float* A,
                               const float* B, float* C);
 
 struct ConvShape {
@@ -41,6 +41,9 @@ cudaError_t launch_matmul_i8_tc(exo_b200_Context* ctx, int64_t N, int64_t M, int
 bool tc_supported_tf32(int64_t M, int64_t N, int64_t K, const void* A, const void* B, const void* C);
 cudaError_t launch_sgemm_3xtf32_tc(exo_b200_Context* ctx, int64_t M, int64_t N, int64_t K,
                                    const float* A, const float* B, float* C);
+
+// one CTA waits on a barrier nobody signals; must end with EXO_B200_ERR_TIMEOUT in the status word
+cudaError_t launch_bounded_wait_selftest(exo_b200_Context* ctx, uint64_t limit_ns);
 
 // ---- CTA-pair (cta_group::2) variants of the bf16 and int8 GEMMs (tc_gemm2.cu)
 bool tc2_wanted(int64_t M, int64_t N);

@@ -12,6 +12,8 @@
 // right-panel / bottom-panel / corner kernels (golden :470-494, :543-737, :768-776).
 #include "ffma_tile.cuh"
 #include "kernels.cuh"
+#include "tc_common.cuh"
+#include "umma.cuh"
 
 namespace exob200 {
 namespace {
@@ -198,13 +200,280 @@ sgemm_skinny_kernel(int M, int N, int K, const float* __restrict__ A, const floa
     }
 }
 
+// --------------------------------------------------------------------------
+// GEMV-like kernel (M <= 4): the same ring, narrower strips.  With so few rows
+// the FMA work is negligible and the job is to keep HBM busy, so a CTA takes only
+// 32 columns (N = 8192 gives 256 CTAs) and 16 stages of 32 K-rows; one warp walks
+// K (thread = column, up to 4 rows, one chain each), all four warps feed the ring.
+constexpr int GV_W = 32, GV_KS = 32, GV_STAGES = 16, GV_THREADS = 128;
+constexpr int GV_SMEM = GV_STAGES * (GV_KS * GV_W + GV_KS * 4) * (int)sizeof(float);  // 72 KiB
+
+template <bool VB>
+__global__ void __launch_bounds__(GV_THREADS)
+sgemm_gemv_kernel(int M, int N, int K, const float* __restrict__ A, const float* __restrict__ B,
+                  float* __restrict__ C) {
+  extern __shared__ __align__(16) float gv_smem[];
+  float(*Bs)[GV_KS][GV_W] = reinterpret_cast<float(*)[GV_KS][GV_W]>(gv_smem);
+  float(*As)[GV_KS][4] = reinterpret_cast<float(*)[GV_KS][4]>(gv_smem + GV_STAGES * GV_KS * GV_W);
+
+  const int tid = threadIdx.x;
+  const int n0 = blockIdx.x * GV_W;
+  const int col = n0 + tid;  // compute threads: tid < 32
+  const bool compute = tid < GV_W;
+
+  float acc[4];
+#pragma unroll
+  for (int i = 0; i < 4; i++) acc[i] = (compute && i < M && col < N) ? C[(int64_t)i * N + col] : 0.f;
+
+  const int nstages = (K + GV_KS - 1) / GV_KS;
+  auto issue = [&](int st) {
+    if (st < nstages) {
+      const int buf = st % GV_STAGES, k0 = st * GV_KS;
+      // B: 32 k-rows x 8 quads = 256 quads, 2 per thread
+#pragma unroll
+      for (int i = 0; i < 2; i++) {
+        const int e = tid + i * GV_THREADS;
+        const int kk = e >> 3, q = e & 7;
+        const int k = k0 + kk, c = n0 + q * 4;
+        const bool kin = k < K;
+        const float* src = B + (kin ? (int64_t)k * N : 0);
+        if (VB) {
+          const bool ok = kin && c < N;
+          ffma::cp_async16(&Bs[buf][kk][q * 4], src + (ok ? c : 0), ok);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 4; j++) {
+            const bool ok = kin && c + j < N;
+            ffma::cp_async4(&Bs[buf][kk][q * 4 + j], src + (ok ? c + j : 0), ok);
+          }
+        }
+      }
+      // A chunk k-major: As[kk][row]
+      if (tid < 4 * GV_KS) {
+        const int r = tid / GV_KS, kk = tid % GV_KS;
+        const bool ok = r < M && k0 + kk < K;
+        ffma::cp_async4(&As[buf][kk][r], A + (ok ? (int64_t)r * K + k0 + kk : 0), ok);
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+
+  for (int st = 0; st < GV_STAGES - 1; st++) issue(st);
+  for (int st = 0; st < nstages; st++) {
+    asm volatile("cp.async.wait_group %0;" ::"n"(GV_STAGES - 2) : "memory");
+    __syncthreads();
+    issue(st + GV_STAGES - 1);
+    if (compute) {
+      const int buf = st % GV_STAGES;
+      const int kmax = min(GV_KS, K - st * GV_KS);
+      auto step = [&](int kk) {
+        const float b = Bs[buf][kk][tid];
+        const float4 a = *reinterpret_cast<const float4*>(&As[buf][kk][0]);
+        acc[0] = fmaf(a.x, b, acc[0]);
+        acc[1] = fmaf(a.y, b, acc[1]);
+        acc[2] = fmaf(a.z, b, acc[2]);
+        acc[3] = fmaf(a.w, b, acc[3]);
+      };
+      if (kmax == GV_KS) {
+#pragma unroll
+        for (int kk = 0; kk < GV_KS; kk++) step(kk);
+      } else {
+        for (int kk = 0; kk < kmax; kk++) step(kk);
+      }
+    }
+  }
+  if (compute && col < N) {
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+      if (i < M) C[(int64_t)i * N + col] = acc[i];
+  }
+}
+
+// --------------------------------------------------------------------------
+// GEMV-like kernel, TMA-fed (M <= 2, N % 4 == 0): the HBM-bound shape.
+// B streams through a ring of 16 KB fp32 boxes (64 columns x 64 K-rows, or 32 x 128) filled by one producer thread
+// with tiled TMA loads (one instruction per 16 KB instead of 1024 cp.async);
+// full/empty mbarriers replace the per-stage CTA barrier, so the two consumer
+// warps (thread = column) never wait for the loaders.  A's few rows are read
+// straight from global memory as broadcast loads.  Chain order per output is
+// unchanged: k ascending, starting from C.
+constexpr int GT_STAGES = 6;
+constexpr int GT_STAGE_BYTES = 16384;  // one box: W columns x (4096 / W) K-rows of fp32
+constexpr int GT_SMEM = GT_STAGES * GT_STAGE_BYTES + 1024 + 128;
+
+// MR = M (1 or 2), unrolled without predicates; W = strip width: 64, or 32 when N
+// is too small to give every SM a 64-column strip.
+template <int MR, int W>
+__global__ void __launch_bounds__(W + 32)
+sgemm_gemv_tma_kernel(const __grid_constant__ CUtensorMap tmB, int N, int K, const float* __restrict__ A,
+                      float* __restrict__ C, DeviceStatus* status) {
+  constexpr int GT_W = W, GT_KS = 4096 / W, AR = GT_KS / 32;  // AR: A values per lane per row
+  using namespace umma;
+  extern __shared__ uint8_t gt_raw[];
+  const uint32_t raw = smem_u32(gt_raw);
+  const uint32_t base = (raw + 127u) & ~127u;
+  const float* tiles = reinterpret_cast<const float*>(gt_raw + (base - raw));
+  const uint32_t bars = base + GT_STAGES * GT_STAGE_BYTES;
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (GT_STAGES + s); };
+  volatile int* abort_flag =
+      reinterpret_cast<volatile int*>(gt_raw + (base - raw) + GT_STAGES * GT_STAGE_BYTES + 16 * GT_STAGES);
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int n0 = blockIdx.x * GT_W;
+  if (tid == 0) {
+    for (int s = 0; s < GT_STAGES; s++) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), W / 32);  // one arrival per consumer warp
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    fence_proxy_async();
+  }
+  __syncthreads();
+  const int nstages = (K + GT_KS - 1) / GT_KS;
+
+  if (warp == W / 32) {
+    if (tid == W) {
+      prefetch_tensormap(&tmB);
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int st = 0; st < nstages; st++) {
+        if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, tc::WAIT_LIMIT_NS)) {
+          tc::report_timeout(status, abort_flag, 31);
+          break;
+        }
+        mbar_arrive_expect_tx(full_bar(stage), GT_STAGE_BYTES);
+        tma_load_2d(base + stage * GT_STAGE_BYTES, &tmB, full_bar(stage), n0, st * GT_KS);
+        if (++stage == GT_STAGES) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+    }
+    __syncwarp();
+  } else {
+    const int col = n0 + tid;
+    const int lane = tid & 31;
+    float acc[MR];
+#pragma unroll
+    for (int i = 0; i < MR; i++) acc[i] = (col < N) ? C[(int64_t)i * N + col] : 0.f;
+    // A's K chunk for a stage lives in registers, 2 values per lane per row (lane l holds
+    // k0 + l and k0 + 32 + l), and is handed out by warp shuffles; the next stage's
+    // values are requested before the current stage is multiplied.
+    auto load_a = [&](int k0, float (&ar)[MR][AR]) {
+#pragma unroll
+      for (int i = 0; i < MR; i++)
+#pragma unroll
+        for (int h = 0; h < AR; h++) {
+          const int k = k0 + h * 32 + lane;
+          ar[i][h] = k < K ? __ldg(A + (int64_t)i * K + k) : 0.f;
+        }
+    };
+    float acur[MR][AR], anext[MR][AR];
+    load_a(0, acur);
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int st = 0; st < nstages && ok; st++) {
+      load_a((st + 1) * GT_KS, anext);
+      if (!mbar_wait(full_bar(stage), phase, abort_flag, tc::WAIT_LIMIT_NS)) {
+        if (lane == 0) tc::report_timeout(status, abort_flag, 32);
+        ok = false;
+        break;
+      }
+      const float* bs = tiles + stage * (GT_KS * GT_W) + tid;
+      const int kmax = min(GT_KS, K - st * GT_KS);
+      if (kmax == GT_KS) {
+#pragma unroll
+        for (int kk = 0; kk < GT_KS; kk++) {
+          const float b = bs[kk * GT_W];
+#pragma unroll
+          for (int i = 0; i < MR; i++)
+            acc[i] = fmaf(__shfl_sync(0xffffffffu, acur[i][kk >> 5], kk & 31), b, acc[i]);
+        }
+      } else {
+        for (int kk = 0; kk < kmax; kk++) {  // ragged K tail: no padded steps
+          const float b = bs[kk * GT_W];
+#pragma unroll
+          for (int i = 0; i < MR; i++) {
+            float a = 0.f;
+#pragma unroll
+            for (int h = 0; h < AR; h++) {
+              const float v = __shfl_sync(0xffffffffu, acur[i][h], kk & 31);
+              if ((kk >> 5) == h) a = v;
+            }
+            acc[i] = fmaf(a, b, acc[i]);
+          }
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < MR; i++)
+#pragma unroll
+        for (int h = 0; h < AR; h++) acur[i][h] = anext[i][h];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(empty_bar(stage));
+      if (++stage == GT_STAGES) {
+        stage = 0;
+        phase ^= 1u;
+      }
+    }
+    if (ok && col < N) {
+#pragma unroll
+      for (int i = 0; i < MR; i++) C[(int64_t)i * N + col] = acc[i];
+    }
+  }
+}
+
 }  // namespace
 
-cudaError_t launch_sgemm_ffma(cudaStream_t stream, int64_t M, int64_t N, int64_t K, const float* A,
+cudaError_t launch_sgemm_ffma(exo_b200_Context* ctx, int64_t M, int64_t N, int64_t K, const float* A,
                               const float* B, float* C) {
+  cudaStream_t stream = ctx->stream;
   if (M > INT32_MAX || N > INT32_MAX || K > INT32_MAX) return cudaErrorInvalidValue;
   const bool va = (K % 4 == 0) && ffma::aligned16(A);
   const bool vb = (N % 4 == 0) && ffma::aligned16(B) && ffma::aligned16(C);
+  static const bool gemv_tma = [] {
+    const char* e = getenv("EXOB200_GEMV_TMA");  // =0: use the cp.async ring instead (timing experiments)
+    return !(e && e[0] == '0');
+  }();
+  if (gemv_tma && M <= 2 && vb && K >= 512) {
+    const int W = (N + 63) / 64 >= 200 ? 64 : 32;
+    CUtensorMap mb;
+    cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)K};
+    cuuint64_t strides[1] = {(cuuint64_t)N * 4};
+    cuuint32_t box[2] = {(cuuint32_t)W, (cuuint32_t)(4096 / W)};
+    if (!tc::make_tiled_map(&mb, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, B, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE))
+      return cudaErrorUnknown;
+    const unsigned grid = (unsigned)((N + W - 1) / W);
+#define EXOB200_GEMV(MR_, W_)                                                                                      \
+  {                                                                                                                \
+    cudaError_t e = cudaFuncSetAttribute(sgemm_gemv_tma_kernel<MR_, W_>,                                           \
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, GT_SMEM);                    \
+    if (e != cudaSuccess) return e;                                                                                \
+    sgemm_gemv_tma_kernel<MR_, W_><<<grid, W_ + 32, GT_SMEM, stream>>>(mb, (int)N, (int)K, A, C, ctx->status_dev); \
+  }
+    if (M == 1 && W == 64) EXOB200_GEMV(1, 64)
+    else if (M == 1) EXOB200_GEMV(1, 32)
+    else if (W == 64) EXOB200_GEMV(2, 64)
+    else EXOB200_GEMV(2, 32)
+#undef EXOB200_GEMV
+    return cudaGetLastError();
+  }
+  if (M <= 4) {
+    const unsigned grid = (unsigned)((N + GV_W - 1) / GV_W);
+    cudaError_t e;
+    if (vb) {
+      e = cudaFuncSetAttribute(sgemm_gemv_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, GV_SMEM);
+      if (e != cudaSuccess) return e;
+      sgemm_gemv_kernel<true><<<grid, GV_THREADS, GV_SMEM, stream>>>((int)M, (int)N, (int)K, A, B, C);
+    } else {
+      e = cudaFuncSetAttribute(sgemm_gemv_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, GV_SMEM);
+      if (e != cudaSuccess) return e;
+      sgemm_gemv_kernel<false><<<grid, GV_THREADS, GV_SMEM, stream>>>((int)M, (int)N, (int)K, A, B, C);
+    }
+    return cudaGetLastError();
+  }
   if (M <= 32) {
     dim3 grid((unsigned)((N + SK_W - 1) / SK_W), (unsigned)((M + 31) / 32));
     cudaError_t e;

@@ -64,7 +64,8 @@ inline EncodeTiledFn encode_fn() {
 // Tiled tensor map, 128-byte swizzle, zero fill outside the tensor.  dims/box are
 // innermost first; strides (bytes) are for dimensions 1..rank-1.
 inline bool make_tiled_map(CUtensorMap* m, CUtensorMapDataType dt, int rank, const void* base,
-                           const cuuint64_t* dims, const cuuint64_t* strides, const cuuint32_t* box) {
+                           const cuuint64_t* dims, const cuuint64_t* strides, const cuuint32_t* box,
+                           CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) {
     set_error(EXO_B200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
@@ -72,7 +73,7 @@ inline bool make_tiled_map(CUtensorMap* m, CUtensorMapDataType dt, int rank, con
   }
   cuuint32_t estr[5] = {1, 1, 1, 1, 1};
   CUresult r = fn(m, dt, (cuuint32_t)rank, const_cast<void*>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     set_error(EXO_B200_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult " + std::to_string((int)r));

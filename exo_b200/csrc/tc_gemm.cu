@@ -577,6 +577,34 @@ cudaError_t launch_sgemm_3xtf32_tc(exo_b200_Context* ctx, int64_t M, int64_t N, 
 }
 
 // --------------------------------------------------------------------------
+// Self-test of the bounded-wait machinery: one CTA waits on an mbarrier that
+// nothing ever arrives on.  The wait must run out after `limit_ns`, record
+// EXO_B200_ERR_TIMEOUT in the context's status word and return normally, leaving
+// the context usable.  (No trap, no fault: this is how a lost producer or
+// consumer would surface in the GEMM kernels.)
+namespace {
+__global__ void bounded_wait_selftest_kernel(DeviceStatus* status, uint64_t limit_ns) {
+  __shared__ __align__(8) uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&bar), 1);
+    abort_flag = 0;
+    fence_barrier_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (!mbar_wait(smem_u32(&bar), 0, &abort_flag, limit_ns)) report_timeout(status, &abort_flag, 99);
+  }
+  __syncthreads();
+}
+}  // namespace
+
+cudaError_t launch_bounded_wait_selftest(exo_b200_Context* ctx, uint64_t limit_ns) {
+  bounded_wait_selftest_kernel<<<1, 32, 0, ctx->stream>>>(ctx->status_dev, limit_ns);
+  return cudaGetLastError();
+}
+
+// --------------------------------------------------------------------------
 // matmul_on_cpu_static: the int8 matmul for callers that must not allocate.
 //
 // Some callers cannot call cudaMalloc at the point where they need a matmul:

@@ -190,6 +190,12 @@ void exo_b200_set_default_stream( void* stream );
 /* Wait for the context's stream (NULL: default context) and collect device-side status. */
 int exo_b200_synchronize( exo_b200_Context* ctxt );
 
+/* Diagnostic: launches one CTA that waits, with a limit of limit_us microseconds, on
+ * a barrier that nothing signals, then synchronises.  The expected result is
+ * EXO_B200_ERR_TIMEOUT (also left in last_error) with the context still usable:
+ * it shows that a wait that cannot complete ends as an error code, not a hang. */
+int exo_b200_selftest_bounded_wait( exo_b200_Context* ctxt, int limit_us );
+
 /* Error of the most recent call on this thread (EXO_B200_OK if it succeeded). */
 int exo_b200_last_error( void );
 const char* exo_b200_last_error_string( void );

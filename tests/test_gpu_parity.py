@@ -55,7 +55,8 @@ def test_sgemm_ffma_host_pointers_bit_exact(lib, port, golden, shape):
     assert np.array_equal(bits(C), bits(port.sgemm(A, B, C0.copy())))
 
 
-@pytest.mark.parametrize("shape", cases.SGEMM_DIGEST_CASES + [(129, 257, 40), (33, 128, 16), (32, 8192, 300)])
+@pytest.mark.parametrize("shape", cases.SGEMM_DIGEST_CASES + [(129, 257, 40), (33, 128, 16), (32, 8192, 300)]
+                         + cases.SGEMM_EXTRA_CASES)
 def test_sgemm_ffma_device_pointers_bit_exact(lib, port, torch, golden, shape):
     M, N, K = shape
     A, B, C0 = cases.sgemm_inputs(M, N, K)
@@ -126,7 +127,8 @@ def tf32x3_bound(K):
 
 
 @pytest.mark.parametrize("shape", [(128, 256, 32), (256, 512, 1024), (1000, 1000, 1000), (17, 4099, 513),
-                                   (4096, 64, 4096), (1, 8192, 2048), (300, 77, 129)])
+                                   (4096, 64, 4096), (1, 8192, 2048), (300, 77, 129), (2048, 1000, 999),
+                                   (1030, 2049, 513)])
 def test_sgemm_3xtf32_within_tolerance(lib, torch, shape):
     M, N, K = shape
     A, B, C0 = cases.sgemm_inputs(M, N, K)
@@ -404,3 +406,24 @@ def test_error_side_channel_on_gpu(lib):
         lib.sgemm_exo(None, -1, 8, 8, A, A, A)
     lib.sgemm_exo(None, 8, 8, 8, A, A, A)  # a good call clears the error
     assert lib.dll.exo_b200_last_error() == 0
+
+
+def test_bounded_wait_times_out_and_context_survives(lib):
+    """Failure detection on the device without a fault: a wait that nothing will
+    ever satisfy must run out, surface as EXO_B200_ERR_TIMEOUT through the status
+    word, and leave the context usable for the next call."""
+    import time
+
+    import exo_b200
+
+    t0 = time.time()
+    code = lib.dll.exo_b200_selftest_bounded_wait(None, 20000)  # 20 ms limit
+    dt = time.time() - t0
+    assert code == exo_b200.ERR_TIMEOUT
+    assert b"wait ran out" in lib.dll.exo_b200_last_error_string()
+    assert dt < 5.0
+    A = np.eye(8, dtype=np.float32)
+    C = np.zeros((8, 8), np.float32)
+    lib.sgemm_exo(None, 8, 8, 8, A, A, C)
+    assert np.array_equal(C, A)
+    assert lib.dll.exo_b200_synchronize(None) == 0
