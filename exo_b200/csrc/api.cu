@@ -20,7 +20,7 @@ bool bad_args(const char* fn, bool cond, const char* what) {
 
 // ---------------------------------------------------------------- SGEMM
 void sgemm_dispatch(const char* fn, void* ctxt, int path, int_fast32_t M, int_fast32_t N, int_fast32_t K,
-                    const float* A, const float* B, float* C) {
+                    const float* A, const float* B, float* C, bool path_by_name = false) {
   clear_error();
   if (bad_args(fn, M < 1 || N < 1 || K < 1, "M, N, K must be >= 1")) return;
   if (bad_args(fn, !A || !B || !C, "NULL tensor")) return;
@@ -37,8 +37,10 @@ void sgemm_dispatch(const char* fn, void* ctxt, int path, int_fast32_t M, int_fa
   cudaError_t e;
   // The tensor path has fixed costs (two split pre-passes, 128 x 256 tiles); for
   // skinny or small problems the exact FFMA kernels are faster and more accurate,
-  // so "3xTF32" only means "tensor cores where they pay".
-  const bool tensor_pays = M >= 128 && N >= 64 && 2.0 * (double)M * (double)N * (double)K >= 1.0e9;
+  // so the context-wide "3xTF32" setting means "tensor cores where they pay"; the
+  // entry point that names the path (sgemm_exo_3xtf32) always takes it.
+  const bool tensor_pays =
+      path_by_name || (M >= 128 && N >= 64 && 2.0 * (double)M * (double)N * (double)K >= 1.0e9);
   if (path == EXO_B200_SGEMM_3XTF32 && tensor_pays && tc_supported_tf32(M, N, K, dA, dB, dC))
     e = launch_sgemm_3xtf32_tc(c, M, N, K, dA, dB, dC);
   else
@@ -201,7 +203,7 @@ void sgemm_exo_ffma(void* ctxt, int_fast32_t M, int_fast32_t N, int_fast32_t K, 
 }
 void sgemm_exo_3xtf32(void* ctxt, int_fast32_t M, int_fast32_t N, int_fast32_t K, const float* A,
                       const float* B, float* C) {
-  sgemm_dispatch("sgemm_exo_3xtf32", ctxt, EXO_B200_SGEMM_3XTF32, M, N, K, A, B, C);
+  sgemm_dispatch("sgemm_exo_3xtf32", ctxt, EXO_B200_SGEMM_3XTF32, M, N, K, A, B, C, true);
 }
 
 void conv_specialized(void* ctxt, const float* inp, float* output, const float* weights, const float* bias) {
