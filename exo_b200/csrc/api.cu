@@ -12,6 +12,26 @@ using namespace exob200;
 
 namespace {
 
+// Row pipeline for host operands: worth it from about 64 MB of row traffic; chunks of
+// about 96 MB (rounded to 256 rows) keep four buffers under 400 MB of device memory.
+bool want_row_pipeline(int64_t rows, const void* host_a, const void* host_c, size_t bytes_per_row) {
+  static const bool off = [] {
+    const char* e = getenv("EXOB200_NO_PIPELINE");
+    return e && e[0] == '1';
+  }();
+  if (off) return false;
+  if (is_device_pointer(host_a) || is_device_pointer(host_c)) return false;
+  return (double)rows * (double)bytes_per_row >= 64.0e6 && rows >= 1024;
+}
+int64_t pipeline_chunk_rows(int64_t rows, size_t bytes_per_row) {
+  int64_t r = (int64_t)(96.0e6 / (double)bytes_per_row);
+  r = r / 256 * 256;
+  if (r < 256) r = 256;
+  // at least four chunks so the pipeline has something to overlap
+  while (r > 256 && (rows + r - 1) / r < 4) r = (r / 2) / 256 * 256 > 0 ? (r / 2) / 256 * 256 : 256;
+  return r;
+}
+
 bool bad_args(const char* fn, bool cond, const char* what) {
   if (!cond) return false;
   set_error(EXO_B200_ERR_INVALID_ARGUMENT, std::string(fn) + ": " + what);
@@ -28,6 +48,20 @@ void sgemm_dispatch(const char* fn, void* ctxt, int path, int_fast32_t M, int_fa
   if (!c) return;
   if (path < 0) path = c->sgemm_path;
   Operand a, b, cc;
+  if (want_row_pipeline(M, A, C, ((size_t)K + 2 * (size_t)N) * 4)) {
+    if (!stage_in(c, 1, B, sizeof(float) * (size_t)K * N, true, &b)) return;
+    const float* dB = static_cast<const float*>(b.dev);
+    RowPipeline p{M, pipeline_chunk_rows(M, ((size_t)K + 2 * (size_t)N) * 4), A, (size_t)K * 4, C, (size_t)N * 4, true};
+    const bool tensor = path == EXO_B200_SGEMM_3XTF32;
+    if (!run_row_pipeline(c, p, [&](int64_t rows, const void* dA, void* dC) {
+          if (tensor && rows >= 128 && N >= 64)
+            return launch_sgemm_3xtf32_tc(c, rows, N, K, static_cast<const float*>(dA), dB, static_cast<float*>(dC));
+          return launch_sgemm_ffma(c, rows, N, K, static_cast<const float*>(dA), dB, static_cast<float*>(dC));
+        }))
+      return;
+    finish(c, true);
+    return;
+  }
   if (!stage_in(c, 0, A, sizeof(float) * (size_t)M * K, true, &a)) return;
   if (!stage_in(c, 1, B, sizeof(float) * (size_t)K * N, true, &b)) return;
   if (!stage_in(c, 2, C, sizeof(float) * (size_t)M * N, true, &cc)) return;  // C is read: +=
@@ -121,6 +155,17 @@ void matmul_i8_dispatch(const char* fn, int_fast32_t N, int_fast32_t M, int_fast
     s = *scale;
   }
   Operand a, b, cc;
+  if (want_row_pipeline(N, A, C, (size_t)K + (size_t)M) && K % 16 == 0) {
+    if (!stage_in(c, 1, B, (size_t)K * M, true, &b)) return;
+    const int8_t* dB = static_cast<const int8_t*>(b.dev);
+    RowPipeline p{N, pipeline_chunk_rows(N, (size_t)K + (size_t)M), A, (size_t)K, C, (size_t)M, false};
+    if (!run_row_pipeline(c, p, [&](int64_t rows, const void* dA, void* dC) {
+          return launch_matmul_i8_tc(c, rows, M, K, s, act, static_cast<const int8_t*>(dA), dB, static_cast<int8_t*>(dC));
+        }))
+      return;
+    finish(c, true);
+    return;
+  }
   if (!stage_in(c, 0, A, (size_t)N * K, true, &a)) return;
   if (!stage_in(c, 1, B, (size_t)K * M, true, &b)) return;
   if (!stage_in(c, 2, C, (size_t)N * M, false, &cc)) return;
@@ -339,6 +384,22 @@ void gemm_bf16_exo(void* ctxt, int_fast32_t M, int_fast32_t N, int_fast32_t K, c
   exo_b200_Context* c = resolve_context(ctxt);
   if (!c) return;
   Operand a, b, cc;
+  if (want_row_pipeline(M, A, C, (size_t)K * 2 + (size_t)N * 2)) {
+    // host A and C: rows are independent, so stream them through in chunks
+    if (!stage_in(c, 1, B, sizeof(uint16_t) * (size_t)K * N, true, &b)) return;
+    if (!tc_supported_bf16(M, N, K, nullptr, b.dev, nullptr)) {
+      set_error(EXO_B200_ERR_UNSUPPORTED, "gemm_bf16_exo: K must be a multiple of 8 and bases 16-byte aligned");
+      return;
+    }
+    RowPipeline p{M, pipeline_chunk_rows(M, (size_t)K * 2 + (size_t)N * 2), A, (size_t)K * 2, C, (size_t)N * 2, false};
+    const uint16_t* dB = static_cast<const uint16_t*>(b.dev);
+    if (!run_row_pipeline(c, p, [&](int64_t rows, const void* dA, void* dC) {
+          return launch_gemm_bf16_tc(c, rows, N, K, static_cast<const uint16_t*>(dA), dB, static_cast<uint16_t*>(dC));
+        }))
+      return;
+    finish(c, true);
+    return;
+  }
   if (!stage_in(c, 0, A, sizeof(uint16_t) * (size_t)M * K, true, &a)) return;
   if (!stage_in(c, 1, B, sizeof(uint16_t) * (size_t)K * N, true, &b)) return;
   if (!stage_in(c, 2, C, sizeof(uint16_t) * (size_t)M * N, false, &cc)) return;

@@ -161,6 +161,36 @@ bool finish(exo_b200_Context* c, bool any_staged) {
   return read_status(c);
 }
 
+bool pipeline_prepare(exo_b200_Context* c, size_t a_chunk_bytes, size_t c_chunk_bytes) {
+  if (!c->pipe_ready) {
+    if (!check_cuda(cudaStreamCreateWithFlags(&c->pipe_in, cudaStreamNonBlocking), "cudaStreamCreate")) return false;
+    if (!check_cuda(cudaStreamCreateWithFlags(&c->pipe_out, cudaStreamNonBlocking), "cudaStreamCreate")) return false;
+    for (int i = 0; i < 2; i++) {
+      cudaEventCreateWithFlags(&c->ev_in[i], cudaEventDisableTiming);
+      cudaEventCreateWithFlags(&c->ev_kernel[i], cudaEventDisableTiming);
+      cudaEventCreateWithFlags(&c->ev_out[i], cudaEventDisableTiming);
+    }
+    if (!check_cuda(cudaEventCreateWithFlags(&c->ev_ready, cudaEventDisableTiming), "cudaEventCreate")) return false;
+    c->pipe_ready = true;
+  }
+  if (c->pipe_a_bytes < a_chunk_bytes || c->pipe_c_bytes < c_chunk_bytes) {
+    if (!check_cuda(cudaStreamSynchronize(c->stream), "cudaStreamSynchronize")) return false;
+    for (int i = 0; i < 2; i++) {
+      if (c->pipe_a[i]) cudaFree(c->pipe_a[i]);
+      if (c->pipe_c[i]) cudaFree(c->pipe_c[i]);
+      c->pipe_a[i] = c->pipe_c[i] = nullptr;
+    }
+    c->pipe_a_bytes = c->pipe_c_bytes = 0;
+    for (int i = 0; i < 2; i++) {
+      if (!check_cuda(cudaMalloc(&c->pipe_a[i], a_chunk_bytes), "cudaMalloc(pipeline)")) return false;
+      if (!check_cuda(cudaMalloc(&c->pipe_c[i], c_chunk_bytes), "cudaMalloc(pipeline)")) return false;
+    }
+    c->pipe_a_bytes = a_chunk_bytes;
+    c->pipe_c_bytes = c_chunk_bytes;
+  }
+  return true;
+}
+
 bool ensure_scratch(exo_b200_Context* c, int slot, size_t bytes) {
   if (c->scratch_bytes[slot] >= bytes) return true;
   if (c->scratch[slot]) {
@@ -194,6 +224,18 @@ void exo_b200_context_destroy(exo_b200_Context* c) {
   for (int i = 0; i < 2; i++)
     if (c->scratch[i]) cudaFree(c->scratch[i]);
   if (c->status_host) cudaFreeHost(c->status_host);
+  if (c->pipe_ready) {
+    cudaStreamDestroy(c->pipe_in);
+    cudaStreamDestroy(c->pipe_out);
+    for (int i = 0; i < 2; i++) {
+      cudaEventDestroy(c->ev_in[i]);
+      cudaEventDestroy(c->ev_kernel[i]);
+      cudaEventDestroy(c->ev_out[i]);
+      if (c->pipe_a[i]) cudaFree(c->pipe_a[i]);
+      if (c->pipe_c[i]) cudaFree(c->pipe_c[i]);
+    }
+    cudaEventDestroy(c->ev_ready);
+  }
   c->magic = 0;
   delete c;
 }

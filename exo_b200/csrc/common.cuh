@@ -36,6 +36,13 @@ struct exo_b200_Context {
   size_t scratch_bytes[2];
   exob200::DeviceStatus* status_dev;   // device word
   exob200::DeviceStatus* status_host;  // pinned mirror
+  // host-pointer row pipeline: copy-in / copy-out streams, two chunk buffers each way
+  cudaStream_t pipe_in, pipe_out;
+  cudaEvent_t ev_in[2], ev_kernel[2], ev_out[2], ev_ready;
+  void* pipe_a[2];
+  void* pipe_c[2];
+  size_t pipe_a_bytes, pipe_c_bytes;
+  bool pipe_ready;
 };
 
 namespace exob200 {
@@ -72,5 +79,71 @@ bool stage_out(exo_b200_Context* c, const Operand& op);
 bool finish(exo_b200_Context* c, bool any_staged);
 
 bool ensure_scratch(exo_b200_Context* c, int slot, size_t bytes);
+
+// Host-pointer calls whose output rows depend only on the matching rows of one
+// input (GEMM: C rows <- A rows) are run as a pipeline over row chunks: while
+// chunk i is multiplied, chunk i+1 is copied in and chunk i-1 is copied out on
+// two side streams, so the PCIe copies in both directions overlap each other and
+// the kernels instead of adding up.  `launch(rows, dA, dC)` enqueues the kernel
+// for one chunk on c->stream.  Returns false with the error set on failure; on
+// return all copies have completed.
+struct RowPipeline {
+  int64_t rows;            // total rows
+  int64_t chunk_rows;      // rows per chunk
+  const void* host_a;      // row-major, a_row_bytes per row
+  size_t a_row_bytes;
+  void* host_c;
+  size_t c_row_bytes;
+  bool c_is_input;         // C is read by the kernel (C += ...): copy it in too
+};
+template <class Launch>
+bool run_row_pipeline(exo_b200_Context* c, const RowPipeline& p, Launch launch);
+bool pipeline_prepare(exo_b200_Context* c, size_t a_chunk_bytes, size_t c_chunk_bytes);
+
+
+template <class Launch>
+bool run_row_pipeline(exo_b200_Context* c, const RowPipeline& p, Launch launch) {
+  const size_t a_chunk = (size_t)p.chunk_rows * p.a_row_bytes, c_chunk = (size_t)p.chunk_rows * p.c_row_bytes;
+  if (!pipeline_prepare(c, a_chunk, c_chunk)) return false;
+  // everything enqueued on c->stream so far (the staged B operand) must be in place first
+  if (!check_cuda(cudaEventRecord(c->ev_ready, c->stream), "cudaEventRecord")) return false;
+  const int64_t nchunks = (p.rows + p.chunk_rows - 1) / p.chunk_rows;
+  for (int64_t i = 0; i < nchunks; i++) {
+    const int b = (int)(i & 1);
+    const int64_t r0 = i * p.chunk_rows;
+    const int64_t rows = p.rows - r0 < p.chunk_rows ? p.rows - r0 : p.chunk_rows;
+    const char* ha = static_cast<const char*>(p.host_a) + (size_t)r0 * p.a_row_bytes;
+    char* hc = static_cast<char*>(p.host_c) + (size_t)r0 * p.c_row_bytes;
+    // copy-in: the kernel that last read buffer b (chunk i-2) must be done; for C as an
+    // input, so must the copy-out that last read it
+    if (i >= 2) {
+      cudaStreamWaitEvent(c->pipe_in, c->ev_kernel[b], 0);
+      if (p.c_is_input) cudaStreamWaitEvent(c->pipe_in, c->ev_out[b], 0);
+    }
+    if (!check_cuda(cudaMemcpyAsync(c->pipe_a[b], ha, (size_t)rows * p.a_row_bytes, cudaMemcpyHostToDevice, c->pipe_in),
+                    "H2D chunk"))
+      return false;
+    if (p.c_is_input &&
+        !check_cuda(cudaMemcpyAsync(c->pipe_c[b], hc, (size_t)rows * p.c_row_bytes, cudaMemcpyHostToDevice, c->pipe_in),
+                    "H2D chunk"))
+      return false;
+    cudaEventRecord(c->ev_in[b], c->pipe_in);
+    // kernel: needs its inputs, and the copy-out of chunk i-2 must have drained C buffer b
+    cudaStreamWaitEvent(c->stream, c->ev_in[b], 0);
+    if (i >= 2) cudaStreamWaitEvent(c->stream, c->ev_out[b], 0);
+    if (!check_cuda(launch(rows, c->pipe_a[b], c->pipe_c[b]), "chunk kernel")) return false;
+    cudaEventRecord(c->ev_kernel[b], c->stream);
+    // copy-out
+    if (i == 0) cudaStreamWaitEvent(c->pipe_out, c->ev_ready, 0);
+    cudaStreamWaitEvent(c->pipe_out, c->ev_kernel[b], 0);
+    if (!check_cuda(cudaMemcpyAsync(hc, c->pipe_c[b], (size_t)rows * p.c_row_bytes, cudaMemcpyDeviceToHost, c->pipe_out),
+                    "D2H chunk"))
+      return false;
+    cudaEventRecord(c->ev_out[b], c->pipe_out);
+  }
+  if (!check_cuda(cudaStreamSynchronize(c->pipe_out), "cudaStreamSynchronize")) return false;
+  if (!check_cuda(cudaStreamSynchronize(c->pipe_in), "cudaStreamSynchronize")) return false;
+  return true;
+}
 
 }  // namespace exob200
