@@ -501,10 +501,15 @@ def run_ours(args):
 
     peak = peaks["bf16_tflops"]
     per_launch_tflops = wl.flops_local / (ms / 1e3) / 1e12
+    # DRAM bytes per launch of the headline shape from a one-pass ncu capture of one full-size
+    # launch (profiles/gemm_tc2_bf16_8192x8192x4096.md); scaled by the rows a rank owns
+    traffic = None
+    if args.workload == "bf16" and shape is None:
+        traffic = 14.43e9 * wl.shape[0] / BF16_SHAPE[0]
     roofline = {"bound": "tensor", "achieved": per_launch_tflops, "peak": peak, "unit": "TFLOP/s",
-                "frac": per_launch_tflops / peak, "traffic": None,
+                "frac": per_launch_tflops / peak, "traffic": traffic,
                 "peak_source": f"{peaks['source']} bf16 burst (sustained: {peaks.get('bf16_tflops_sustained')})",
-                "kernel": "gemm_tc_kernel<bf16>" if args.workload == "bf16" else args.workload}
+                "kernel": "gemm_tc2_kernel<bf16>" if args.workload == "bf16" else args.workload}
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",

@@ -92,6 +92,27 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster), "r"(x), "r"(y)
       : "memory");
 }
+// L2 eviction-priority policies for the TMA loads: the operand panel that the next
+// waves of tiles will read again is kept (evict_last), the one that streams
+// through is marked evict_first so it does not push the panel out.
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ void tma_load_2d_pair_hint(uint32_t dst, const CUtensorMap* m, uint32_t bar_cluster, int x,
+                                                      int y, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint "
+      "[%0], [%1, {%3, %4}], [%2], %5;"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster), "r"(x), "r"(y), "l"(policy)
+      : "memory");
+}
 __device__ __forceinline__ void tmem_alloc2(uint32_t smem_result, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_result), "r"(ncols)
                : "memory");
@@ -189,7 +210,7 @@ __device__ __forceinline__ void store_chunk2(const Epi2& ep, const uint32_t (&r)
 template <int MODE>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, int M, int N, int K,
-                Epi2 ep, DeviceStatus* status, int tiles_m, int tiles_n) {
+                Epi2 ep, DeviceStatus* status, int tiles_m, int tiles_n, int GM, int use_hints) {
   using C = Cfg2<MODE>;
   constexpr int BK = ROW_BYTES / C::ELEM;
   constexpr uint32_t IDESC =
@@ -240,7 +261,6 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 
   const int num_tiles = tiles_m * tiles_n;  // 256 x 256 tiles
   const int num_kb = (K + BK - 1) / BK;
-  constexpr int GM = 8;
   auto tile_coord = [&](int t, int& tm, int& tn) {
     const int per_group = GM * tiles_n;
     const int group = t / per_group;
@@ -261,6 +281,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      const uint64_t keep = l2_policy_evict_last(), stream_through = l2_policy_evict_first();
       for (int t = pair; t < num_tiles && ok; t += num_pairs) {
         int tm, tn;
         tile_coord(t, tm, tn);
@@ -276,11 +297,26 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           const uint32_t dst = tiles + stage * STAGE2_BYTES;
           if (rank == 0) mbar_arrive_expect_tx(full_bar(stage), 2 * STAGE2_BYTES);
           const int k0 = kb * BK;
-          tma_load_2d_pair(dst, &tmA, bar0, k0, m0);
-          if (C::BMN)
-            tma_load_2d_pair(dst + A_TILE_BYTES, &tmB, bar0, n0, k0);  // {128 bytes of N, BK rows of K}
-          else
-            tma_load_2d_pair(dst + A_TILE_BYTES, &tmB, bar0, k0, n0);
+          if (use_hints) {
+            // experiment knob (1: A evict_last + B evict_first, 2: A evict_last only); both
+            // measured worse than the default policy and are off by default
+            tma_load_2d_pair_hint(dst, &tmA, bar0, k0, m0, keep);
+            if (use_hints == 2) {
+              if (C::BMN)
+                tma_load_2d_pair(dst + A_TILE_BYTES, &tmB, bar0, n0, k0);
+              else
+                tma_load_2d_pair(dst + A_TILE_BYTES, &tmB, bar0, k0, n0);
+            } else if (C::BMN)
+              tma_load_2d_pair_hint(dst + A_TILE_BYTES, &tmB, bar0, n0, k0, stream_through);
+            else
+              tma_load_2d_pair_hint(dst + A_TILE_BYTES, &tmB, bar0, k0, n0, stream_through);
+          } else {
+            tma_load_2d_pair(dst, &tmA, bar0, k0, m0);
+            if (C::BMN)
+              tma_load_2d_pair(dst + A_TILE_BYTES, &tmB, bar0, n0, k0);  // {128 bytes of N, BK rows of K}
+            else
+              tma_load_2d_pair(dst + A_TILE_BYTES, &tmB, bar0, k0, n0);
+          }
           if (++stage == STAGES2) {
             stage = 0;
             phase ^= 1u;
@@ -410,8 +446,16 @@ cudaError_t launch_tc2(exo_b200_Context* ctx, const CUtensorMap& ma, const CUten
   }
   const int pairs = (int)std::min<int64_t>(tiles_m * tiles_n, max_clusters);
   cfg.gridDim = dim3(2 * pairs);
+  static const int gm = [] {
+    const char* e = getenv("EXOB200_TC2_GM");
+    return e ? std::max(1, atoi(e)) : 8;
+  }();
+  static const int hints = [] {
+    const char* e = getenv("EXOB200_TC2_HINT");
+    return e ? atoi(e) : 0;
+  }();
   return cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<MODE>, ma, mb, (int)M, (int)N, (int)K, ep, ctx->status_dev,
-                            (int)tiles_m, (int)tiles_n);
+                            (int)tiles_m, (int)tiles_n, gm, hints);
 }
 
 }  // namespace
