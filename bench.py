@@ -275,15 +275,14 @@ class Workload:
     # -- fp32 SGEMM 8192^3 (FFMA exact / 3xTF32)
     def _setup_sgemm(self, n=8192):
         t = self.torch
-        if self.custom_shape:
-            n = self.custom_shape[0]
+        M, N, K = self.custom_shape or (n, n, n)
         self.dtype = "f32"
-        self.shape = (n, n, n)
+        self.shape = (M, N, K)
         g = t.Generator(device="cuda").manual_seed(5)
-        self.A = t.rand((n, n), generator=g, device="cuda") * 2 - 1
-        self.B = t.rand((n, n), generator=g, device="cuda") * 2 - 1
-        self.C = t.zeros((n, n), device="cuda")
-        self.flops_total = self.flops_local = 2.0 * n ** 3
+        self.A = t.rand((M, K), generator=g, device="cuda") * 2 - 1
+        self.B = t.rand((K, N), generator=g, device="cuda") * 2 - 1
+        self.C = t.zeros((M, N), device="cuda")
+        self.flops_total = self.flops_local = 2.0 * M * N * K
         self.bound = "tensor"
 
     _setup_sgemm_ffma = _setup_sgemm
@@ -293,12 +292,12 @@ class Workload:
         self.launches_per_step = 3  # two split pre-passes + the GEMM
 
     def step_sgemm_ffma(self):
-        n = self.shape[0]
-        self.lib.sgemm_exo_ffma(None, n, n, n, self.A, self.B, self.C)
+        M, N, K = self.shape
+        self.lib.sgemm_exo_ffma(None, M, N, K, self.A, self.B, self.C)
 
     def step_sgemm_3xtf32(self):
-        n = self.shape[0]
-        self.lib.sgemm_exo_3xtf32(None, n, n, n, self.A, self.B, self.C)
+        M, N, K = self.shape
+        self.lib.sgemm_exo_3xtf32(None, M, N, K, self.A, self.B, self.C)
 
     def host_sgemm(self):
         t = self.torch
@@ -310,12 +309,12 @@ class Workload:
     host_sgemm_ffma = host_sgemm_3xtf32 = host_sgemm
 
     def e2e_sgemm_ffma(self):
-        n = self.shape[0]
-        self.lib.sgemm_exo_ffma(None, n, n, n, self.hA, self.hB, self.hC)
+        M, N, K = self.shape
+        self.lib.sgemm_exo_ffma(None, M, N, K, self.hA, self.hB, self.hC)
 
     def e2e_sgemm_3xtf32(self):
-        n = self.shape[0]
-        self.lib.sgemm_exo_3xtf32(None, n, n, n, self.hA, self.hB, self.hC)
+        M, N, K = self.shape
+        self.lib.sgemm_exo_3xtf32(None, M, N, K, self.hA, self.hB, self.hC)
 
     # -- int8 4096^3
     def _setup_i8(self, n=4096):
@@ -639,7 +638,8 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="bf16", choices=["bf16", "sgemm_ffma", "sgemm_3xtf32", "i8"])
+    ap.add_argument("--workload", default="bf16", choices=["bf16", "sgemm_ffma", "sgemm_3xtf32", "i8", "conv", "conv_3xtf32", "conv1x1", "conv1x1_3xtf32",
+                             "conv_i8"])
     ap.add_argument("--shape", default=None, help="MxNxK override for small profiling cases")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-sweep", action="store_true")
