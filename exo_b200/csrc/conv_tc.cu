@@ -262,7 +262,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
     for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
       int img, oy0, ox0, n0;
       tile_coord(t, img, oy0, ox0, n0);
-      if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, WAIT_LIMIT_NS)) {
+      if (!mbar_wait_warp(tfull_bar(acc), acc_phase, abort_flag, WAIT_LIMIT_NS)) {
         if (lane == 0) report_timeout(status, abort_flag, 14);
         break;
       }

@@ -56,16 +56,24 @@ struct Cfg;
 template <>
 struct Cfg<MODE_BF16> {
   static constexpr int ELEM = 2, NA = 1, NB = 1, NPROD = 1, STAGES = 4, KIND = KIND_F16;
+  static constexpr int CHUNK_KB = 1 << 30;  // k-blocks accumulated in tensor memory before a drain: all
   static constexpr uint32_t IDESC = make_idesc(1, 1, 1, BM, BN);
 };
 template <>
 struct Cfg<MODE_I8> {
   static constexpr int ELEM = 1, NA = 1, NB = 1, NPROD = 1, STAGES = 4, KIND = KIND_I8;
+  static constexpr int CHUNK_KB = 1 << 30;
   static constexpr uint32_t IDESC = make_idesc(2, 1, 1, BM, BN);
 };
 template <>
 struct Cfg<MODE_TF32X3> {
   static constexpr int ELEM = 4, NA = 2, NB = 2, NPROD = 3, STAGES = 2, KIND = KIND_TF32;
+  // The tensor core adds into its fp32 accumulator without round-to-nearest, a bias that
+  // grows with the number of accumulation steps.  So K is accumulated in tensor memory in
+  // chunks of 32 k-blocks (1024 elements); each chunk's partial sum is then added to C by
+  // the epilogue warps with ordinary round-to-nearest fp32 adds (the epilogue is "C +="
+  // anyway, and it overlaps the next chunk's MMAs through the second accumulator).
+  static constexpr int CHUNK_KB = 32;
   static constexpr uint32_t IDESC = make_idesc(1, 2, 2, BM, BN);
 };
 
@@ -162,11 +170,20 @@ __device__ __forceinline__ void store_chunk(const EpiParams& ep, const uint32_t 
 // BMN: B is read MN-major straight from the caller's row-major K x N array (no
 // transposing pre-pass): per stage BN*ELEM/128 TMA boxes {128 bytes of N, BK rows
 // of K}, and the B descriptor / instruction descriptor say "MN-major".
+template <int MODE>
+__host__ __device__ constexpr int epi_warps() {
+  return MODE == MODE_TF32X3 ? 8 : 4;  // 3xTF32 keeps a tile's running sum in registers: 128 columns per thread
+}
+template <int MODE>
+__host__ __device__ constexpr int tc_threads() {
+  return 64 + 32 * epi_warps<MODE>();
+}
+
 template <int MODE, bool BMN = false>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__global__ void __launch_bounds__(tc_threads<MODE>(), 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmA1,
                const __grid_constant__ CUtensorMap tmB0, const __grid_constant__ CUtensorMap tmB1, int M, int N,
-               int K, EpiParams ep, DeviceStatus* status, int tiles_m, int tiles_n) {
+               int K, EpiParams ep, DeviceStatus* status, int tiles_m, int tiles_n, int chunk_kb) {
   using C = Cfg<MODE>;
   constexpr int STAGES = C::STAGES;
   constexpr int STAGE_BYTES = stage_bytes<MODE>();
@@ -193,7 +210,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
     }
     for (int b = 0; b < 2; b++) {
       mbar_init(tfull_bar(b), 1);
-      mbar_init(tempty_bar(b), 4);  // one arrival per epilogue warp
+      mbar_init(tempty_bar(b), epi_warps<MODE>());  // one arrival per epilogue warp
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -283,51 +300,56 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
       uint32_t acc_phase = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, WAIT_LIMIT_NS)) {
-          report_timeout(status, abort_flag, 2);
-          break;
-        }
-        tc_fence_after();
-        const uint32_t d = tmem_base + (uint32_t)(acc * BN);
-        for (int kb = 0; kb < num_kb; kb++) {
-          if (!mbar_wait(full_bar(stage), phase, abort_flag, WAIT_LIMIT_NS)) {
-            report_timeout(status, abort_flag, 3);
+        for (int kb0 = 0; kb0 < num_kb && ok; kb0 += chunk_kb) {
+          const int kb1 = min(num_kb, kb0 + chunk_kb);
+          if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, WAIT_LIMIT_NS)) {
+            report_timeout(status, abort_flag, 2);
             ok = false;
             break;
           }
           tc_fence_after();
-          const uint32_t a0 = tiles + stage * STAGE_BYTES;
-          const uint32_t b0 = a0 + C::NA * A_TILE_BYTES;
-          const uint64_t da_hi = smem_desc_k_sw128(a0);
-          const uint64_t db_hi = BMN ? smem_desc_mn_sw128(b0, BK) : smem_desc_k_sw128(b0);
-          constexpr uint32_t IDESC = C::IDESC | (BMN ? IDESC_B_MN_MAJOR : 0u);
-          // one MMA consumes 32 bytes of K: K-major that is 32 bytes along the row;
-          // MN-major it is (32 / ELEM) K-rows of 128 bytes
-          constexpr uint64_t B_ADV = BMN ? (uint64_t)((32 / C::ELEM) * ROW_BYTES / 16) : 2u;
+          const uint32_t d = tmem_base + (uint32_t)(acc * BN);
+          for (int kb = kb0; kb < kb1; kb++) {
+            if (!mbar_wait(full_bar(stage), phase, abort_flag, WAIT_LIMIT_NS)) {
+              report_timeout(status, abort_flag, 3);
+              ok = false;
+              break;
+            }
+            tc_fence_after();
+            const uint32_t a0 = tiles + stage * STAGE_BYTES;
+            const uint32_t b0 = a0 + C::NA * A_TILE_BYTES;
+            const uint64_t da_hi = smem_desc_k_sw128(a0);
+            const uint64_t db_hi = BMN ? smem_desc_mn_sw128(b0, BK) : smem_desc_k_sw128(b0);
+            constexpr uint32_t IDESC = C::IDESC | (BMN ? IDESC_B_MN_MAJOR : 0u);
+            // one MMA consumes 32 bytes of K: K-major that is 32 bytes along the row;
+            // MN-major it is (32 / ELEM) K-rows of 128 bytes
+            constexpr uint64_t B_ADV = BMN ? (uint64_t)((32 / C::ELEM) * ROW_BYTES / 16) : 2u;
+            const uint32_t first = (kb == kb0) ? 0u : 1u;  // the chunk's first MMA overwrites the accumulator
 #pragma unroll
-          for (int ks = 0; ks < KSTEPS; ks++) {
-            const uint64_t adv = (uint64_t)(ks * 2);  // 32 bytes, in 16-byte units
-            if (C::NPROD == 1) {
-              tc_mma<C::KIND>(d, da_hi + adv, db_hi + ks * B_ADV, IDESC, (kb | ks) != 0);
-            } else {
-              const uint64_t da_lo = smem_desc_k_sw128(a0 + A_TILE_BYTES);
-              const uint64_t db_lo = smem_desc_k_sw128(b0 + B_TILE_BYTES);
-              // small terms first, then the leading term
-              tc_mma<C::KIND>(d, da_lo + adv, db_hi + adv, C::IDESC, (kb | ks) != 0);
-              tc_mma<C::KIND>(d, da_hi + adv, db_lo + adv, C::IDESC, 1);
-              tc_mma<C::KIND>(d, da_hi + adv, db_hi + adv, C::IDESC, 1);
+            for (int ks = 0; ks < KSTEPS; ks++) {
+              const uint64_t adv = (uint64_t)(ks * 2);  // 32 bytes, in 16-byte units
+              if (C::NPROD == 1) {
+                tc_mma<C::KIND>(d, da_hi + adv, db_hi + ks * B_ADV, IDESC, first | (uint32_t)ks);
+              } else {
+                const uint64_t da_lo = smem_desc_k_sw128(a0 + A_TILE_BYTES);
+                const uint64_t db_lo = smem_desc_k_sw128(b0 + B_TILE_BYTES);
+                // small terms first, then the leading term
+                tc_mma<C::KIND>(d, da_lo + adv, db_hi + adv, C::IDESC, first | (uint32_t)ks);
+                tc_mma<C::KIND>(d, da_hi + adv, db_lo + adv, C::IDESC, 1);
+                tc_mma<C::KIND>(d, da_hi + adv, db_hi + adv, C::IDESC, 1);
+              }
+            }
+            tc_commit(empty_bar(stage));  // stage reusable once these MMAs have read it
+            if (++stage == STAGES) {
+              stage = 0;
+              phase ^= 1u;
             }
           }
-          tc_commit(empty_bar(stage));  // stage reusable once these MMAs have read it
-          if (++stage == STAGES) {
-            stage = 0;
-            phase ^= 1u;
-          }
+          if (!ok) break;
+          tc_commit(tfull_bar(acc));  // this chunk's accumulator is complete
+          acc ^= 1;
+          if (acc == 0) acc_phase ^= 1u;
         }
-        if (!ok) break;
-        tc_commit(tfull_bar(acc));  // accumulator complete
-        acc ^= 1;
-        if (acc == 0) acc_phase ^= 1u;
       }
     }
     __syncwarp();
@@ -340,26 +362,81 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
       int tm, tn;
       tile_coord(t, tm, tn);
       const int m0 = tm * BM, n0 = tn * BN;
-      if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, WAIT_LIMIT_NS)) {
-        if (lane == 0) report_timeout(status, abort_flag, 4);
-        break;
-      }
-      tc_fence_after();
       const int row = m0 + q * 32 + lane;
-#pragma unroll 1
-      for (int ch = 0; ch < BN / 32; ch++) {
-        const int col = n0 + ch * 32;
-        if (col >= N) break;  // warp-uniform
-        uint32_t r[32];
-        tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + ch * 32), r);
-        tmem_ld_wait();
-        store_chunk<MODE>(ep, r, row, col, M, N);
+      bool ok = true;
+      const int half = (warp - 2) >> 2;  // 3xTF32 only: which 128 columns of the tile this warp owns
+      float part[MODE == MODE_TF32X3 ? 128 : 1];
+      if (MODE == MODE_TF32X3) {
+#pragma unroll
+        for (int j = 0; j < 128; j++) part[j] = 0.f;
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(tempty_bar(acc));
-      acc ^= 1;
-      if (acc == 0) acc_phase ^= 1u;
+      // one pass per K chunk (a single pass except for 3xTF32, whose passes each add a
+      // partial sum to C; the same thread owns the same elements in every pass)
+      for (int kb0 = 0; kb0 < num_kb; kb0 += chunk_kb) {
+        if (!mbar_wait_warp(tfull_bar(acc), acc_phase, abort_flag, WAIT_LIMIT_NS)) {
+          if (lane == 0) report_timeout(status, abort_flag, 4);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        if (MODE == MODE_TF32X3) {
+          // add this chunk's partial sums (tensor memory) to the tile's running sums
+          // (registers, round-to-nearest adds); this warp owns columns [half*128, +128)
+#pragma unroll
+          for (int cc = 0; cc < 8; cc++) {
+            if (n0 + half * 128 + cc * 16 < N) {  // warp-uniform
+              uint32_t r[16];
+              tmem_ld_32x16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + half * 128 + cc * 16), r);
+              tmem_ld_wait();
+#pragma unroll
+              for (int j = 0; j < 16; j++) part[cc * 16 + j] += __uint_as_float(r[j]);
+            }
+          }
+        } else {
+#pragma unroll 1
+          for (int ch = 0; ch < BN / 32; ch++) {
+            const int col = n0 + ch * 32;
+            if (col >= N) break;  // warp-uniform
+            uint32_t r[32];
+            tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + ch * 32), r);
+            tmem_ld_wait();
+            store_chunk<MODE>(ep, r, row, col, M, N);
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty_bar(acc));
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+      if (!ok) break;
+      if (MODE == MODE_TF32X3 && row < M) {
+        // C += running sum: one read-modify-write per tile, loads issued ahead of the adds
+        float* crow = static_cast<float*>(ep.C) + (int64_t)row * ep.ldc + n0 + half * 128;
+        const int ncols = min(128, N - (n0 + half * 128));
+        if (ep.vec_ok) {
+#pragma unroll
+          for (int g = 0; g < 8; g++) {
+            float4 c[4];
+#pragma unroll
+            for (int v = 0; v < 4; v++)
+              if (g * 16 + v * 4 + 4 <= ncols) c[v] = *reinterpret_cast<const float4*>(crow + g * 16 + v * 4);
+#pragma unroll
+            for (int v = 0; v < 4; v++)
+              if (g * 16 + v * 4 + 4 <= ncols) {
+                c[v].x += part[g * 16 + v * 4 + 0];
+                c[v].y += part[g * 16 + v * 4 + 1];
+                c[v].z += part[g * 16 + v * 4 + 2];
+                c[v].w += part[g * 16 + v * 4 + 3];
+                *reinterpret_cast<float4*>(crow + g * 16 + v * 4) = c[v];
+              }
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 128; j++)
+            if (j < ncols) crow[j] += part[j];
+        }
+      }
     }
   }
 
@@ -468,6 +545,19 @@ bool make_mnmajor_map(CUtensorMap* m, CUtensorMapDataType dt, int elem, const vo
   return make_tiled_map(m, dt, 2, base, dims, strides, box);
 }
 
+// k-blocks accumulated in tensor memory between drains (EXOB200_TF32_CHUNK overrides the
+// 3xTF32 value, in k-blocks of 32 elements; timing / accuracy experiments)
+template <int MODE>
+int chunk_kb() {
+  if (MODE != MODE_TF32X3) return Cfg<MODE>::CHUNK_KB;
+  static const int v = [] {
+    const char* e = getenv("EXOB200_TF32_CHUNK");
+    const int n = e ? atoi(e) : 0;
+    return n > 0 ? n : Cfg<MODE_TF32X3>::CHUNK_KB;
+  }();
+  return v;
+}
+
 template <int MODE, bool BMN = false>
 cudaError_t launch_tc(exo_b200_Context* ctx, const CUtensorMap& a0, const CUtensorMap& a1, const CUtensorMap& b0,
                       const CUtensorMap& b1, int64_t M, int64_t N, int64_t K, const EpiParams& ep) {
@@ -480,8 +570,8 @@ cudaError_t launch_tc(exo_b200_Context* ctx, const CUtensorMap& a0, const CUtens
   if (tiles_m * tiles_n > INT32_MAX || M > INT32_MAX || N > INT32_MAX || K > INT32_MAX)
     return cudaErrorInvalidValue;
   const int grid = (int)std::min<int64_t>(tiles_m * tiles_n, ctx->sm_count);
-  gemm_tc_kernel<MODE, BMN><<<grid, NUM_THREADS, smem_bytes<MODE>(), ctx->stream>>>(
-      a0, a1, b0, b1, (int)M, (int)N, (int)K, ep, ctx->status_dev, (int)tiles_m, (int)tiles_n);
+  gemm_tc_kernel<MODE, BMN><<<grid, tc_threads<MODE>(), smem_bytes<MODE>(), ctx->stream>>>(
+      a0, a1, b0, b1, (int)M, (int)N, (int)K, ep, ctx->status_dev, (int)tiles_m, (int)tiles_n, chunk_kb<MODE>());
   return cudaGetLastError();
 }
 
@@ -726,7 +816,7 @@ extern "C" __attribute__((visibility("default"))) void matmul_on_cpu_static(
   // no status word: a bounded device-side wait that runs out ends the kernel but is not reported here
   gemm_tc_kernel<MODE_I8><<<grid, NUM_THREADS, smem_bytes<MODE_I8>(), s>>>(ma, ma, mb, mb, (int)rows, (int)cols,
                                                                            (int)K, ep, nullptr, (int)tiles_m,
-                                                                           (int)tiles_n);
+                                                                           (int)tiles_n, 1 << 30);
   check_cuda(cudaGetLastError(), fn);
 }
 

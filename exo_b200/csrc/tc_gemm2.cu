@@ -384,7 +384,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       int tm, tn;
       tile_coord(t, tm, tn);
       const int m0 = tm * 2 * BM + (int)rank * BM, n0 = tn * BN2;
-      if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, WAIT_LIMIT_NS)) {
+      if (!mbar_wait_warp(tfull_bar(acc), acc_phase, abort_flag, WAIT_LIMIT_NS)) {
         if (lane == 0) give_up(24);
         break;
       }

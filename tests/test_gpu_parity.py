@@ -116,19 +116,21 @@ def test_sgemm_ffma_full_size_rows_against_oracle(lib, port, torch):
 
 # ------------------------------------------------------------ SGEMM (3xTF32)
 # Tolerance, stated: per element, with S = |C0| + sum_k |a_ik| |b_kj|,
-#     |C_gpu - C_fp64| <= (1.5e-6 + 1e-6 * K / 1024) * S.
+#     |C_gpu - C_fp64| <= (1.5e-6 + 1e-6 * min(K, 1024) / 1024 + 1e-7 * K / 1024) * S.
 # The constant term: each product carries a relative error of about 2^-21 from
-# the dropped lo*lo term and the TF32 rounding of lo.  The K term: the tensor
+# the dropped lo*lo term and the TF32 rounding of lo.  The second term: the tensor
 # core adds into its fp32 accumulator without round-to-nearest, a bias that grows
-# linearly with the number of accumulation steps (measured: 3.1e-3 absolute at
-# K = 4096 on uniform[-1,1) inputs, where S is about 1024).
+# linearly with the number of accumulation steps (measured before chunking: 3.1e-3
+# absolute at K = 4096 on uniform[-1,1) inputs, where S is about 1024); the kernel
+# therefore drains its accumulator into C every 1024 elements of K, which caps that
+# term.  The last term: one round-to-nearest fp32 add into C per chunk.
 def tf32x3_bound(K):
-    return 1.5e-6 + 1e-6 * K / 1024.0
+    return 1.5e-6 + 1e-6 * min(K, 1024) / 1024.0 + 1e-7 * K / 1024.0
 
 
 @pytest.mark.parametrize("shape", [(128, 256, 32), (256, 512, 1024), (1000, 1000, 1000), (17, 4099, 513),
                                    (4096, 64, 4096), (1, 8192, 2048), (300, 77, 129), (2048, 1000, 999),
-                                   (1030, 2049, 513)])
+                                   (1030, 2049, 513), (512, 512, 8192), (256, 300, 2500)])
 def test_sgemm_3xtf32_within_tolerance(lib, torch, shape):
     M, N, K = shape
     A, B, C0 = cases.sgemm_inputs(M, N, K)
@@ -139,6 +141,7 @@ def test_sgemm_3xtf32_within_tolerance(lib, torch, shape):
     ref = C0.astype(np.float64) + A.astype(np.float64) @ B.astype(np.float64)
     bound = tf32x3_bound(K) * (np.abs(C0).astype(np.float64) + np.abs(A).astype(np.float64) @ np.abs(B).astype(np.float64))
     err = np.abs(C - ref)
+    print(f"3xTF32 {shape}: max err {err.max():.3e}, worst err/bound {(err / (bound + 1e-30)).max():.3f}")
     assert (err <= bound + 1e-30).all(), f"max err {err.max():.3e}, worst ratio {(err / bound).max():.3f}"
 
 
