@@ -83,9 +83,15 @@ template <int MODE>
 __host__ __device__ constexpr int stage_bytes() {
   return Cfg<MODE>::NA * A_TILE_BYTES + Cfg<MODE>::NB * B_TILE_BYTES;
 }
+// 3xTF32 epilogue staging: per epilogue warp a 32-row x 16-column fp32 patch (pitch 20
+// floats) through which the tile's running sums are transposed, so that the final
+// "C += sum" reads and writes C in row-contiguous pieces instead of one row per lane.
+constexpr int EPI_PITCH = 20;
+constexpr int EPI_PATCH_BYTES = 32 * EPI_PITCH * 4;
 template <int MODE>
 __host__ __device__ constexpr int smem_bytes() {
-  return Cfg<MODE>::STAGES * stage_bytes<MODE>() + 1024 /* alignment slack */ + 256 /* barriers */;
+  return Cfg<MODE>::STAGES * stage_bytes<MODE>() + 1024 /* alignment slack */ + 256 /* barriers */ +
+         (MODE == MODE_TF32X3 ? 8 * EPI_PATCH_BYTES : 0);
 }
 
 struct EpiParams {
@@ -410,31 +416,63 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
         if (acc == 0) acc_phase ^= 1u;
       }
       if (!ok) break;
-      if (MODE == MODE_TF32X3 && row < M) {
-        // C += running sum: one read-modify-write per tile, loads issued ahead of the adds
-        float* crow = static_cast<float*>(ep.C) + (int64_t)row * ep.ldc + n0 + half * 128;
-        const int ncols = min(128, N - (n0 + half * 128));
-        if (ep.vec_ok) {
+      if (MODE == MODE_TF32X3) {
+        // C += running sums, once per tile.  A lane owns a row, but reading and writing C
+        // one row per lane (32 rows, a power-of-two pitch apart, per instruction) is an
+        // order of magnitude slower than row-contiguous access, so each 16-column group
+        // is transposed through a shared-memory patch: afterwards one instruction covers
+        // 8 rows x 64 contiguous bytes.
+        float* patch = reinterpret_cast<float*>(ctrl + 256) + (warp - 2) * (EPI_PATCH_BYTES / 4);
+        const int row0 = m0 + q * 32;
+        const int colbase = n0 + half * 128;
 #pragma unroll
-          for (int g = 0; g < 8; g++) {
-            float4 c[4];
+        for (int g = 0; g < 8; g++) {
+          const int col0 = colbase + g * 16;
+          if (col0 >= N) continue;  // warp-uniform
 #pragma unroll
-            for (int v = 0; v < 4; v++)
-              if (g * 16 + v * 4 + 4 <= ncols) c[v] = *reinterpret_cast<const float4*>(crow + g * 16 + v * 4);
+          for (int v = 0; v < 4; v++)
+            *reinterpret_cast<float4*>(patch + lane * EPI_PITCH + v * 4) = make_float4(
+                part[g * 16 + v * 4], part[g * 16 + v * 4 + 1], part[g * 16 + v * 4 + 2], part[g * 16 + v * 4 + 3]);
+          __syncwarp();
+          float4 c[4], p4[4];
+          float* gptr[4];
+          bool okk[4];
 #pragma unroll
-            for (int v = 0; v < 4; v++)
-              if (g * 16 + v * 4 + 4 <= ncols) {
-                c[v].x += part[g * 16 + v * 4 + 0];
-                c[v].y += part[g * 16 + v * 4 + 1];
-                c[v].z += part[g * 16 + v * 4 + 2];
-                c[v].w += part[g * 16 + v * 4 + 3];
-                *reinterpret_cast<float4*>(crow + g * 16 + v * 4) = c[v];
+          for (int it = 0; it < 4; it++) {
+            const int idx = it * 32 + lane;
+            const int r = idx >> 2, c4 = (idx & 3) * 4;
+            p4[it] = *reinterpret_cast<const float4*>(patch + r * EPI_PITCH + c4);
+            gptr[it] = static_cast<float*>(ep.C) + (int64_t)(row0 + r) * ep.ldc + col0 + c4;
+            okk[it] = row0 + r < M && col0 + c4 < N;
+            if (okk[it]) {
+              if (ep.vec_ok) {
+                c[it] = *reinterpret_cast<const float4*>(gptr[it]);
+              } else {
+                c[it].x = gptr[it][0];
+                c[it].y = col0 + c4 + 1 < N ? gptr[it][1] : 0.f;
+                c[it].z = col0 + c4 + 2 < N ? gptr[it][2] : 0.f;
+                c[it].w = col0 + c4 + 3 < N ? gptr[it][3] : 0.f;
               }
+            }
           }
-        } else {
 #pragma unroll
-          for (int j = 0; j < 128; j++)
-            if (j < ncols) crow[j] += part[j];
+          for (int it = 0; it < 4; it++) {
+            if (!okk[it]) continue;
+            const int c4 = ((it * 32 + lane) & 3) * 4;
+            c[it].x += p4[it].x;
+            c[it].y += p4[it].y;
+            c[it].z += p4[it].z;
+            c[it].w += p4[it].w;
+            if (ep.vec_ok) {
+              *reinterpret_cast<float4*>(gptr[it]) = c[it];
+            } else {
+              gptr[it][0] = c[it].x;
+              if (col0 + c4 + 1 < N) gptr[it][1] = c[it].y;
+              if (col0 + c4 + 2 < N) gptr[it][2] = c[it].z;
+              if (col0 + c4 + 3 < N) gptr[it][3] = c[it].w;
+            }
+          }
+          __syncwarp();
         }
       }
     }
