@@ -528,6 +528,7 @@ def run_ours(args):
             line["sweep"] = run_sweep(lib, torch, peaks, args.workload)
             try:
                 line["sgemm_shapes"] = run_shapes(lib, torch, peaks)
+                line["sgemm_aspect_k512"] = run_shapes(lib, torch, peaks, ASPECT_SHAPES, ("ffma",))
             except Exception as e:
                 line["sgemm_shapes"] = {"error": str(e)[:200]}
         if not args.no_cpu:
@@ -572,7 +573,13 @@ SGEMM_SHAPES = [(256, 256, 256), (512, 512, 512), (1024, 1024, 1024), (2048, 204
                 (1000, 1000, 1000), (17, 4099, 513), (4096, 64, 4096), (1, 8192, 8192)]
 
 
-def run_shapes(lib, torch, peaks):
+# the K = 512 aspect-ratio sweep of the reference's SGEMM bench (apps/x86/sgemm/bench_sgemm.cpp:85-97)
+ASPECT_SHAPES = [(32768, 8, 512), (16384, 16, 512), (8192, 32, 512), (4096, 64, 512), (2048, 128, 512),
+                 (1024, 256, 512), (256, 1024, 512), (128, 2048, 512), (64, 4096, 512), (32, 8192, 512),
+                 (16, 16384, 512), (8, 32768, 512)]
+
+
+def run_shapes(lib, torch, peaks, shapes=None, paths=("ffma", "3xtf32")):
     """The SGEMM shape sweep (squares and ragged / skinny shapes) on both fp32
     paths, device time per launch.  Small shapes finish faster than the host can
     launch them, so launches are replayed from a CUDA graph: R x [L2 flush (a
@@ -604,7 +611,7 @@ def run_shapes(lib, torch, peaks):
     flush_ms = replay_ms(lambda: flush.fill_(1))
     out = []
     gen = torch.Generator(device="cuda").manual_seed(3)
-    for (M, N, K) in SGEMM_SHAPES:
+    for (M, N, K) in (shapes or SGEMM_SHAPES):
         A = torch.rand((M, K), generator=gen, device="cuda") * 2 - 1
         B = torch.rand((K, N), generator=gen, device="cuda") * 2 - 1
         C = torch.zeros((M, N), device="cuda")
@@ -612,6 +619,8 @@ def run_shapes(lib, torch, peaks):
         nbytes = 4.0 * (M * K + K * N + 2 * M * N)
         row = {"shape": [M, N, K], "flop_per_byte": flops / nbytes}
         for path, fn in (("ffma", lib.sgemm_exo_ffma), ("3xtf32", lib.sgemm_exo_3xtf32)):
+            if path not in paths:
+                continue
             for _ in range(3):
                 fn(None, M, N, K, A, B, C)  # warm-up: also sizes the scratch before capture
             torch.cuda.synchronize()
