@@ -329,7 +329,14 @@ class Workload:
         self.C = t.empty((n, n), dtype=t.int8, device="cuda")
         self.flops_total = self.flops_local = 2.0 * n ** 3
         self.bound = "tensor"
-        self.launches_per_step = 2  # B transpose pre-pass + the GEMM
+        self.launches_per_step = 1  # B is read MN-major in place: no pre-pass
+
+    def _setup_i8_512(self):
+        self._setup_i8(512)
+        self.launches_per_step = 1
+
+    def step_i8_512(self):
+        self.step_i8()
 
     def step_i8(self):
         n = self.shape[0]
@@ -543,7 +550,7 @@ def run_sweep(lib, torch, peaks, skip):
     out = {}
     sm_count = torch.cuda.get_device_properties(0).multi_processor_count
     simt_peak = sm_count * 128 * 2 * 1.965e9 / 1e12  # fp32 FFMA at max SM clock
-    for name in ("sgemm_ffma", "sgemm_3xtf32", "i8", "conv", "conv_3xtf32", "conv1x1", "conv1x1_3xtf32", "conv_i8",
+    for name in ("sgemm_ffma", "sgemm_3xtf32", "i8", "i8_512", "conv", "conv_3xtf32", "conv1x1", "conv1x1_3xtf32", "conv_i8",
                  "bf16"):
         if name == skip:
             continue
@@ -556,7 +563,7 @@ def run_sweep(lib, torch, peaks, skip):
                 peak, pname = simt_peak, "fp32 SIMT at max SM clock (computed)"
             elif name in ("sgemm_3xtf32", "conv_3xtf32", "conv1x1_3xtf32"):
                 peak, pname = peaks["bf16_tflops"] / 2 / 3, "bf16 measured / 2 (tf32) / 3 (three MMAs per product)"
-            elif name in ("i8", "conv_i8"):
+            elif name in ("i8", "i8_512", "conv_i8"):
                 peak, pname = peaks["bf16_tflops"] * 2, "2 x bf16 measured (nominal int8 ratio)"
             else:
                 peak, pname = peaks["bf16_tflops"], "bf16 measured"
