@@ -19,6 +19,13 @@ def _free_port():
 
 
 def _rank(rank, world, port, M, N, K, q):
+    try:
+        _rank_body(rank, world, port, M, N, K, q)
+    except Exception as e:  # report instead of leaving the parent to time out
+        q.put(f"rank {rank}: {type(e).__name__}: {e}")
+
+
+def _rank_body(rank, world, port, M, N, K, q):
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     import torch
@@ -37,15 +44,16 @@ def _rank(rank, world, port, M, N, K, q):
     c = torch.empty((sg.block.rows, N), dtype=torch.int16, device="cuda")
     sg.step(sg.local_rows(A).contiguous(), B, c)
     torch.cuda.synchronize()
-    parts = [torch.empty((b.rows, N), dtype=torch.int16, device="cuda") for b in sg.blocks]
-    dist.all_gather(parts, c) if len({b.rows for b in sg.blocks}) == 1 else None
+    # NCCL has no int16: gather the raw bytes
+    parts = [torch.empty((b.rows, N * 2), dtype=torch.uint8, device="cuda") for b in sg.blocks]
+    dist.all_gather(parts, c.view(torch.uint8))
     if rank == 0:
         import exo_b200
 
         full = torch.empty((M, N), dtype=torch.int16, device="cuda")
         exo_b200.library().gemm_bf16_exo(None, M, N, K, A, B, full)
         torch.cuda.synchronize()
-        q.put(bool(torch.equal(torch.cat(parts, 0), full)))
+        q.put(bool(torch.equal(torch.cat(parts, 0), full.view(torch.uint8))))
     dist.barrier()
     dist.destroy_process_group()
 
@@ -64,8 +72,9 @@ def test_sharded_bf16_gemm_is_bitwise_equal_to_one_gpu():
     procs = [ctx.Process(target=_rank, args=(r, world, port, M, N, K, q)) for r in range(world)]
     for p in procs:
         p.start()
-    ok = q.get(timeout=300)
+    ok = q.get(timeout=150)
     for p in procs:
-        p.join(timeout=120)
-        assert p.exitcode == 0
-    assert ok
+        p.join(timeout=30)
+        if p.is_alive():
+            p.kill()
+    assert ok is True, ok
