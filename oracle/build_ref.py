@@ -46,7 +46,10 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT = os.path.join(HERE, "_ref")
-DEFAULT_REFERENCE = os.environ.get("EXO_REFERENCE", "/root/reference")
+# Where the exo-lang/exo checkout lives: $EXO_REFERENCE, else a "reference" directory
+# beside this repository.
+DEFAULT_REFERENCE = os.environ.get(
+    "EXO_REFERENCE", os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference"))
 
 SPLIT_MARK = '#include "test_case.h"'
 
