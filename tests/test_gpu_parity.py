@@ -469,3 +469,38 @@ def test_host_pointer_pipeline_matches_device_pointer_path(lib, torch):
     lib.matmul_on_cpu(None, n, m, k, 1.0 / 128, True, dev(torch, A8), dev(torch, B8), dC8)
     torch.cuda.synchronize()
     assert np.array_equal(C8, dC8.cpu().numpy())
+
+
+def test_unaligned_device_pointers(lib, port, torch):
+    """Operands that start at an odd offset inside an allocation (4 bytes for fp32, 1 byte
+    for int8) must take the scalar / SIMT paths and still match the oracle bit for bit."""
+    M, N, K = 130, 260, 96
+    A, B, C0 = cases.sgemm_inputs(M, N, K, seed=77)
+
+    def shifted(a, dtype):
+        flat = torch.empty(a.size + 1, dtype=dtype, device="cuda")
+        view = flat[1:].view(a.shape)
+        view.copy_(torch.from_numpy(a))
+        assert view.data_ptr() % 16 != 0
+        return view
+
+    dA, dB, dC = shifted(A, torch.float32), shifted(B, torch.float32), shifted(C0, torch.float32)
+    lib.sgemm_exo(None, M, N, K, dA, dB, dC)
+    torch.cuda.synchronize()
+    want = port.sgemm(A, B, C0.copy())
+    assert np.array_equal(bits(dC.cpu().numpy()), bits(want))
+    # 3xTF32 repacks its operands, so alignment does not matter there either
+    dC2 = shifted(C0, torch.float32)
+    lib.sgemm_exo_3xtf32(None, M, N, K, dA, dB, dC2)
+    torch.cuda.synchronize()
+    ref = C0.astype(np.float64) + A.astype(np.float64) @ B.astype(np.float64)
+    bound = tf32x3_bound(K) * (np.abs(C0) + np.abs(A).astype(np.float64) @ np.abs(B).astype(np.float64))
+    assert (np.abs(dC2.cpu().numpy() - ref) <= bound).all()
+    # int8
+    n, m, k = 130, 256, 128
+    A8, B8 = inputs.int8(5, (n, k), -20, 20), inputs.int8(6, (k, m), -20, 20)
+    dA8, dB8 = shifted(A8, torch.int8), shifted(B8, torch.int8)
+    dC8 = torch.empty(n * m + 1, dtype=torch.int8, device="cuda")[1:].view(n, m)
+    lib.matmul_on_cpu(None, n, m, k, 1.0 / 32, True, dA8, dB8, dC8)
+    torch.cuda.synchronize()
+    assert np.array_equal(dC8.cpu().numpy(), port.matmul_i8(A8, B8, 1.0 / 32, True))
