@@ -376,8 +376,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
 #pragma unroll
         for (int j = 0; j < 128; j++) part[j] = 0.f;
       }
-      // one pass per K chunk (a single pass except for 3xTF32, whose passes each add a
-      // partial sum to C; the same thread owns the same elements in every pass)
+      // one pass per K chunk: a single pass that writes C, except for 3xTF32, whose passes
+      // each add the chunk's partial sums to per-thread running sums (same thread, same
+      // elements in every pass) that are added to C once, after the last chunk
       for (int kb0 = 0; kb0 < num_kb; kb0 += chunk_kb) {
         if (!mbar_wait_warp(tfull_bar(acc), acc_phase, abort_flag, WAIT_LIMIT_NS)) {
           if (lane == 0) report_timeout(status, abort_flag, 4);
