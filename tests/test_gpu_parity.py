@@ -504,3 +504,32 @@ def test_unaligned_device_pointers(lib, port, torch):
     lib.matmul_on_cpu(None, n, m, k, 1.0 / 32, True, dA8, dB8, dC8)
     torch.cuda.synchronize()
     assert np.array_equal(dC8.cpu().numpy(), port.matmul_i8(A8, B8, 1.0 / 32, True))
+
+
+def test_explicit_context_stream_and_path(lib, port, torch):
+    """ctxt != NULL: an exo_b200_Context carrying its own stream and SGEMM path."""
+    import exo_b200
+
+    M, N, K = 512, 384, 1024
+    A, B, C0 = cases.sgemm_inputs(M, N, K, seed=88)
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        dA, dB, dC = dev(torch, A), dev(torch, B), dev(torch, C0)
+        ctx = exo_b200.Context(stream=side.cuda_stream)  # default path: exact FFMA
+        lib.sgemm_exo(ctx, M, N, K, dA, dB, dC)
+        lib.synchronize(ctx)
+        assert np.array_equal(bits(dC.cpu().numpy()), bits(port.sgemm(A, B, C0.copy())))
+        # same context switched to the tensor path: within the 3xTF32 bound, and not the exact bits
+        lib.dll.exo_b200_context_set_sgemm_path(ctx.handle, exo_b200.SGEMM_3XTF32)
+        dC2 = dev(torch, C0)
+        lib.sgemm_exo(ctx, M, N, K, dA, dB, dC2)
+        lib.synchronize(ctx)
+        ref = C0.astype(np.float64) + A.astype(np.float64) @ B.astype(np.float64)
+        bound = tf32x3_bound(K) * (np.abs(C0) + np.abs(A).astype(np.float64) @ np.abs(B).astype(np.float64))
+        got = dC2.cpu().numpy()
+        assert (np.abs(got - ref) <= bound).all()
+        ctx.close()
+    # a pointer that is not a context is rejected, not dereferenced as one
+    junk = np.zeros(64, np.uint8)
+    lib.dll.sgemm_exo(junk.ctypes.data, M, N, K, A.ctypes.data, B.ctypes.data, C0.ctypes.data)
+    assert lib.dll.exo_b200_last_error() == exo_b200.ERR_INVALID_ARGUMENT
