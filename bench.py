@@ -381,6 +381,18 @@ class Workload:
         b, h, w, ci, co, k, pad = self.cv
         self.lib.conv_nhwc_exo_3xtf32(None, b, h, w, ci, co, k, pad, True, self.A, self.C, self.B, self.bias)
 
+    # -- the reference's own instance (apps/x86/conv/conv.py:49,55): batch 5, 82x102 -> 80x100, 128 -> 128, 3x3
+    def _setup_conv_ref(self):
+        self._setup_conv(cv=(5, 82, 102, 128, 128, 3, 0))
+
+    step_conv_ref = step_conv
+
+    def _setup_conv_ref_3xtf32(self):
+        self._setup_conv(cv=(5, 82, 102, 128, 128, 3, 0))
+        self.launches_per_step = 3
+
+    step_conv_ref_3xtf32 = step_conv_3xtf32
+
     # -- the 1x1 conv: batch 8, 28x28, 256 -> 512 (exact FFMA and 3xTF32)
     def _setup_conv1x1(self):
         self._setup_conv(cv=(8, 28, 28, 256, 512, 1, 0))
@@ -550,8 +562,8 @@ def run_sweep(lib, torch, peaks, skip):
     out = {}
     sm_count = torch.cuda.get_device_properties(0).multi_processor_count
     simt_peak = sm_count * 128 * 2 * 1.965e9 / 1e12  # fp32 FFMA at max SM clock
-    for name in ("sgemm_ffma", "sgemm_3xtf32", "i8", "i8_512", "conv", "conv_3xtf32", "conv1x1", "conv1x1_3xtf32", "conv_i8",
-                 "bf16"):
+    for name in ("sgemm_ffma", "sgemm_3xtf32", "i8", "i8_512", "conv", "conv_3xtf32", "conv1x1", "conv1x1_3xtf32", "conv_ref", "conv_ref_3xtf32",
+                 "conv_i8", "bf16"):
         if name == skip:
             continue
         try:
@@ -559,9 +571,9 @@ def run_sweep(lib, torch, peaks, skip):
             ms, _, _ = time_steps(torch, wl.step, 5 if wl.flops_total > 1e12 else 50, 3)
             lib.synchronize()
             tf = wl.flops_total / (ms / 1e3) / 1e12
-            if name in ("sgemm_ffma", "conv", "conv1x1"):
+            if name in ("sgemm_ffma", "conv", "conv1x1", "conv_ref"):
                 peak, pname = simt_peak, "fp32 SIMT at max SM clock (computed)"
-            elif name in ("sgemm_3xtf32", "conv_3xtf32", "conv1x1_3xtf32"):
+            elif name in ("sgemm_3xtf32", "conv_3xtf32", "conv1x1_3xtf32", "conv_ref_3xtf32"):
                 peak, pname = peaks["bf16_tflops"] / 2 / 3, "bf16 measured / 2 (tf32) / 3 (three MMAs per product)"
             elif name in ("i8", "i8_512", "conv_i8"):
                 peak, pname = peaks["bf16_tflops"] * 2, "2 x bf16 measured (nominal int8 ratio)"
