@@ -526,6 +526,7 @@ def run_ours(args):
         traffic = 14.43e9 * wl.shape[0] / BF16_SHAPE[0]
     roofline = {"bound": "tensor", "achieved": per_launch_tflops, "peak": peak, "unit": "TFLOP/s",
                 "frac": per_launch_tflops / peak, "traffic": traffic,
+                "frac_of_sustained_peak": per_launch_tflops / peaks.get("bf16_tflops_sustained", peak),
                 "peak_source": f"{peaks['source']} bf16 burst (sustained: {peaks.get('bf16_tflops_sustained')})",
                 "kernel": "gemm_tc2_kernel<bf16>" if args.workload == "bf16" else args.workload}
     line = {
