@@ -520,10 +520,10 @@ def run_ours(args):
     peak = peaks["bf16_tflops"]
     per_launch_tflops = wl.flops_local / (ms / 1e3) / 1e12
     # DRAM bytes per launch of the headline shape from a one-pass ncu capture of one full-size
-    # launch (13.36 GB read + 1.07 GB written); scaled by the rows a rank owns
+    # launch (10.91 GB read + 1.07 GB written); scaled by the rows a rank owns
     traffic = None
     if args.workload == "bf16" and shape is None:
-        traffic = 14.43e9 * wl.shape[0] / BF16_SHAPE[0]
+        traffic = 11.98e9 * wl.shape[0] / BF16_SHAPE[0]
     roofline = {"bound": "tensor", "achieved": per_launch_tflops, "peak": peak, "unit": "TFLOP/s",
                 "frac": per_launch_tflops / peak, "traffic": traffic,
                 "frac_of_sustained_peak": per_launch_tflops / peaks.get("bf16_tflops_sustained", peak),

@@ -210,7 +210,8 @@ __device__ __forceinline__ void store_chunk2(const Epi2& ep, const uint32_t (&r)
 template <int MODE>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, int M, int N, int K,
-                Epi2 ep, DeviceStatus* status, int tiles_m, int tiles_n, int GM, int use_hints) {
+                Epi2 ep, DeviceStatus* status, int tiles_m, int tiles_n, int GM, int use_hints, int stages,
+                int plain_leader) {
   using C = Cfg2<MODE>;
   constexpr int BK = ROW_BYTES / C::ELEM;
   constexpr uint32_t IDESC =
@@ -310,6 +311,13 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
               tma_load_2d_pair_hint(dst + A_TILE_BYTES, &tmB, bar0, n0, k0, stream_through);
             else
               tma_load_2d_pair_hint(dst + A_TILE_BYTES, &tmB, bar0, k0, n0, stream_through);
+          } else if (plain_leader && rank == 0) {
+            // experiment: the even CTA's own loads as ordinary (single-CTA) TMA loads
+            tma_load_2d(dst, &tmA, full_bar(stage), k0, m0);
+            if (C::BMN)
+              tma_load_2d(dst + A_TILE_BYTES, &tmB, full_bar(stage), n0, k0);
+            else
+              tma_load_2d(dst + A_TILE_BYTES, &tmB, full_bar(stage), k0, n0);
           } else {
             tma_load_2d_pair(dst, &tmA, bar0, k0, m0);
             if (C::BMN)
@@ -317,7 +325,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             else
               tma_load_2d_pair(dst + A_TILE_BYTES, &tmB, bar0, k0, n0);
           }
-          if (++stage == STAGES2) {
+          if (++stage == stages) {
             stage = 0;
             phase ^= 1u;
           }
@@ -363,7 +371,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           for (int ks = 0; ks < KSTEPS; ks++)
             tc_mma_pair<C::KIND>(d, da + (uint64_t)(ks * 2), db + ks * B_ADV, IDESC, (kb | ks) != 0);
           tc_commit_pair(empty_bar(stage));
-          if (++stage == STAGES2) {
+          if (++stage == stages) {
             stage = 0;
             phase ^= 1u;
           }
@@ -454,8 +462,22 @@ cudaError_t launch_tc2(exo_b200_Context* ctx, const CUtensorMap& ma, const CUten
     const char* e = getenv("EXOB200_TC2_HINT");
     return e ? atoi(e) : 0;
   }();
+  // Ring depth actually used (the shared-memory layout always has room for STAGES2).
+  // Measured on the 32768 x 16384 x 8192 bf16 problem: 6 stages let the pairs drift so
+  // far apart in K that L2 sharing drops (13.0 GB of DRAM reads per launch), 4 stages
+  // read 8.2 GB, 3 stages starve the tensor pipe; 5 is the fastest both cold and under
+  // the power cap.  EXOB200_TC2_STAGES overrides it.
+  static const int stages = [] {
+    const char* e = getenv("EXOB200_TC2_STAGES");
+    const int n = e ? atoi(e) : 5;
+    return n >= 2 && n <= STAGES2 ? n : 5;
+  }();
+  static const int plain_leader = [] {
+    const char* e = getenv("EXOB200_TC2_PLAIN");
+    return e ? atoi(e) : 0;
+  }();
   return cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<MODE>, ma, mb, (int)M, (int)N, (int)K, ep, ctx->status_dev,
-                            (int)tiles_m, (int)tiles_n, gm, hints);
+                            (int)tiles_m, (int)tiles_n, gm, hints, stages, plain_leader);
 }
 
 }  // namespace
