@@ -533,3 +533,24 @@ def test_explicit_context_stream_and_path(lib, port, torch):
     junk = np.zeros(64, np.uint8)
     lib.dll.sgemm_exo(junk.ctypes.data, M, N, K, A.ctypes.data, B.ctypes.data, C0.ctypes.data)
     assert lib.dll.exo_b200_last_error() == exo_b200.ERR_INVALID_ARGUMENT
+
+
+def test_conv_reference_layout_on_tensor_path(lib, port, torch):
+    """conv (weights [Ci, Kh, Kw, Co], the x86 app's layout) with the context switched to
+    3xTF32: the weight pre-pass has to reorder K to (ky, kx, ci) from either layout."""
+    import exo_b200
+
+    inp = inputs.uniform_f32(401, (2, 20, 22, 32))
+    wts = inputs.uniform_f32(402, (32, 3, 3, 48))  # [Ci, Kh, Kw, Co]
+    bias = inputs.uniform_f32(403, (48,))
+    ctx = exo_b200.Context(sgemm_path=exo_b200.SGEMM_3XTF32)
+    out = torch.empty((2, 18, 20, 48), dtype=torch.float32, device="cuda")
+    lib.conv(ctx, 18, 20, 48, 20, 22, 32, 3, 2, dev(torch, inp), out, dev(torch, wts), dev(torch, bias))
+    lib.synchronize(ctx)
+    want = port.conv(inp, wts, bias)
+    S = port.conv_nhwc(np.abs(inp), np.ascontiguousarray(np.abs(wts).transpose(1, 2, 0, 3)), np.abs(bias), 0, False)
+    err = np.abs(out.cpu().numpy().astype(np.float64) - want.astype(np.float64))
+    bound = (tf32x3_bound(9 * 32) + 2e-7) * S.astype(np.float64)
+    assert (err <= bound).all(), f"max err {err.max():.3e}, worst ratio {(err / bound).max():.3f}"
+    assert err.max() > 0  # it really took the tensor path (the FFMA path would be bit-exact)
+    ctx.close()
