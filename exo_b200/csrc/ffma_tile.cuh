@@ -31,11 +31,14 @@ namespace exob200 {
 namespace ffma {
 
 constexpr int BK = 16;
-constexpr int THREADS = 256;
-// Two tile sizes from one engine: H = 2 -> 128 x 128 (8 x 8 per thread), the
-// throughput configuration; H = 1 -> 64 x 64 (4 x 4 per thread) for problems with
-// too few 128 x 128 tiles to occupy the machine (without split-K, which the
-// reference's per-element chain order rules out, parallelism only comes from M x N).
+// Three tile sizes from one engine (TD x TD threads, each 4H x 4H outputs):
+//   TD = 16, H = 2 -> 128 x 128, 256 threads, 8 x 8 per thread: the throughput configuration;
+//   TD = 16, H = 1 ->  64 x  64, 256 threads, 4 x 4 per thread: too few 128 x 128 tiles for the machine;
+//   TD =  8, H = 1 ->  32 x  32,  64 threads, 4 x 4 per thread: too few 64 x 64 tiles.  Such problems are
+//     bound by the latency of one warp's k loop, so spreading the same warps over more SMs (one or two
+//     per scheduler instead of four) is what shortens them.
+// Without split-K, which the reference's per-element chain order rules out, parallelism only comes
+// from M x N.
 
 __device__ __forceinline__ float4 ldg4(const float* p) {
   return __ldg(reinterpret_cast<const float4*>(p));
@@ -73,9 +76,11 @@ __device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
   return d;
 }
 
-template <class Policy, bool PACKED, int H>
-__global__ void __launch_bounds__(THREADS, 2) tile_kernel(const Policy P, int tiles_m, int tiles_n) {
-  constexpr int BM = 64 * H, BN = 64 * H;
+template <class Policy, bool PACKED, int H, int TD>
+__global__ void __launch_bounds__(TD * TD, TD == 16 ? 2 : 8) tile_kernel(const Policy P, int tiles_m, int tiles_n) {
+  constexpr int THREADS = TD * TD;
+  constexpr int QS = 4 * TD;  // rows (columns) per quadrant
+  constexpr int BM = QS * H, BN = QS * H;
   constexpr int AS_PITCH = BM + 4;  // floats; keeps 16-byte alignment, spreads the transposing stores
   constexpr int R = 4 * H;          // rows (and columns) per thread
   __shared__ __align__(16) float As[2][BK][AS_PITCH];
@@ -97,35 +102,37 @@ __global__ void __launch_bounds__(THREADS, 2) tile_kernel(const Policy P, int ti
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
-  const int ty = (warp >> 1) * 4 + (lane >> 3);  // 0..15
-  const int tx = (warp & 1) * 8 + (lane & 7);    // 0..15
+  constexpr int WX = TD / 8;                       // warps side by side
+  const int ty = (warp / WX) * 4 + (lane >> 3);  // 0..TD-1
+  const int tx = (warp % WX) * 8 + (lane & 7);   // 0..TD-1
 
   // global -> register staging coordinates
-  // A tile: BM rows x 16 k.  thread -> rows tid/4 (+ 64), k quad (tid%4)*4
+  // A tile: BM rows x 16 k.  thread -> rows tid/4 (+ THREADS/4 per pass), k quad (tid%4)*4
   const int a_row = tid >> 2, a_kq = (tid & 3) * 4;
-  // B tile: 16 k x BN cols = 256 H column quads, H per thread
-  constexpr int QPR = 16 * H;  // quads per k row
+  constexpr int A_RSTEP = THREADS / 4, PA = BM / A_RSTEP;  // passes over the A tile
+  // B tile: 16 k x BN cols = 16 * BN/4 column quads, PB per thread
+  constexpr int QPR = BN / 4;  // quads per k row
   const int b_k = tid / QPR, b_c4 = (tid % QPR) * 4;
-  constexpr int B_KSTEP = THREADS / QPR;  // k rows covered per pass
+  constexpr int B_KSTEP = THREADS / QPR, PB = BK / B_KSTEP;  // k rows covered per pass, passes
 
-  typename Policy::RowCtx rc[H];
+  typename Policy::RowCtx rc[PA];
 #pragma unroll
-  for (int h = 0; h < H; h++) rc[h] = P.row_ctx(m0 + a_row + h * 64);
+  for (int h = 0; h < PA; h++) rc[h] = P.row_ctx(m0 + a_row + h * A_RSTEP);
 
   // A goes through registers (it is transposed on the way into shared memory);
   // B is copied global -> shared asynchronously, 16 bytes (or 4 x 4) per thread.
-  float4 pa[H];
+  float4 pa[PA];
   auto load_tile = [&](int k0, int buf) {
 #pragma unroll
-    for (int h = 0; h < H; h++) pa[h] = P.load_a(rc[h], m0 + a_row + h * 64, k0 + a_kq);
+    for (int h = 0; h < PA; h++) pa[h] = P.load_a(rc[h], m0 + a_row + h * A_RSTEP, k0 + a_kq);
 #pragma unroll
-    for (int h = 0; h < H; h++)
+    for (int h = 0; h < PB; h++)
       P.copy_b(&Bs[buf][b_k + h * B_KSTEP][b_c4], k0 + b_k + h * B_KSTEP, n0 + b_c4);
   };
   auto store_tile = [&](int buf) {
 #pragma unroll
-    for (int h = 0; h < H; h++) {
-      const int r = a_row + h * 64;
+    for (int h = 0; h < PA; h++) {
+      const int r = a_row + h * A_RSTEP;
       As[buf][a_kq + 0][r] = pa[h].x;
       As[buf][a_kq + 1][r] = pa[h].y;
       As[buf][a_kq + 2][r] = pa[h].z;
@@ -139,10 +146,10 @@ __global__ void __launch_bounds__(THREADS, 2) tile_kernel(const Policy P, int ti
   uint64_t acc2[PACKED ? R : 1][PACKED ? R / 2 : 1];  // [row][column pair]
 #pragma unroll
   for (int i = 0; i < R; i++) {
-    const int row = m0 + (i >> 2) * 64 + ty * 4 + (i & 3);
+    const int row = m0 + (i >> 2) * QS + ty * 4 + (i & 3);
 #pragma unroll
     for (int jq = 0; jq < H; jq++) {
-      const float4 v = P.init(row, n0 + jq * 64 + tx * 4);
+      const float4 v = P.init(row, n0 + jq * QS + tx * 4);
       if (PACKED) {
         acc2[i][jq * 2 + 0] = pack2(v.x, v.y);
         acc2[i][jq * 2 + 1] = pack2(v.z, v.w);
@@ -169,7 +176,7 @@ __global__ void __launch_bounds__(THREADS, 2) tile_kernel(const Policy P, int ti
       float a[R];
 #pragma unroll
       for (int h = 0; h < H; h++) {
-        const float4 av = *reinterpret_cast<const float4*>(&As[buf][kk][h * 64 + ty * 4]);
+        const float4 av = *reinterpret_cast<const float4*>(&As[buf][kk][h * QS + ty * 4]);
         a[h * 4 + 0] = av.x;
         a[h * 4 + 1] = av.y;
         a[h * 4 + 2] = av.z;
@@ -179,7 +186,7 @@ __global__ void __launch_bounds__(THREADS, 2) tile_kernel(const Policy P, int ti
         uint64_t b[R / 2];
 #pragma unroll
         for (int h = 0; h < H; h++) {
-          const ulonglong2 bv = *reinterpret_cast<const ulonglong2*>(&Bs[buf][kk][h * 64 + tx * 4]);
+          const ulonglong2 bv = *reinterpret_cast<const ulonglong2*>(&Bs[buf][kk][h * QS + tx * 4]);
           b[h * 2 + 0] = bv.x;
           b[h * 2 + 1] = bv.y;
         }
@@ -193,7 +200,7 @@ __global__ void __launch_bounds__(THREADS, 2) tile_kernel(const Policy P, int ti
         float b[R];
 #pragma unroll
         for (int h = 0; h < H; h++) {
-          const float4 bv = *reinterpret_cast<const float4*>(&Bs[buf][kk][h * 64 + tx * 4]);
+          const float4 bv = *reinterpret_cast<const float4*>(&Bs[buf][kk][h * QS + tx * 4]);
           b[h * 4 + 0] = bv.x;
           b[h * 4 + 1] = bv.y;
           b[h * 4 + 2] = bv.z;
@@ -218,7 +225,7 @@ __global__ void __launch_bounds__(THREADS, 2) tile_kernel(const Policy P, int ti
 
 #pragma unroll
   for (int i = 0; i < R; i++) {
-    const int row = m0 + (i >> 2) * 64 + ty * 4 + (i & 3);
+    const int row = m0 + (i >> 2) * QS + ty * 4 + (i & 3);
 #pragma unroll
     for (int jq = 0; jq < H; jq++) {
       float4 v;
@@ -228,7 +235,7 @@ __global__ void __launch_bounds__(THREADS, 2) tile_kernel(const Policy P, int ti
       } else {
         v = make_float4(acc[i][jq * 4], acc[i][jq * 4 + 1], acc[i][jq * 4 + 2], acc[i][jq * 4 + 3]);
       }
-      P.store(row, n0 + jq * 64 + tx * 4, v);
+      P.store(row, n0 + jq * QS + tx * 4, v);
     }
   }
 }
@@ -242,29 +249,36 @@ inline bool use_packed() {
   return packed;
 }
 
-template <class Policy, int H>
+template <class Policy, int H, int TD>
 cudaError_t launch_tiles_h(cudaStream_t stream, const Policy& P) {
-  constexpr int T = 64 * H;
+  constexpr int T = 4 * TD * H;
   const int64_t tiles_m = (P.M + T - 1) / T, tiles_n = (P.N + T - 1) / T;
   if (tiles_m * tiles_n > INT32_MAX) return cudaErrorInvalidValue;
   const unsigned grid = (unsigned)(tiles_m * tiles_n);
   if (use_packed())
-    tile_kernel<Policy, true, H><<<grid, THREADS, 0, stream>>>(P, (int)tiles_m, (int)tiles_n);
+    tile_kernel<Policy, true, H, TD><<<grid, TD * TD, 0, stream>>>(P, (int)tiles_m, (int)tiles_n);
   else
-    tile_kernel<Policy, false, H><<<grid, THREADS, 0, stream>>>(P, (int)tiles_m, (int)tiles_n);
+    tile_kernel<Policy, false, H, TD><<<grid, TD * TD, 0, stream>>>(P, (int)tiles_m, (int)tiles_n);
   return cudaGetLastError();
 }
 
-// 128 x 128 tiles unless they would leave most SMs without work.
+// 128 x 128 tiles unless they would leave most SMs without work; 32 x 32 when even
+// 64 x 64 tiles would.
 template <class Policy>
 cudaError_t launch_tiles(cudaStream_t stream, const Policy& P) {
   const int64_t big_tiles = ((int64_t)(P.M + 127) / 128) * ((P.N + 127) / 128);
+  const int64_t mid_tiles = ((int64_t)(P.M + 63) / 64) * ((P.N + 63) / 64);
   static const int force = [] {
-    const char* e = getenv("EXOB200_FFMA_TILE");  // 64 or 128 forces a tile size (timing experiments)
+    const char* e = getenv("EXOB200_FFMA_TILE");  // 32, 64 or 128 forces a tile size (timing experiments)
     return e ? atoi(e) : 0;
   }();
-  const bool small = force == 64 || (force != 128 && big_tiles <= 148);
-  return small ? launch_tiles_h<Policy, 1>(stream, P) : launch_tiles_h<Policy, 2>(stream, P);
+  const int tile = force == 32 || force == 64 || force == 128 ? force
+                   : big_tiles > 148                         ? 128
+                   : mid_tiles > 148                         ? 64
+                                                             : 32;
+  if (tile == 128) return launch_tiles_h<Policy, 2, 16>(stream, P);
+  if (tile == 64) return launch_tiles_h<Policy, 1, 16>(stream, P);
+  return launch_tiles_h<Policy, 1, 8>(stream, P);
 }
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }

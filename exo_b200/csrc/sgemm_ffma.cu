@@ -425,6 +425,141 @@ sgemm_gemv_tma_kernel(const __grid_constant__ CUtensorMap tmB, int N, int K, con
   }
 }
 
+// --------------------------------------------------------------------------
+// Tall kernel (N <= 16, many rows): the mirror image of the skinny kernel.  A is
+// streamed exactly once; a thread owns one row of C (all N columns, N <= 16
+// accumulators), so the chain order is unchanged.  A CTA takes ROWS = 128 rows; the K chunk of A (ROWS x 32 k, row
+// pitch 36 floats so that a quarter-warp's 128-bit reads are conflict free) and of B
+// (32 k x 32 columns) flow through a cp.async ring.
+constexpr int TL_KS = 32, TL_STAGES = 5, TL_PITCH = 36;
+template <int ROWS>
+__host__ __device__ constexpr int tl_stage_floats() { return ROWS * TL_PITCH + TL_KS * 32; }
+template <int ROWS>
+__host__ __device__ constexpr int tl_smem() { return TL_STAGES * tl_stage_floats<ROWS>() * (int)sizeof(float); }  // 110 KiB / 42.5 KiB
+
+template <int NQ, int ROWS>  // NQ = ceil(N / 4): column quads per row, 1..4
+__global__ void __launch_bounds__(ROWS)
+sgemm_tall_kernel(int M, int N, int K, const float* __restrict__ A, const float* __restrict__ B,
+                  float* __restrict__ C, int a_vec, int b_vec) {
+  extern __shared__ __align__(16) float tl_smem_buf[];
+  constexpr int STAGE = tl_stage_floats<ROWS>();
+  const int tid = threadIdx.x;
+  const int m0 = blockIdx.x * ROWS;
+  const int row = m0 + tid;
+
+  uint64_t acc2[NQ][2];
+#pragma unroll
+  for (int q = 0; q < NQ; q++) {
+    float v[4];
+#pragma unroll
+    for (int j = 0; j < 4; j++) v[j] = (row < M && q * 4 + j < N) ? C[(int64_t)row * N + q * 4 + j] : 0.f;
+    acc2[q][0] = ffma::pack2(v[0], v[1]);
+    acc2[q][1] = ffma::pack2(v[2], v[3]);
+  }
+
+  const int nstages = (K + TL_KS - 1) / TL_KS;
+  auto issue = [&](int st) {
+    if (st < nstages) {
+      float* as = tl_smem_buf + (st % TL_STAGES) * STAGE;
+      float* bs = as + ROWS * TL_PITCH;
+      const int k0 = st * TL_KS;
+      // A: ROWS rows x 8 k-quads, 8 quads per thread; 8 consecutive threads cover one row segment
+#pragma unroll
+      for (int i = 0; i < 8; i++) {
+        const int e = tid + i * ROWS;
+        const int r = e >> 3, kq = (e & 7) * 4;
+        const bool rin = m0 + r < M;
+        const float* src = A + (rin ? (int64_t)(m0 + r) * K : 0);
+        if (a_vec) {
+          const bool ok = rin && k0 + kq < K;  // K % 4 == 0
+          ffma::cp_async16(as + r * TL_PITCH + kq, src + (ok ? k0 + kq : 0), ok);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 4; j++) {
+            const bool ok = rin && k0 + kq + j < K;
+            ffma::cp_async4(as + r * TL_PITCH + kq + j, src + (ok ? k0 + kq + j : 0), ok);
+          }
+        }
+      }
+      // B: 32 k x 32 columns (zero beyond N)
+      if (b_vec) {  // N % 4 == 0
+        for (int e = tid; e < TL_KS * 8; e += ROWS) {
+          const int kk = e >> 3, c = (e & 7) * 4;
+          const bool ok = k0 + kk < K && c < N;
+          ffma::cp_async16(bs + kk * 32 + c, B + (ok ? (int64_t)(k0 + kk) * N + c : 0), ok);
+        }
+      } else {
+        for (int e = tid; e < TL_KS * 32; e += ROWS) {
+          const int kk = e >> 5, c = e & 31;
+          const bool ok = k0 + kk < K && c < N;
+          ffma::cp_async4(bs + kk * 32 + c, B + (ok ? (int64_t)(k0 + kk) * N + c : 0), ok);
+        }
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+
+  for (int st = 0; st < TL_STAGES - 1; st++) issue(st);
+  for (int st = 0; st < nstages; st++) {
+    asm volatile("cp.async.wait_group %0;" ::"n"(TL_STAGES - 2) : "memory");
+    __syncthreads();
+    issue(st + TL_STAGES - 1);
+    const float* as = tl_smem_buf + (st % TL_STAGES) * STAGE + tid * TL_PITCH;
+    const float* bs = tl_smem_buf + (st % TL_STAGES) * STAGE + ROWS * TL_PITCH;
+    const int kmax = min(TL_KS, K - st * TL_KS);
+    auto step = [&](float a, int kk) {
+      const uint64_t aa = ffma::pack2(a, a);
+#pragma unroll
+      for (int q = 0; q < NQ; q++) {
+        const ulonglong2 bv = *reinterpret_cast<const ulonglong2*>(bs + kk * 32 + q * 4);
+        acc2[q][0] = ffma::fma2(aa, bv.x, acc2[q][0]);
+        acc2[q][1] = ffma::fma2(aa, bv.y, acc2[q][1]);
+      }
+    };
+    if (kmax == TL_KS) {
+#pragma unroll
+      for (int k4 = 0; k4 < TL_KS; k4 += 4) {
+        const float4 av = *reinterpret_cast<const float4*>(as + k4);
+        step(av.x, k4 + 0);
+        step(av.y, k4 + 1);
+        step(av.z, k4 + 2);
+        step(av.w, k4 + 3);
+      }
+    } else {
+      for (int kk = 0; kk < kmax; kk++) step(as[kk], kk);  // ragged K tail: no padded steps
+    }
+  }
+  if (row < M) {
+#pragma unroll
+    for (int q = 0; q < NQ; q++) {
+      float v[4];
+      ffma::unpack2(acc2[q][0], v[0], v[1]);
+      ffma::unpack2(acc2[q][1], v[2], v[3]);
+#pragma unroll
+      for (int j = 0; j < 4; j++)
+        if (q * 4 + j < N) C[(int64_t)row * N + q * 4 + j] = v[j];
+    }
+  }
+}
+
+template <int NQ, int ROWS>
+cudaError_t launch_tall_r(cudaStream_t stream, int M, int N, int K, const float* A, const float* B, float* C,
+                          int a_vec, int b_vec) {
+  cudaError_t e = cudaFuncSetAttribute(sgemm_tall_kernel<NQ, ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       tl_smem<ROWS>());
+  if (e != cudaSuccess) return e;
+  sgemm_tall_kernel<NQ, ROWS><<<(unsigned)((M + ROWS - 1) / ROWS), ROWS, tl_smem<ROWS>(), stream>>>(M, N, K, A, B, C,
+                                                                                                   a_vec, b_vec);
+  return cudaGetLastError();
+}
+
+template <int NQ>
+cudaError_t launch_tall(cudaStream_t stream, int M, int N, int K, const float* A, const float* B, float* C, int a_vec,
+                        int b_vec) {
+  // 32-row (one warp) CTAs were measured too: slower than 128-row CTAs from 8192 rows up, equal below
+  return launch_tall_r<NQ, 128>(stream, M, N, K, A, B, C, a_vec, b_vec);
+}
+
 }  // namespace
 
 cudaError_t launch_sgemm_ffma(exo_b200_Context* ctx, int64_t M, int64_t N, int64_t K, const float* A,
@@ -433,6 +568,16 @@ cudaError_t launch_sgemm_ffma(exo_b200_Context* ctx, int64_t M, int64_t N, int64
   if (M > INT32_MAX || N > INT32_MAX || K > INT32_MAX) return cudaErrorInvalidValue;
   const bool va = (K % 4 == 0) && ffma::aligned16(A);
   const bool vb = (N % 4 == 0) && ffma::aligned16(B) && ffma::aligned16(C);
+  if (N <= 16 && M >= 1024) {  // wider rows reuse too little of each B fragment here; the tile kernel takes them
+    const int a_vec = va ? 1 : 0, b_vec = vb ? 1 : 0;
+    const int m = (int)M, n = (int)N, k = (int)K;
+    switch ((n + 3) / 4) {
+      case 1: return launch_tall<1>(stream, m, n, k, A, B, C, a_vec, b_vec);
+      case 2: return launch_tall<2>(stream, m, n, k, A, B, C, a_vec, b_vec);
+      case 3: return launch_tall<3>(stream, m, n, k, A, B, C, a_vec, b_vec);
+      default: return launch_tall<4>(stream, m, n, k, A, B, C, a_vec, b_vec);
+    }
+  }
   static const bool gemv_tma = [] {
     const char* e = getenv("EXOB200_GEMV_TMA");  // =0: use the cp.async ring instead (timing experiments)
     return !(e && e[0] == '0');
