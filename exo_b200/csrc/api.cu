@@ -44,7 +44,8 @@ void sgemm_dispatch(const char* fn, void* ctxt, int path, int_fast32_t M, int_fa
   clear_error();
   if (bad_args(fn, M < 1 || N < 1 || K < 1, "M, N, K must be >= 1")) return;
   if (bad_args(fn, !A || !B || !C, "NULL tensor")) return;
-  exo_b200_Context* c = resolve_context(ctxt);
+  ContextUse use(resolve_context(ctxt));
+  exo_b200_Context* c = use.get();
   if (!c) return;
   if (path < 0) path = c->sgemm_path;
   Operand a, b, cc;
@@ -93,7 +94,8 @@ void conv_dispatch(const char* fn, void* ctxt, const ConvShape& s, const float* 
                "sizes must be >= 1 (pad >= 0) and the kernel must fit the padded input"))
     return;
   if (bad_args(fn, !inp || !output || !weights, "NULL tensor")) return;
-  exo_b200_Context* c = resolve_context(ctxt);
+  ContextUse use(resolve_context(ctxt));
+  exo_b200_Context* c = use.get();
   if (!c) return;
   Operand i, o, w, b;
   const size_t in_elems = (size_t)s.batch * s.in_h * s.in_w * s.in_c;
@@ -145,7 +147,8 @@ void matmul_i8_dispatch(const char* fn, int_fast32_t N, int_fast32_t M, int_fast
   clear_error();
   if (bad_args(fn, N < 1 || M < 1 || K < 1, "N, M, K must be >= 1")) return;
   if (bad_args(fn, !A || !B || !C || !scale, "NULL tensor or scale")) return;
-  exo_b200_Context* c = default_context();  // ctxt may be an uninitialised pointer: never read it
+  ContextUse use(default_context());  // ctxt may be an uninitialised pointer: never read it
+  exo_b200_Context* c = use.get();
   if (!c) return;
   float s;
   if (is_device_pointer(scale)) {
@@ -194,7 +197,8 @@ void conv_i8_dispatch(const char* fn, int_fast32_t batch_size, int_fast32_t out_
     return;
   if (bad_args(fn, out_dim != in_dim - kernel_dim + 1, "out_dim must equal in_dim - kernel_dim + 1")) return;
   if (bad_args(fn, !output || !bias || !inp || !weights || !scale, "NULL tensor or scale")) return;
-  exo_b200_Context* c = default_context();
+  ContextUse use(default_context());
+  exo_b200_Context* c = use.get();
   if (!c) return;
   float sc;
   if (is_device_pointer(scale)) {
@@ -364,7 +368,8 @@ EXOB200_CONV_INSTANCE(30, 4, 14, 256, 3, 256, 16)
 
 int exo_b200_selftest_bounded_wait(exo_b200_Context* ctxt, int limit_us) {
   clear_error();
-  exo_b200_Context* c = resolve_context(ctxt);
+  ContextUse use(resolve_context(ctxt));
+  exo_b200_Context* c = use.get();
   if (!c) return exo_b200_last_error();
   if (limit_us < 1 || limit_us > 2000000) {
     set_error(EXO_B200_ERR_INVALID_ARGUMENT, "exo_b200_selftest_bounded_wait: limit_us must be in [1, 2000000]");
@@ -381,7 +386,8 @@ void gemm_bf16_exo(void* ctxt, int_fast32_t M, int_fast32_t N, int_fast32_t K, c
   clear_error();
   if (bad_args(fn, M < 1 || N < 1 || K < 1, "M, N, K must be >= 1")) return;
   if (bad_args(fn, !A || !B || !C, "NULL tensor")) return;
-  exo_b200_Context* c = resolve_context(ctxt);
+  ContextUse use(resolve_context(ctxt));
+  exo_b200_Context* c = use.get();
   if (!c) return;
   Operand a, b, cc;
   if (want_row_pipeline(M, A, C, (size_t)K * 2 + (size_t)N * 2)) {

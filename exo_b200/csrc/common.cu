@@ -51,6 +51,7 @@ static exo_b200_Context* make_context(int device, cudaStream_t stream) {
   c->stream = stream;
   c->sm_count = prop.multiProcessorCount;
   c->sgemm_path = EXO_B200_SGEMM_FFMA;
+  c->mutex = new std::recursive_mutex();
   if (const char* p = getenv("EXOB200_SGEMM_PATH")) {
     if (!strcmp(p, "3xtf32")) c->sgemm_path = EXO_B200_SGEMM_3XTF32;
   }
@@ -68,6 +69,7 @@ static exo_b200_Context* make_context(int device, cudaStream_t stream) {
   }
   cudaSetDevice(cur);
   if (!check_cuda(e, "status word allocation")) {
+    delete c->mutex;
     delete c;
     return nullptr;
   }
@@ -82,10 +84,19 @@ exo_b200_Context* default_context() {
   if (it == g_default.end()) {
     exo_b200_Context* c = make_context(device, nullptr);
     if (!c) return nullptr;
+    c->is_default = true;
     it = g_default.emplace(device, c).first;
   }
-  it->second->stream = tl_default_stream;
   return it->second;
+}
+
+ContextUse::ContextUse(exo_b200_Context* c) : c_(c) {
+  if (!c_) return;
+  c_->mutex->lock();
+  if (c_->is_default) c_->stream = tl_default_stream;
+}
+ContextUse::~ContextUse() {
+  if (c_) c_->mutex->unlock();
 }
 
 exo_b200_Context* resolve_context(void* ctxt) {
@@ -218,6 +229,7 @@ exo_b200_Context* exo_b200_context_create(int device, void* stream) {
 
 void exo_b200_context_destroy(exo_b200_Context* c) {
   if (!c || c->magic != kContextMagic) return;
+  c->mutex->lock();  // waits for a call in flight on another thread
   cudaStreamSynchronize(c->stream);
   for (int i = 0; i < 4; i++)
     if (c->stage[i]) cudaFree(c->stage[i]);
@@ -237,22 +249,29 @@ void exo_b200_context_destroy(exo_b200_Context* c) {
     cudaEventDestroy(c->ev_ready);
   }
   c->magic = 0;
+  c->mutex->unlock();
+  delete c->mutex;
   delete c;
 }
 
 void exo_b200_context_set_stream(exo_b200_Context* c, void* stream) {
-  if (c && c->magic == kContextMagic) c->stream = static_cast<cudaStream_t>(stream);
+  if (!c || c->magic != kContextMagic) return;
+  ContextUse use(c);
+  c->stream = static_cast<cudaStream_t>(stream);
 }
 
 void exo_b200_context_set_sgemm_path(exo_b200_Context* c, int path) {
-  if (c && c->magic == kContextMagic) c->sgemm_path = path;
+  if (!c || c->magic != kContextMagic) return;
+  ContextUse use(c);
+  c->sgemm_path = path;
 }
 
 void exo_b200_set_default_stream(void* stream) { tl_default_stream = static_cast<cudaStream_t>(stream); }
 
 int exo_b200_synchronize(exo_b200_Context* ctxt) {
   clear_error();
-  exo_b200_Context* c = resolve_context(ctxt);
+  ContextUse use(resolve_context(ctxt));
+  exo_b200_Context* c = use.get();
   if (!c) return exo_b200_last_error();
   if (check_cuda(cudaStreamSynchronize(c->stream), "cudaStreamSynchronize")) read_status(c);
   return exo_b200_last_error();

@@ -4,6 +4,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <mutex>
 #include <string>
 
 #include "../../include/exo_b200.h"
@@ -43,6 +44,8 @@ struct exo_b200_Context {
   void* pipe_c[2];
   size_t pipe_a_bytes, pipe_c_bytes;
   bool pipe_ready;
+  bool is_default;              // the per-device context that ctxt == NULL resolves to
+  std::recursive_mutex* mutex;  // held by an entry point for the whole call (staging and scratch are shared)
 };
 
 namespace exob200 {
@@ -57,6 +60,22 @@ bool check_cuda(cudaError_t e, const char* what);
 // usable context on an sm_100 device, or returns nullptr with the error set.
 exo_b200_Context* resolve_context(void* ctxt);
 exo_b200_Context* default_context();
+
+// Holds the context's mutex for the scope of one entry-point call, so that host threads
+// calling into one context (in particular the shared default context, as OpenMP callers of
+// the generated C would) take turns with its staging buffers, scratch and pipeline.  For the
+// default context it also installs the calling thread's default stream.
+class ContextUse {
+ public:
+  explicit ContextUse(exo_b200_Context* c);
+  ~ContextUse();
+  ContextUse(const ContextUse&) = delete;
+  ContextUse& operator=(const ContextUse&) = delete;
+  exo_b200_Context* get() const { return c_; }
+
+ private:
+  exo_b200_Context* c_;
+};
 
 // true if p is device-accessible memory (device or managed allocation)
 bool is_device_pointer(const void* p);

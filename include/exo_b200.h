@@ -25,9 +25,14 @@
  * functions receive an UNINITIALISED pointer from their reference callers
  * (apps/gemmini/test/run_matmul.c:49-52), so they never look at ctxt.
  *
- * Thread safety: calls that share a context are serialised by the caller (the
- * reference's sgemm_exo is not reentrant either: it keeps tiles in function
- * statics, tests/golden/test_apps/test_x86_sgemm.txt:797,804).
+ * Thread safety: every entry point holds its context's mutex for the length of
+ * the call, so host threads may call into one context -- the default one
+ * included -- at the same time; they take turns.  (The reference's sgemm_exo is
+ * not reentrant at all: it keeps tiles in function statics,
+ * tests/golden/test_apps/test_x86_sgemm.txt:797,804.)  A call with device
+ * pointers only enqueues kernels; kernels enqueued through ONE context on
+ * DIFFERENT streams may overlap on the GPU and share that context's scratch,
+ * so give each stream its own context.
  */
 #pragma once
 #ifndef EXO_B200_H

@@ -554,3 +554,37 @@ def test_conv_reference_layout_on_tensor_path(lib, port, torch):
     assert (err <= bound).all(), f"max err {err.max():.3e}, worst ratio {(err / bound).max():.3f}"
     assert err.max() > 0  # it really took the tensor path (the FFMA path would be bit-exact)
     ctx.close()
+
+
+@pytest.mark.gpu
+def test_concurrent_host_threads_share_the_default_context(lib, port):
+    """Host threads calling with host buffers and ctxt = NULL at the same time (what an
+    OpenMP caller of the generated C would do) take turns inside the library; every
+    result is still bit-identical to the oracle."""
+    import threading
+    shapes = [(192, 130, 77), (64, 64, 300), (257, 33, 129), (100, 200, 50)]
+    work = []
+    for i, (M, N, K) in enumerate(shapes):
+        A, B, C = cases.sgemm_inputs(M, N, K, seed=40 + i)
+        want = C.copy()
+        port.sgemm(A, B, want)
+        work.append((M, N, K, A, B, C, want))
+    errors = []
+
+    def run(item):
+        M, N, K, A, B, C, want = item
+        try:
+            for _ in range(5):
+                got = C.copy()
+                lib.sgemm_exo_ffma(None, M, N, K, A, B, got)
+                if not np.array_equal(bits(got), bits(want)):
+                    errors.append((M, N, K))
+        except Exception as e:  # noqa: BLE001 - reported through the list
+            errors.append(repr(e))
+
+    threads = [threading.Thread(target=run, args=(w,)) for w in work]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
