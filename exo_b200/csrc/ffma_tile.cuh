@@ -31,10 +31,12 @@ namespace exob200 {
 namespace ffma {
 
 constexpr int BK = 16;
-// Three tile sizes from one engine (TD x TD threads, each 4H x 4H outputs):
-//   TD = 16, H = 2 -> 128 x 128, 256 threads, 8 x 8 per thread: the throughput configuration;
-//   TD = 16, H = 1 ->  64 x  64, 256 threads, 4 x 4 per thread: too few 128 x 128 tiles for the machine;
-//   TD =  8, H = 1 ->  32 x  32,  64 threads, 4 x 4 per thread: too few 64 x 64 tiles.  Such problems are
+// Tile sizes from one engine (TDY x TDX threads, each 4H x 4H outputs):
+//   16 x 16, H = 2 -> 128 x 128, 256 threads, 8 x 8 per thread: the throughput configuration;
+//   16 x  8, H = 2 -> 128 x  64, 128 threads, same per-thread work: when the 128 x 128 tiles would
+//     leave a nearly empty last wave (tile counts just above a multiple of the resident CTAs);
+//   16 x 16, H = 1 ->  64 x  64, 256 threads, 4 x 4 per thread: too few 128 x 128 tiles for the machine;
+//    8 x  8, H = 1 ->  32 x  32,  64 threads, 4 x 4 per thread: too few 64 x 64 tiles.  Such problems are
 //     bound by the latency of one warp's k loop, so spreading the same warps over more SMs (one or two
 //     per scheduler instead of four) is what shortens them.
 // Without split-K, which the reference's per-element chain order rules out, parallelism only comes
@@ -76,11 +78,12 @@ __device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
   return d;
 }
 
-template <class Policy, bool PACKED, int H, int TD>
-__global__ void __launch_bounds__(TD * TD, TD == 16 ? 2 : 8) tile_kernel(const Policy P, int tiles_m, int tiles_n) {
-  constexpr int THREADS = TD * TD;
-  constexpr int QS = 4 * TD;  // rows (columns) per quadrant
-  constexpr int BM = QS * H, BN = QS * H;
+template <class Policy, bool PACKED, int H, int TDY, int TDX>
+__global__ void __launch_bounds__(TDY * TDX, 512 / (TDY * TDX))
+tile_kernel(const Policy P, int tiles_m, int tiles_n) {
+  constexpr int THREADS = TDY * TDX;
+  constexpr int QSM = 4 * TDY, QSN = 4 * TDX;  // rows / columns per quadrant
+  constexpr int BM = QSM * H, BN = QSN * H;
   constexpr int AS_PITCH = BM + 4;  // floats; keeps 16-byte alignment, spreads the transposing stores
   constexpr int R = 4 * H;          // rows (and columns) per thread
   __shared__ __align__(16) float As[2][BK][AS_PITCH];
@@ -102,9 +105,9 @@ __global__ void __launch_bounds__(TD * TD, TD == 16 ? 2 : 8) tile_kernel(const P
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
-  constexpr int WX = TD / 8;                       // warps side by side
-  const int ty = (warp / WX) * 4 + (lane >> 3);  // 0..TD-1
-  const int tx = (warp % WX) * 8 + (lane & 7);   // 0..TD-1
+  constexpr int WX = TDX / 8;                      // warps side by side
+  const int ty = (warp / WX) * 4 + (lane >> 3);  // 0..TDY-1
+  const int tx = (warp % WX) * 8 + (lane & 7);   // 0..TDX-1
 
   // global -> register staging coordinates
   // A tile: BM rows x 16 k.  thread -> rows tid/4 (+ THREADS/4 per pass), k quad (tid%4)*4
@@ -146,10 +149,10 @@ __global__ void __launch_bounds__(TD * TD, TD == 16 ? 2 : 8) tile_kernel(const P
   uint64_t acc2[PACKED ? R : 1][PACKED ? R / 2 : 1];  // [row][column pair]
 #pragma unroll
   for (int i = 0; i < R; i++) {
-    const int row = m0 + (i >> 2) * QS + ty * 4 + (i & 3);
+    const int row = m0 + (i >> 2) * QSM + ty * 4 + (i & 3);
 #pragma unroll
     for (int jq = 0; jq < H; jq++) {
-      const float4 v = P.init(row, n0 + jq * QS + tx * 4);
+      const float4 v = P.init(row, n0 + jq * QSN + tx * 4);
       if (PACKED) {
         acc2[i][jq * 2 + 0] = pack2(v.x, v.y);
         acc2[i][jq * 2 + 1] = pack2(v.z, v.w);
@@ -176,7 +179,7 @@ __global__ void __launch_bounds__(TD * TD, TD == 16 ? 2 : 8) tile_kernel(const P
       float a[R];
 #pragma unroll
       for (int h = 0; h < H; h++) {
-        const float4 av = *reinterpret_cast<const float4*>(&As[buf][kk][h * QS + ty * 4]);
+        const float4 av = *reinterpret_cast<const float4*>(&As[buf][kk][h * QSM + ty * 4]);
         a[h * 4 + 0] = av.x;
         a[h * 4 + 1] = av.y;
         a[h * 4 + 2] = av.z;
@@ -186,7 +189,7 @@ __global__ void __launch_bounds__(TD * TD, TD == 16 ? 2 : 8) tile_kernel(const P
         uint64_t b[R / 2];
 #pragma unroll
         for (int h = 0; h < H; h++) {
-          const ulonglong2 bv = *reinterpret_cast<const ulonglong2*>(&Bs[buf][kk][h * QS + tx * 4]);
+          const ulonglong2 bv = *reinterpret_cast<const ulonglong2*>(&Bs[buf][kk][h * QSN + tx * 4]);
           b[h * 2 + 0] = bv.x;
           b[h * 2 + 1] = bv.y;
         }
@@ -200,7 +203,7 @@ __global__ void __launch_bounds__(TD * TD, TD == 16 ? 2 : 8) tile_kernel(const P
         float b[R];
 #pragma unroll
         for (int h = 0; h < H; h++) {
-          const float4 bv = *reinterpret_cast<const float4*>(&Bs[buf][kk][h * QS + tx * 4]);
+          const float4 bv = *reinterpret_cast<const float4*>(&Bs[buf][kk][h * QSN + tx * 4]);
           b[h * 4 + 0] = bv.x;
           b[h * 4 + 1] = bv.y;
           b[h * 4 + 2] = bv.z;
@@ -225,7 +228,7 @@ __global__ void __launch_bounds__(TD * TD, TD == 16 ? 2 : 8) tile_kernel(const P
 
 #pragma unroll
   for (int i = 0; i < R; i++) {
-    const int row = m0 + (i >> 2) * QS + ty * 4 + (i & 3);
+    const int row = m0 + (i >> 2) * QSM + ty * 4 + (i & 3);
 #pragma unroll
     for (int jq = 0; jq < H; jq++) {
       float4 v;
@@ -235,7 +238,7 @@ __global__ void __launch_bounds__(TD * TD, TD == 16 ? 2 : 8) tile_kernel(const P
       } else {
         v = make_float4(acc[i][jq * 4], acc[i][jq * 4 + 1], acc[i][jq * 4 + 2], acc[i][jq * 4 + 3]);
       }
-      P.store(row, n0 + jq * QS + tx * 4, v);
+      P.store(row, n0 + jq * QSN + tx * 4, v);
     }
   }
 }
@@ -249,36 +252,45 @@ inline bool use_packed() {
   return packed;
 }
 
-template <class Policy, int H, int TD>
+template <class Policy, int H, int TDY, int TDX>
 cudaError_t launch_tiles_h(cudaStream_t stream, const Policy& P) {
-  constexpr int T = 4 * TD * H;
-  const int64_t tiles_m = (P.M + T - 1) / T, tiles_n = (P.N + T - 1) / T;
+  constexpr int TM = 4 * TDY * H, TN = 4 * TDX * H;
+  const int64_t tiles_m = (P.M + TM - 1) / TM, tiles_n = (P.N + TN - 1) / TN;
   if (tiles_m * tiles_n > INT32_MAX) return cudaErrorInvalidValue;
   const unsigned grid = (unsigned)(tiles_m * tiles_n);
   if (use_packed())
-    tile_kernel<Policy, true, H, TD><<<grid, TD * TD, 0, stream>>>(P, (int)tiles_m, (int)tiles_n);
+    tile_kernel<Policy, true, H, TDY, TDX><<<grid, TDY * TDX, 0, stream>>>(P, (int)tiles_m, (int)tiles_n);
   else
-    tile_kernel<Policy, false, H, TD><<<grid, TD * TD, 0, stream>>>(P, (int)tiles_m, (int)tiles_n);
+    tile_kernel<Policy, false, H, TDY, TDX><<<grid, TDY * TDX, 0, stream>>>(P, (int)tiles_m, (int)tiles_n);
   return cudaGetLastError();
 }
 
 // 128 x 128 tiles unless they would leave most SMs without work; 32 x 32 when even
-// 64 x 64 tiles would.
+// 64 x 64 tiles would.  128 x 64 tiles when the last wave of 128 x 128 tiles would be
+// less than half full (two resident CTAs per SM): the tail then costs half a tile time.
 template <class Policy>
-cudaError_t launch_tiles(cudaStream_t stream, const Policy& P) {
+cudaError_t launch_tiles(cudaStream_t stream, const Policy& P, int sm_count = 148) {
   const int64_t big_tiles = ((int64_t)(P.M + 127) / 128) * ((P.N + 127) / 128);
   const int64_t mid_tiles = ((int64_t)(P.M + 63) / 64) * ((P.N + 63) / 64);
   static const int force = [] {
-    const char* e = getenv("EXOB200_FFMA_TILE");  // 32, 64 or 128 forces a tile size (timing experiments)
+    const char* e = getenv("EXOB200_FFMA_TILE");  // 32, 64, 128 or 12864 forces a tile size (timing experiments)
     return e ? atoi(e) : 0;
   }();
-  const int tile = force == 32 || force == 64 || force == 128 ? force
-                   : big_tiles > 148                         ? 128
-                   : mid_tiles > 148                         ? 64
-                                                             : 32;
-  if (tile == 128) return launch_tiles_h<Policy, 2, 16>(stream, P);
-  if (tile == 64) return launch_tiles_h<Policy, 1, 16>(stream, P);
-  return launch_tiles_h<Policy, 1, 8>(stream, P);
+  int tile;
+  if (force == 32 || force == 64 || force == 128 || force == 12864) {
+    tile = force;
+  } else if (big_tiles > sm_count) {
+    const int64_t slots = 2 * (int64_t)sm_count, tail = big_tiles % slots;
+    // measured: 324 tiles 578 -> 517 us, 313 tiles 332 -> 299 us; but 1024 tiles (tail 136) 2564 -> 2654 us:
+    // after a few waves the CTAs have drifted apart and the half tiles' ~4 % lower efficiency is all that is left
+    tile = (big_tiles < 2 * slots && tail != 0 && tail <= slots / 2) ? 12864 : 128;
+  } else {
+    tile = mid_tiles > sm_count ? 64 : 32;
+  }
+  if (tile == 128) return launch_tiles_h<Policy, 2, 16, 16>(stream, P);
+  if (tile == 12864) return launch_tiles_h<Policy, 2, 16, 8>(stream, P);
+  if (tile == 64) return launch_tiles_h<Policy, 1, 16, 16>(stream, P);
+  return launch_tiles_h<Policy, 1, 8, 8>(stream, P);
 }
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
