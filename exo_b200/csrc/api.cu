@@ -23,6 +23,21 @@ bool want_row_pipeline(int64_t rows, const void* host_a, const void* host_c, siz
   if (is_device_pointer(host_a) || is_device_pointer(host_c)) return false;
   return (double)rows * (double)bytes_per_row >= 64.0e6 && rows >= 1024;
 }
+// The two-dimensional pipeline pays when the second operand is a sizeable part of the
+// upload (the row pipeline cannot start before all of it is in place) and there are
+// enough blocks to overlap.  EXOB200_PIPELINE=rows keeps the row pipeline (A/B timing).
+bool want_block_pipeline(int64_t rows, int64_t cols, size_t k_bytes, const void* host_a, const void* host_b,
+                         const void* host_c) {
+  static const bool off = [] {
+    const char* e = getenv("EXOB200_NO_PIPELINE");
+    const char* m = getenv("EXOB200_PIPELINE");
+    return (e && e[0] == '1') || (m && !strcmp(m, "rows"));
+  }();
+  if (off) return false;
+  if (is_device_pointer(host_a) || is_device_pointer(host_b) || is_device_pointer(host_c)) return false;
+  const double a_bytes = (double)rows * (double)k_bytes, b_bytes = (double)cols * (double)k_bytes;
+  return rows >= 8192 && cols >= 8192 && b_bytes >= 32.0e6 && a_bytes + b_bytes <= 8.0e9;
+}
 int64_t pipeline_chunk_rows(int64_t rows, size_t bytes_per_row) {
   int64_t r = (int64_t)(96.0e6 / (double)bytes_per_row);
   r = r / 256 * 256;
@@ -390,6 +405,26 @@ void gemm_bf16_exo(void* ctxt, int_fast32_t M, int_fast32_t N, int_fast32_t K, c
   exo_b200_Context* c = use.get();
   if (!c) return;
   Operand a, b, cc;
+  if (want_block_pipeline(M, N, (size_t)K * 2, A, B, C)) {
+    // everything on the host and B large too: upload both operands piecewise and let
+    // output blocks leave as soon as their row chunk and column block are on the device
+    if (K % 8 != 0) {
+      set_error(EXO_B200_ERR_UNSUPPORTED, "gemm_bf16_exo: K must be a multiple of 8 and bases 16-byte aligned");
+      return;
+    }
+    static const int64_t br = getenv("EXOB200_BLOCK_ROWS") ? atoll(getenv("EXOB200_BLOCK_ROWS")) : 2048;
+    // 2048 x 4096 blocks measured best on the 32768 x 16384 x 8192 problem (25.0 ms against 26.1 ms for the row
+    // pipeline); 2048-wide blocks lose to it (28.0 ms): their 4 KB rows make the strided copy-out slow
+    static const int64_t bc = getenv("EXOB200_BLOCK_COLS") ? atoll(getenv("EXOB200_BLOCK_COLS")) : 4096;
+    BlockPipeline p{M, N, br, bc, A, (size_t)K * 2, B, (size_t)K * 2, C, 2};
+    if (!run_block_pipeline(c, p, [&](int64_t rows, int64_t cols, const void* dA, const void* dB, void* dC) {
+          return launch_gemm_bf16_tc(c, rows, cols, K, static_cast<const uint16_t*>(dA),
+                                     static_cast<const uint16_t*>(dB), static_cast<uint16_t*>(dC));
+        }))
+      return;
+    finish(c, true);
+    return;
+  }
   if (want_row_pipeline(M, A, C, (size_t)K * 2 + (size_t)N * 2)) {
     // host A and C: rows are independent, so stream them through in chunks
     if (!stage_in(c, 1, B, sizeof(uint16_t) * (size_t)K * N, true, &b)) return;

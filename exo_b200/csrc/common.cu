@@ -172,18 +172,22 @@ bool finish(exo_b200_Context* c, bool any_staged) {
   return read_status(c);
 }
 
-bool pipeline_prepare(exo_b200_Context* c, size_t a_chunk_bytes, size_t c_chunk_bytes) {
-  if (!c->pipe_ready) {
-    if (!check_cuda(cudaStreamCreateWithFlags(&c->pipe_in, cudaStreamNonBlocking), "cudaStreamCreate")) return false;
-    if (!check_cuda(cudaStreamCreateWithFlags(&c->pipe_out, cudaStreamNonBlocking), "cudaStreamCreate")) return false;
-    for (int i = 0; i < 2; i++) {
-      cudaEventCreateWithFlags(&c->ev_in[i], cudaEventDisableTiming);
-      cudaEventCreateWithFlags(&c->ev_kernel[i], cudaEventDisableTiming);
-      cudaEventCreateWithFlags(&c->ev_out[i], cudaEventDisableTiming);
-    }
-    if (!check_cuda(cudaEventCreateWithFlags(&c->ev_ready, cudaEventDisableTiming), "cudaEventCreate")) return false;
-    c->pipe_ready = true;
+static bool pipeline_streams(exo_b200_Context* c) {
+  if (c->pipe_ready) return true;
+  if (!check_cuda(cudaStreamCreateWithFlags(&c->pipe_in, cudaStreamNonBlocking), "cudaStreamCreate")) return false;
+  if (!check_cuda(cudaStreamCreateWithFlags(&c->pipe_out, cudaStreamNonBlocking), "cudaStreamCreate")) return false;
+  for (int i = 0; i < 2; i++) {
+    cudaEventCreateWithFlags(&c->ev_in[i], cudaEventDisableTiming);
+    cudaEventCreateWithFlags(&c->ev_kernel[i], cudaEventDisableTiming);
+    cudaEventCreateWithFlags(&c->ev_out[i], cudaEventDisableTiming);
   }
+  if (!check_cuda(cudaEventCreateWithFlags(&c->ev_ready, cudaEventDisableTiming), "cudaEventCreate")) return false;
+  c->pipe_ready = true;
+  return true;
+}
+
+bool pipeline_prepare(exo_b200_Context* c, size_t a_chunk_bytes, size_t c_chunk_bytes) {
+  if (!pipeline_streams(c)) return false;
   if (c->pipe_a_bytes < a_chunk_bytes || c->pipe_c_bytes < c_chunk_bytes) {
     if (!check_cuda(cudaStreamSynchronize(c->stream), "cudaStreamSynchronize")) return false;
     for (int i = 0; i < 2; i++) {
@@ -200,6 +204,65 @@ bool pipeline_prepare(exo_b200_Context* c, size_t a_chunk_bytes, size_t c_chunk_
     c->pipe_c_bytes = c_chunk_bytes;
   }
   return true;
+}
+
+static bool ensure_stage(exo_b200_Context* c, int slot, size_t bytes) {
+  if (c->stage_bytes[slot] >= bytes) return true;
+  if (c->stage[slot]) {
+    if (!check_cuda(cudaStreamSynchronize(c->stream), "cudaStreamSynchronize")) return false;
+    cudaFree(c->stage[slot]);
+    c->stage[slot] = nullptr;
+    c->stage_bytes[slot] = 0;
+  }
+  const size_t want = bytes + bytes / 8 + 256;
+  if (!check_cuda(cudaMalloc(&c->stage[slot], want), "cudaMalloc(staging)")) return false;
+  c->stage_bytes[slot] = want;
+  return true;
+}
+
+bool block_pipeline_prepare(exo_b200_Context* c, size_t a_bytes, size_t b_bytes, size_t c_block_bytes) {
+  if (!pipeline_streams(c)) return false;
+  if (!c->blk_ready) {
+    for (int i = 0; i < 4; i++) {
+      cudaEventCreateWithFlags(&c->ev_blk_kernel[i], cudaEventDisableTiming);
+      cudaEventCreateWithFlags(&c->ev_blk_out[i], cudaEventDisableTiming);
+    }
+    if (!check_cuda(cudaEventCreateWithFlags(&c->ev_upload, cudaEventDisableTiming), "cudaEventCreate")) return false;
+    c->blk_ready = true;
+  }
+  if (!ensure_stage(c, 0, a_bytes) || !ensure_stage(c, 1, b_bytes)) return false;
+  if (c->blk_c_bytes < c_block_bytes) {
+    if (!check_cuda(cudaStreamSynchronize(c->stream), "cudaStreamSynchronize")) return false;
+    for (int i = 0; i < 4; i++) {
+      if (c->blk_c[i]) cudaFree(c->blk_c[i]);
+      c->blk_c[i] = nullptr;
+    }
+    c->blk_c_bytes = 0;
+    for (int i = 0; i < 4; i++)
+      if (!check_cuda(cudaMalloc(&c->blk_c[i], c_block_bytes), "cudaMalloc(block pipeline)")) return false;
+    c->blk_c_bytes = c_block_bytes;
+  }
+  return true;
+}
+
+std::vector<char> block_upload_order(const BlockPipeline& p) {
+  const int64_t na = (p.rows + p.chunk_rows - 1) / p.chunk_rows, nb = (p.cols + p.chunk_cols - 1) / p.chunk_cols;
+  std::vector<char> order;
+  order.reserve((size_t)(na + nb));
+  int64_t a = 0, b = 0;
+  while (a < na || b < nb) {
+    // output bytes enabled per input byte: a row chunk enables b blocks, a column block a blocks
+    const double gain_a = a < na ? (double)b * p.chunk_cols * p.c_elem_bytes / (double)p.a_row_bytes : -1.0;
+    const double gain_b = b < nb ? (double)a * p.chunk_rows * p.c_elem_bytes / (double)p.b_col_bytes : -1.0;
+    if (gain_a >= gain_b) {
+      order.push_back('A');
+      a++;
+    } else {
+      order.push_back('B');
+      b++;
+    }
+  }
+  return order;
 }
 
 bool ensure_scratch(exo_b200_Context* c, int slot, size_t bytes) {
@@ -248,6 +311,15 @@ void exo_b200_context_destroy(exo_b200_Context* c) {
     }
     cudaEventDestroy(c->ev_ready);
   }
+  if (c->blk_ready) {
+    for (int i = 0; i < 4; i++) {
+      cudaEventDestroy(c->ev_blk_kernel[i]);
+      cudaEventDestroy(c->ev_blk_out[i]);
+    }
+    cudaEventDestroy(c->ev_upload);
+  }
+  for (int i = 0; i < 4; i++)
+    if (c->blk_c[i]) cudaFree(c->blk_c[i]);
   c->magic = 0;
   c->mutex->unlock();
   delete c->mutex;

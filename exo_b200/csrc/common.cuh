@@ -4,8 +4,10 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <algorithm>
 #include <mutex>
 #include <string>
+#include <vector>
 
 #include "../../include/exo_b200.h"
 
@@ -44,6 +46,11 @@ struct exo_b200_Context {
   void* pipe_c[2];
   size_t pipe_a_bytes, pipe_c_bytes;
   bool pipe_ready;
+  // host-pointer block pipeline: ring of dense C blocks and the events that guard them
+  void* blk_c[4];
+  size_t blk_c_bytes;
+  cudaEvent_t ev_blk_kernel[4], ev_blk_out[4], ev_upload;
+  bool blk_ready;
   bool is_default;              // the per-device context that ctxt == NULL resolves to
   std::recursive_mutex* mutex;  // held by an entry point for the whole call (staging and scratch are shared)
 };
@@ -118,6 +125,96 @@ struct RowPipeline {
 template <class Launch>
 bool run_row_pipeline(exo_b200_Context* c, const RowPipeline& p, Launch launch);
 bool pipeline_prepare(exo_b200_Context* c, size_t a_chunk_bytes, size_t c_chunk_bytes);
+
+// The same idea in two dimensions, for products whose second operand is also on the
+// host and large: C[i-th row chunk, j-th column block] needs only row chunk i of the
+// first operand and column block j of the second, so waiting for all of the second
+// operand before the first output can leave (as the row pipeline does) is not
+// necessary.  Both operands are uploaded piecewise in the order that enables the most
+// output bytes per uploaded byte; every block that becomes computable is multiplied
+// into a dense block buffer and copied out as a strided 2-D copy.  `launch(rows, cols,
+// dA, dB, dC)` enqueues the kernel for one block (dC dense, pitch = cols) on c->stream.
+struct BlockPipeline {
+  int64_t rows, cols;              // C is rows x cols, row-major
+  int64_t chunk_rows, chunk_cols;  // block size
+  const void* host_a;              // rows x a_row_bytes
+  size_t a_row_bytes;
+  const void* host_b;              // cols x b_col_bytes: column j of the product's second operand is contiguous
+  size_t b_col_bytes;
+  void* host_c;
+  size_t c_elem_bytes;
+};
+bool block_pipeline_prepare(exo_b200_Context* c, size_t a_bytes, size_t b_bytes, size_t c_block_bytes);
+// The upload order: 'A' / 'B' per step, chosen greedily by output bytes enabled per byte uploaded.
+std::vector<char> block_upload_order(const BlockPipeline& p);
+
+template <class Launch>
+bool run_block_pipeline(exo_b200_Context* c, const BlockPipeline& p, Launch launch) {
+  const int64_t na = (p.rows + p.chunk_rows - 1) / p.chunk_rows, nb = (p.cols + p.chunk_cols - 1) / p.chunk_cols;
+  const size_t blk_bytes = (size_t)p.chunk_rows * p.chunk_cols * p.c_elem_bytes;
+  if (!block_pipeline_prepare(c, (size_t)p.rows * p.a_row_bytes, (size_t)p.cols * p.b_col_bytes, blk_bytes))
+    return false;
+  char* dA = static_cast<char*>(c->stage[0]);
+  char* dB = static_cast<char*>(c->stage[1]);
+  // work enqueued earlier on c->stream may still read the staging buffers
+  if (!check_cuda(cudaEventRecord(c->ev_ready, c->stream), "cudaEventRecord")) return false;
+  cudaStreamWaitEvent(c->pipe_in, c->ev_ready, 0);
+  cudaStreamWaitEvent(c->pipe_out, c->ev_ready, 0);
+  auto rows_of = [&](int64_t i) { return std::min(p.chunk_rows, p.rows - i * p.chunk_rows); };
+  auto cols_of = [&](int64_t j) { return std::min(p.chunk_cols, p.cols - j * p.chunk_cols); };
+  int64_t a_done = 0, b_done = 0, nblk = 0;
+  auto run_block = [&](int64_t i, int64_t j) -> bool {
+    const int buf = (int)(nblk & 3);
+    if (nblk >= 4) cudaStreamWaitEvent(c->stream, c->ev_blk_out[buf], 0);  // its last copy-out has drained
+    const int64_t r = rows_of(i), w = cols_of(j);
+    if (!check_cuda(launch(r, w, dA + (size_t)i * p.chunk_rows * p.a_row_bytes,
+                           dB + (size_t)j * p.chunk_cols * p.b_col_bytes, c->blk_c[buf]),
+                    "block kernel"))
+      return false;
+    cudaEventRecord(c->ev_blk_kernel[buf], c->stream);
+    cudaStreamWaitEvent(c->pipe_out, c->ev_blk_kernel[buf], 0);
+    char* hc = static_cast<char*>(p.host_c) +
+               ((size_t)i * p.chunk_rows * p.cols + (size_t)j * p.chunk_cols) * p.c_elem_bytes;
+    if (!check_cuda(cudaMemcpy2DAsync(hc, (size_t)p.cols * p.c_elem_bytes, c->blk_c[buf], (size_t)w * p.c_elem_bytes,
+                                      (size_t)w * p.c_elem_bytes, (size_t)r, cudaMemcpyDeviceToHost, c->pipe_out),
+                    "D2H block"))
+      return false;
+    cudaEventRecord(c->ev_blk_out[buf], c->pipe_out);
+    nblk++;
+    return true;
+  };
+  for (char step : block_upload_order(p)) {
+    if (step == 'A') {
+      const size_t off = (size_t)a_done * p.chunk_rows * p.a_row_bytes;
+      if (!check_cuda(cudaMemcpyAsync(dA + off, static_cast<const char*>(p.host_a) + off,
+                                      (size_t)rows_of(a_done) * p.a_row_bytes, cudaMemcpyHostToDevice, c->pipe_in),
+                      "H2D chunk"))
+        return false;
+    } else {
+      const size_t off = (size_t)b_done * p.chunk_cols * p.b_col_bytes;
+      if (!check_cuda(cudaMemcpyAsync(dB + off, static_cast<const char*>(p.host_b) + off,
+                                      (size_t)cols_of(b_done) * p.b_col_bytes, cudaMemcpyHostToDevice, c->pipe_in),
+                      "H2D chunk"))
+        return false;
+    }
+    // the copy stream is in order: this event also covers every earlier piece.  It is
+    // re-recorded per step, which is safe because the wait below is enqueued first.
+    cudaEventRecord(c->ev_upload, c->pipe_in);
+    cudaStreamWaitEvent(c->stream, c->ev_upload, 0);
+    if (step == 'A') {
+      for (int64_t j = 0; j < b_done; j++)
+        if (!run_block(a_done, j)) return false;
+      a_done++;
+    } else {
+      for (int64_t i = 0; i < a_done; i++)
+        if (!run_block(i, b_done)) return false;
+      b_done++;
+    }
+  }
+  if (!check_cuda(cudaStreamSynchronize(c->pipe_out), "cudaStreamSynchronize")) return false;
+  if (!check_cuda(cudaStreamSynchronize(c->pipe_in), "cudaStreamSynchronize")) return false;
+  return nblk == na * nb;
+}
 
 
 template <class Launch>

@@ -471,6 +471,26 @@ def test_host_pointer_pipeline_matches_device_pointer_path(lib, torch):
     assert np.array_equal(C8, dC8.cpu().numpy())
 
 
+def test_host_pointer_block_pipeline_matches_device_pointer_path(lib, port, torch):
+    """With A, B and C all on the host and B large, the bf16 GEMM uploads both operands
+    piecewise and sends 2048 x 4096 output blocks back as they become computable (ragged
+    last row chunk and column block here).  Bit-identical to the device-pointer call; a
+    sample of rows is also checked against the oracle."""
+    M, N, K = 8192 + 640, 8192 + 328, 2048
+    Ab = inputs.normal_bf16(71, (M, K))
+    Bb = inputs.normal_bf16(72, (N, K))
+    Cb = np.full((M, N), 0x7FC0, np.uint16)  # NaN pattern: every element must be overwritten
+    lib.gemm_bf16_exo(None, M, N, K, Ab, Bb, Cb)
+    dCb = torch.empty((M, N), dtype=torch.int16, device="cuda")
+    lib.gemm_bf16_exo(None, M, N, K, dev(torch, Ab.view(np.int16)), dev(torch, Bb.view(np.int16)), dCb)
+    torch.cuda.synchronize()
+    assert np.array_equal(Cb, dCb.cpu().numpy().view(np.uint16))
+    rows = np.array([0, 1, 2047, 2048, 4095, 6144, 8191, 8192, M - 1])
+    ref = inputs.bf16_bits_to_f32(Ab[rows]).astype(np.float64) @ inputs.bf16_bits_to_f32(Bb).astype(np.float64).T
+    got = inputs.bf16_bits_to_f32(Cb[rows]).astype(np.float64)
+    assert (np.abs(got - ref) <= 2.0 ** -7 * np.abs(ref) + 1e-3 * np.sqrt(K) * 4e-4).all()
+
+
 def test_unaligned_device_pointers(lib, port, torch):
     """Operands that start at an odd offset inside an allocation (4 bytes for fp32, 1 byte
     for int8) must take the scalar / SIMT paths and still match the oracle bit for bit."""
