@@ -65,6 +65,23 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 
+// Bounded wait for a thread that is normally far ahead of what it waits for (a TMA
+// producer waiting for a free ring stage): it sleeps between polls instead of
+// spinning, so that it does not spend issue slots -- and power -- for nothing.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity, volatile int* abort,
+                                                  uint64_t limit_ns, uint32_t sleep_ns) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = globaltimer_ns();
+  for (uint32_t it = 1;; ++it) {
+    __nanosleep(sleep_ns);
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((it & 15u) == 0) {
+      if (*abort) return false;
+      if (globaltimer_ns() - t0 > limit_ns) return false;
+    }
+  }
+}
+
 // Warp-wide bounded wait for warps that wait a long time (epilogue warps waiting for
 // a whole tile): one lane polls, with a sleep between polls, so the waiting warps
 // neither occupy issue slots nor load the shared-memory pipe that the tensor core
