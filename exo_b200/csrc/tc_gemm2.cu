@@ -524,7 +524,8 @@ gemm_tc2t_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   const int num_tiles = tiles_m * tiles_n;  // 512 x 256 tiles
   const int num_kb = (K + BK - 1) / BK;
-  const int d = min(skew, num_kb);
+  const bool snake = skew < 0;
+  const int d = snake ? 0 : min(skew, num_kb);
   auto tile_coord = [&](int t, int& tm, int& tn) {
     const int per_group = GM * tiles_n;
     const int group = t / per_group;
@@ -669,6 +670,56 @@ gemm_tc2t_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           break;
         }
         tc_fence_after();
+        if (snake) {
+          // experiment: no skew; the two halves of a k-block alternate their order from one
+          // k-block to the next (hi lo | lo hi | hi lo ...), so the accumulator changes once
+          // per k-block instead of twice
+          if (!mbar_wait(tempty_bar(1), acc_phase ^ 1u, abort_flag, WAIT_LIMIT_NS)) {
+            give_up(44);
+            break;
+          }
+          tc_fence_after();
+          for (int kb = 0; kb < num_kb; kb++) {
+            if (!mbar_wait(a_full(as), aphase, abort_flag, WAIT_LIMIT_NS) ||
+                !mbar_wait(b_full(bs_hi), bphase, abort_flag, WAIT_LIMIT_NS) ||
+                !mbar_wait(l_full(ls), lphase, abort_flag, WAIT_LIMIT_NS)) {
+              give_up(49);
+              ok = false;
+              break;
+            }
+            tc_fence_after();
+            const uint32_t a0 = a_tiles + as * T_STAGE_BYTES, a1 = l_tiles + ls * T_STAGE_BYTES;
+            const uint32_t b0 = b_tiles + bs_hi * T_STAGE_BYTES;
+            if (kb & 1) {
+              issue(a1, b0, 1, false);
+              issue(a0, b0, 0, false);
+            } else {
+              issue(a0, b0, 0, kb == 0);
+              issue(a1, b0, 1, kb == 0);
+            }
+            tc_commit_pair(a_empty(as));
+            tc_commit_pair(b_empty(bs_hi));
+            tc_commit_pair(l_empty(ls));
+            if (++as == TA_STAGES) {
+              as = 0;
+              aphase ^= 1u;
+            }
+            if (++bs_hi == TB_STAGES) {
+              bs_hi = 0;
+              bphase ^= 1u;
+            }
+            bs_lo = bs_hi;
+            if (++ls == TL_STAGES2) {
+              ls = 0;
+              lphase ^= 1u;
+            }
+          }
+          if (!ok) break;
+          tc_commit_pair(tfull_bar(0));
+          tc_commit_pair(tfull_bar(1));
+          acc_phase ^= 1u;
+          continue;
+        }
         for (int kb = 0; kb < d && ok; kb++) ok = hi_step(kb);
         if (!ok) break;
         if (d == num_kb) tc_commit_pair(tfull_bar(0));
@@ -701,25 +752,23 @@ gemm_tc2t_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const uint32_t stg = staging + (uint32_t)(warp - 2) * 2048u;
     uint32_t acc_phase = 0;
     bool ok = true;
-    auto emit = [&](const uint32_t (&r)[32], int row0, int col) {
-      if (!tma_store) {
-        store_chunk2<MODE>(ep, r, row0 + lane, col, M, N);
-        return;
+    auto pack = [&](const uint32_t (&r)[32], uint32_t (&o)[16]) {
+#pragma unroll
+      for (int i = 0; i < 16; i++) {
+        const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+        o[i] = *reinterpret_cast<const uint32_t*>(&h);
       }
+    };
+    // 32 rows x 32 bf16 columns: registers -> staging buffer -> TMA store
+    auto stage_store = [&](const uint32_t (&o)[16], int row0, int col) {
       if (row0 >= M || col >= N) return;  // warp-uniform
       if (lane == 0) bulk_wait_read();    // the previous store has read the staging buffer
       __syncwarp();
 #pragma unroll
       for (int j = 0; j < 4; j++) {
-        uint32_t w[4];
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-          const __nv_bfloat162 h =
-              __floats2bfloat162_rn(__uint_as_float(r[j * 8 + 2 * i]), __uint_as_float(r[j * 8 + 2 * i + 1]));
-          w[i] = *reinterpret_cast<const uint32_t*>(&h);
-        }
         const uint32_t dst = stg + (uint32_t)lane * 64u + (uint32_t)((j ^ ((lane >> 1) & 3)) * 16);
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3])
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(o[4 * j]), "r"(o[4 * j + 1]),
+                     "r"(o[4 * j + 2]), "r"(o[4 * j + 3])
                      : "memory");
       }
       fence_proxy_async();
@@ -744,21 +793,45 @@ gemm_tc2t_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const int row0 = m0 + q * 32;
         const uint32_t src = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(half * BN2 + part * (BN2 / 2));
         uint32_t r0[32], r1[32];
-        tmem_ld_32x32(src, r0);
-        tmem_ld_wait();
-        tmem_ld_32x32(src + 32, r1);
-        emit(r0, row0, n0);
-        tmem_ld_wait();
-        tmem_ld_32x32(src + 64, r0);
-        emit(r1, row0, n0 + 32);
-        tmem_ld_wait();
-        tmem_ld_32x32(src + 96, r1);
-        emit(r0, row0, n0 + 64);
-        tmem_ld_wait();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive_cluster(mapa(tempty_bar(half), 0));  // the accumulator is free: registers hold the rest
-        emit(r1, row0, n0 + 96);
+        if (tma_store) {
+          // Drain this warp's share of the accumulator into registers first (converting one
+          // chunk while the next is in flight) and hand the accumulator back; the stores
+          // follow off the critical path.
+          uint32_t pk[4][16];
+          tmem_ld_32x32(src, r0);
+          tmem_ld_wait();
+          tmem_ld_32x32(src + 32, r1);
+          pack(r0, pk[0]);
+          tmem_ld_wait();
+          tmem_ld_32x32(src + 64, r0);
+          pack(r1, pk[1]);
+          tmem_ld_wait();
+          tmem_ld_32x32(src + 96, r1);
+          pack(r0, pk[2]);
+          tmem_ld_wait();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(mapa(tempty_bar(half), 0));
+          pack(r1, pk[3]);
+#pragma unroll
+          for (int c = 0; c < 4; c++) stage_store(pk[c], row0, n0 + 32 * c);
+        } else {
+          tmem_ld_32x32(src, r0);
+          tmem_ld_wait();
+          tmem_ld_32x32(src + 32, r1);
+          store_chunk2<MODE>(ep, r0, row0 + lane, n0, M, N);
+          tmem_ld_wait();
+          tmem_ld_32x32(src + 64, r0);
+          store_chunk2<MODE>(ep, r1, row0 + lane, n0 + 32, M, N);
+          tmem_ld_wait();
+          tmem_ld_32x32(src + 96, r1);
+          store_chunk2<MODE>(ep, r0, row0 + lane, n0 + 64, M, N);
+          tmem_ld_wait();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(mapa(tempty_bar(half), 0));
+          store_chunk2<MODE>(ep, r1, row0 + lane, n0 + 96, M, N);
+        }
       }
       acc_phase ^= 1u;
     }
@@ -810,7 +883,7 @@ cudaError_t launch_tc2t(exo_b200_Context* ctx, const CUtensorMap& ma, const CUte
   static const int skew = [] {
     const char* e = getenv("EXOB200_TC2T_SKEW");
     const int n = e ? atoi(e) : 1;
-    return n >= 0 && n <= TB_STAGES - 2 ? n : 1;
+    return n >= -1 && n <= TB_STAGES - 2 ? n : 1;
   }();
   static const int relax = [] {
     const char* e = getenv("EXOB200_TC2T_RELAX");  // ns the producer sleeps between polls (0: spin)
@@ -828,15 +901,15 @@ template <int MODE>
 cudaError_t launch_tc2(exo_b200_Context* ctx, const CUtensorMap& ma, const CUtensorMap& mb, int64_t M, int64_t N,
                        int64_t K, const Epi2& ep) {
   cudaError_t e =
-      cudaFuncSetAttribute(gemm_tc2_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM2T_BYTES);
+      cudaFuncSetAttribute(gemm_tc2_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM2_BYTES);
   if (e != cudaSuccess) return e;
   const int64_t tiles_m = (M + 2 * BM - 1) / (2 * BM), tiles_n = (N + BN2 - 1) / BN2;
   if (tiles_m * tiles_n > INT32_MAX || M > INT32_MAX || N > INT32_MAX || K > INT32_MAX) return cudaErrorInvalidValue;
   // launched as clusters of two CTAs; size the grid to the number of pairs that
   // can be resident at once (a pair needs two SMs of the same GPC)
   cudaLaunchConfig_t cfg = {};
-  cfg.blockDim = dim3(THREADS2T);
-  cfg.dynamicSmemBytes = SMEM2T_BYTES;
+  cfg.blockDim = dim3(NUM_THREADS);
+  cfg.dynamicSmemBytes = SMEM2_BYTES;
   cfg.stream = ctx->stream;
   cudaLaunchAttribute attr;
   attr.id = cudaLaunchAttributeClusterDimension;
