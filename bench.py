@@ -502,6 +502,21 @@ def run_ours(args):
     lib.synchronize()
     value = wl.flops_total / (ms / 1e3) / 1e12
 
+    # Optional same-GPU, same-minute denominator: the vendor library's GEMM (torch.matmul ->
+    # cuBLAS) on the same buffers with the same timing loop.  A library call, reported for
+    # comparison only; nothing of the product runs through it.
+    library = None
+    if args.library_gemm and args.workload == "bf16" and world == 1:
+        time.sleep(1.0)
+        lib_c = torch.empty_like(wl.C)
+        sampler2 = ClockSampler(local)
+        sampler2.start()
+        time.sleep(0.3)
+        lms, lt0, lt1 = time_steps(torch, lambda: torch.matmul(wl.A, wl.B.t(), out=lib_c), args.steps, args.warmup)
+        library = {"impl": "torch.matmul (cuBLAS)", "tflops": wl.flops_total / (lms / 1e3) / 1e12, "ms_per_step": lms,
+                   "clocks": sampler2.stop(lt0, lt1), "ours_over_library": lms / ms}
+        del lib_c
+
     # end to end: pinned host buffers through the C ABI, copies inside the timed region
     if args.no_e2e:
         h2d = d2h = 0
@@ -520,15 +535,15 @@ def run_ours(args):
     peak = peaks["bf16_tflops"]
     per_launch_tflops = wl.flops_local / (ms / 1e3) / 1e12
     # DRAM bytes per launch of the headline shape from a one-pass ncu capture of one full-size
-    # launch (10.91 GB read + 1.07 GB written); scaled by the rows a rank owns
+    # launch (6.28 GB read + 1.06 GB written); scaled by the rows a rank owns
     traffic = None
     if args.workload == "bf16" and shape is None:
-        traffic = 11.98e9 * wl.shape[0] / BF16_SHAPE[0]
+        traffic = 7.34e9 * wl.shape[0] / BF16_SHAPE[0]
     roofline = {"bound": "tensor", "achieved": per_launch_tflops, "peak": peak, "unit": "TFLOP/s",
                 "frac": per_launch_tflops / peak, "traffic": traffic,
                 "frac_of_sustained_peak": per_launch_tflops / peaks.get("bf16_tflops_sustained", peak),
                 "peak_source": f"{peaks['source']} bf16 burst (sustained: {peaks.get('bf16_tflops_sustained')})",
-                "kernel": "gemm_tc2_kernel<bf16>" if args.workload == "bf16" else args.workload}
+                "kernel": "gemm_tc2t_kernel<bf16>" if args.workload == "bf16" else args.workload}
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
@@ -541,6 +556,8 @@ def run_ours(args):
     }
     if bcast_ms is not None:
         line["b_broadcast_ms"] = bcast_ms
+    if library is not None:
+        line["library_gemm"] = library
     if world == 1:
         del wl
         torch.cuda.empty_cache()
@@ -670,6 +687,8 @@ def main():
     ap.add_argument("--workload", default="bf16", choices=["bf16", "sgemm_ffma", "sgemm_3xtf32", "i8", "conv", "conv_3xtf32", "conv1x1", "conv1x1_3xtf32",
                              "conv_i8"])
     ap.add_argument("--shape", default=None, help="MxNxK override for small profiling cases")
+    ap.add_argument("--library-gemm", action="store_true",
+                    help="bf16, 1 GPU: also time torch.matmul (cuBLAS) on the same buffers, for comparison")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")

@@ -427,46 +427,28 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 // Tall variant: one pair computes a 512 x 256 tile as two 256 x 256 halves that
 // share every B stage.  Each CTA holds two 128 x 256 accumulators (all 512
 // tensor-memory columns), so there is no second tile to fill while one drains,
-// but A0 | A1 | B-half (48 KiB per k-block) feed twice the FLOPs: 24 instead of
-// 32 bytes into shared memory per 128 x 256 x 64 block.  The bytes saved are L2
-// and DRAM reads, i.e. power under the cap.  The epilogue is made short instead
-// of hidden: eight warps, output staged in shared memory and written with TMA
-// stores (whole lines instead of 16-byte pieces of 32 different lines per
-// instruction), and the lower half runs `skew` k-blocks behind the upper one, so
-// the upper accumulator drains while the lower one still multiplies and the next
-// tile's upper half starts while the lower accumulator drains.
+// but a stage of A0 | A1 | B-half (48 KiB, four stages) feeds twice the FLOPs:
+// 24 instead of 32 bytes into shared memory per 128 x 256 x 64 block, and half
+// the DRAM reads (6.3 instead of 10.9 - 13.6 GB per launch of the 32768 x 16384
+// x 8192 problem).  Those bytes are power under the cap.  The price is an
+// epilogue that is no longer hidden behind the next tile's MMAs; the lower half
+// therefore runs `skew` k-blocks behind the upper one, so that the upper
+// accumulator drains while the lower one still multiplies, and the next tile's
+// upper half starts while the lower accumulator drains.
 //
-// Three rings, because the operands live for different lengths of time: A0 (used
-// by the upper half, four stages), A1 (lower half, four stages) and the B half
-// (needed by the upper half and, `skew` k-blocks later, by the lower half; five
-// stages).  16 KiB each per stage.
-constexpr int T_STAGE_BYTES = A_TILE_BYTES;  // every ring: 128 rows x 128 bytes
-static_assert(BHALF * ROW_BYTES == T_STAGE_BYTES, "B half tile and A tile have the same size");
-constexpr int TA_STAGES = 4, TL_STAGES2 = 4, TB_STAGES = 5;
-constexpr int T_STAGING_BYTES = 8 * 2048;  // per epilogue warp: 32 rows x 64 bytes
-constexpr int TALL_TILE_BYTES = (TA_STAGES + TL_STAGES2 + TB_STAGES) * T_STAGE_BYTES + T_STAGING_BYTES;  // 224 KiB
-constexpr int SMEM2T_BYTES = TALL_TILE_BYTES + 1024 + 256;
-static_assert(SMEM2T_BYTES <= 232448, "exceeds the shared memory a CTA can opt in to");
-constexpr int THREADS2T = 32 * (2 + 8);  // warp 0 TMA, warp 1 MMA, warps 2-9 epilogue (two per tensor-memory lane quarter)
-
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, uint32_t src, int x, int y) {
-  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
-                   reinterpret_cast<uint64_t>(m)),
-               "r"(src), "r"(x), "r"(y)
-               : "memory");
-}
-__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-// the bulk stores issued by this thread have finished READING shared memory
-__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
-__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+// More elaborate versions were built and measured slower than this one: separate
+// rings for A0, A1 and B (more barrier waits and commits per k-block for the one
+// issuing thread), eight epilogue warps with staged TMA stores, and orders of the
+// MMAs that change accumulator less often.
+constexpr int STAGE2T_BYTES = 2 * A_TILE_BYTES + BHALF * ROW_BYTES;  // 48 KiB per CTA
+constexpr int STAGES2T = 4;
+static_assert(STAGES2T * STAGE2T_BYTES <= STAGES2 * STAGE2_BYTES, "tall ring must fit the same allocation");
 
 template <int MODE>
-__global__ void __launch_bounds__(THREADS2T, 1)
-gemm_tc2t_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 const __grid_constant__ CUtensorMap tmC, int M, int N, int K, Epi2 ep, DeviceStatus* status,
-                 int tiles_m, int tiles_n, int GM, int skew, int relax, int tma_store) {
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tc2t_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, int M, int N, int K,
+                 Epi2 ep, DeviceStatus* status, int tiles_m, int tiles_n, int GM, int skew, int relax) {
   using C = Cfg2<MODE>;
-  static_assert(MODE == M2_BF16, "the staged epilogue is written for 2-byte outputs");
   constexpr int BK = ROW_BYTES / C::ELEM;
   constexpr uint32_t IDESC =
       make_idesc(C::D_FMT, C::AB_FMT, C::AB_FMT, 2 * BM, BN2) | (C::BMN ? IDESC_B_MN_MAJOR : 0u);
@@ -474,25 +456,15 @@ gemm_tc2t_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t tiles = (raw + 1023u) & ~1023u;
-  const uint32_t a_tiles = tiles;
-  const uint32_t l_tiles = a_tiles + TA_STAGES * T_STAGE_BYTES;
-  const uint32_t b_tiles = l_tiles + TL_STAGES2 * T_STAGE_BYTES;
-  const uint32_t staging = b_tiles + TB_STAGES * T_STAGE_BYTES;
-  uint8_t* ctrl = smem_raw + (tiles - raw) + TALL_TILE_BYTES;
-  const uint32_t bars = tiles + TALL_TILE_BYTES;
-  auto a_full = [&](int s) { return bars + 8u * s; };
-  auto a_empty = [&](int s) { return bars + 8u * (TA_STAGES + s); };
-  auto l_full = [&](int s) { return bars + 8u * (2 * TA_STAGES + s); };
-  auto l_empty = [&](int s) { return bars + 8u * (2 * TA_STAGES + TL_STAGES2 + s); };
-  auto b_full = [&](int s) { return bars + 8u * (2 * TA_STAGES + 2 * TL_STAGES2 + s); };
-  auto b_empty = [&](int s) { return bars + 8u * (2 * TA_STAGES + 2 * TL_STAGES2 + TB_STAGES + s); };
-  constexpr int NRING = 2 * (TA_STAGES + TL_STAGES2 + TB_STAGES);
-  auto tfull_bar = [&](int b) { return bars + 8u * (NRING + b); };
-  auto tempty_bar = [&](int b) { return bars + 8u * (NRING + 2 + b); };
-  const uint32_t slot_addr = bars + 8u * (NRING + 4);
-  static_assert(8 * (NRING + 4) + 8 <= 256, "control block");
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(ctrl + 8 * (NRING + 4));
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(ctrl + 8 * (NRING + 4) + 4);
+  uint8_t* ctrl = smem_raw + (tiles - raw) + STAGES2 * STAGE2_BYTES;
+  const uint32_t bars = tiles + STAGES2 * STAGE2_BYTES;
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (STAGES2 + s); };
+  auto tfull_bar = [&](int b) { return bars + 8u * (2 * STAGES2 + b); };
+  auto tempty_bar = [&](int b) { return bars + 8u * (2 * STAGES2 + 2 + b); };
+  const uint32_t slot_addr = bars + 8u * (2 * STAGES2 + 4);
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(ctrl + 8 * (2 * STAGES2 + 4));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(ctrl + 8 * (2 * STAGES2 + 4) + 4);
   const uint32_t abort_addr = slot_addr + 4;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -501,17 +473,19 @@ gemm_tc2t_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int num_pairs = gridDim.x >> 1;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < NRING; i++) mbar_init(bars + 8u * i, 1);
+    for (int s = 0; s < STAGES2T; s++) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
     for (int b = 0; b < 2; b++) {
       mbar_init(tfull_bar(b), 1);
-      mbar_init(tempty_bar(b), 16);  // eight epilogue warps in each CTA of the pair
+      mbar_init(tempty_bar(b), 8);  // four epilogue warps in each CTA of the pair
     }
     *abort_flag = 0;
     fence_barrier_init();
     fence_proxy_async();
     prefetch_tensormap(&tmA);
     prefetch_tensormap(&tmB);
-    prefetch_tensormap(&tmC);
   }
   if (warp == 1) {
     tmem_alloc2(smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM2_COLS);
@@ -524,8 +498,7 @@ gemm_tc2t_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   const int num_tiles = tiles_m * tiles_n;  // 512 x 256 tiles
   const int num_kb = (K + BK - 1) / BK;
-  const bool snake = skew < 0;
-  const int d = snake ? 0 : min(skew, num_kb);
+  const int d = min(skew, num_kb);
   auto tile_coord = [&](int t, int& tm, int& tn) {
     const int per_group = GM * tiles_n;
     const int group = t / per_group;
@@ -542,66 +515,39 @@ gemm_tc2t_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   if (warp == 0) {
     // ------------------------------------------------ TMA producer (both CTAs)
-    // Loads are issued in the order the MMAs need them: A0 and B of k-block kb, then
-    // A1 of k-block kb - d.
     if (lane == 0) {
-      int as = 0, ls = 0, bs = 0;
-      uint32_t aphase = 0, lphase = 0, bphase = 0;
+      int stage = 0;
+      uint32_t phase = 0;
       bool ok = true;
-      auto wait_free = [&](uint32_t bar, uint32_t parity) {
-        return relax ? mbar_wait_relaxed(bar, parity, abort_flag, WAIT_LIMIT_NS, (uint32_t)relax)
-                     : mbar_wait(bar, parity, abort_flag, WAIT_LIMIT_NS);
-      };
       for (int t = pair; t < num_tiles && ok; t += num_pairs) {
         int tm, tn;
         tile_coord(t, tm, tn);
         const int m0 = tm * 4 * BM + (int)rank * BM;  // this CTA's rows of the upper half; lower half: + 2 BM
         const int n0 = tn * BN2 + (int)rank * BHALF;
-        auto load_hi = [&](int kb) -> bool {
-          const int k0 = kb * BK;
-          if (!wait_free(a_empty(as), aphase ^ 1u)) {
+        for (int kb = 0; kb < num_kb; kb++) {
+          // this thread is normally a ring ahead: sleeping between polls (relax ns) instead of
+          // spinning is worth about 2 % under the power cap
+          if (!(relax ? mbar_wait_relaxed(empty_bar(stage), phase ^ 1u, abort_flag, WAIT_LIMIT_NS, (uint32_t)relax)
+                      : mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, WAIT_LIMIT_NS))) {
             give_up(41);
-            return false;
+            ok = false;
+            break;
           }
-          if (rank == 0) mbar_arrive_expect_tx(a_full(as), 2 * T_STAGE_BYTES);
-          tma_load_2d_pair(a_tiles + as * T_STAGE_BYTES, &tmA, mapa(a_full(as), 0), k0, m0);
-          if (++as == TA_STAGES) {
-            as = 0;
-            aphase ^= 1u;
-          }
-          if (!wait_free(b_empty(bs), bphase ^ 1u)) {
-            give_up(48);
-            return false;
-          }
-          if (rank == 0) mbar_arrive_expect_tx(b_full(bs), 2 * T_STAGE_BYTES);
+          const uint32_t bar0 = mapa(full_bar(stage), 0);
+          const uint32_t dst = tiles + stage * STAGE2T_BYTES;
+          if (rank == 0) mbar_arrive_expect_tx(full_bar(stage), 2 * STAGE2T_BYTES);
+          const int k0 = kb * BK;
+          tma_load_2d_pair(dst, &tmA, bar0, k0, m0);
+          tma_load_2d_pair(dst + A_TILE_BYTES, &tmA, bar0, k0, m0 + 2 * BM);
           if (C::BMN)
-            tma_load_2d_pair(b_tiles + bs * T_STAGE_BYTES, &tmB, mapa(b_full(bs), 0), n0, k0);
+            tma_load_2d_pair(dst + 2 * A_TILE_BYTES, &tmB, bar0, n0, k0);
           else
-            tma_load_2d_pair(b_tiles + bs * T_STAGE_BYTES, &tmB, mapa(b_full(bs), 0), k0, n0);
-          if (++bs == TB_STAGES) {
-            bs = 0;
-            bphase ^= 1u;
+            tma_load_2d_pair(dst + 2 * A_TILE_BYTES, &tmB, bar0, k0, n0);
+          if (++stage == STAGES2T) {
+            stage = 0;
+            phase ^= 1u;
           }
-          return true;
-        };
-        auto load_lo = [&](int kb) -> bool {
-          if (!wait_free(l_empty(ls), lphase ^ 1u)) {
-            give_up(46);
-            return false;
-          }
-          if (rank == 0) mbar_arrive_expect_tx(l_full(ls), 2 * T_STAGE_BYTES);
-          tma_load_2d_pair(l_tiles + ls * T_STAGE_BYTES, &tmA, mapa(l_full(ls), 0), kb * BK, m0 + 2 * BM);
-          if (++ls == TL_STAGES2) {
-            ls = 0;
-            lphase ^= 1u;
-          }
-          return true;
-        };
-        for (int kb = 0; kb < num_kb && ok; kb++) {
-          ok = load_hi(kb);
-          if (ok && kb >= d) ok = load_lo(kb - d);
         }
-        for (int kb = num_kb - d; kb < num_kb && ok; kb++) ok = load_lo(kb);
       }
       if (!ok || *abort_flag) {
         const uint64_t t0 = globaltimer_ns();
@@ -613,14 +559,16 @@ gemm_tc2t_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   } else if (warp == 1) {
     // ------------------------------------------------ MMA issuer (even CTA only)
     if (lane == 0 && rank == 0) {
-      // `hi` (upper half, accumulator 0) runs d k-blocks ahead of `lo` (lower half,
-      // accumulator 1).  hi releases A0 stages; lo releases A1 and B stages.
-      int as = 0, ls = 0, bs_hi = 0, bs_lo = 0;
-      uint32_t aphase = 0, lphase = 0, bphase = 0;
+      // two cursors into the ring: `hi` (upper half, accumulator 0) runs d k-blocks
+      // ahead of `lo` (lower half, accumulator 1); a stage is released by lo
+      int hi_stage = 0, lo_stage = 0;
+      uint32_t hi_phase = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
       constexpr uint64_t B_ADV = C::BMN ? (uint64_t)((32 / C::ELEM) * ROW_BYTES / 16) : 2u;
-      auto issue = [&](uint32_t a0, uint32_t b0, int half, bool first) {
+      auto issue = [&](int stage, int half, bool first) {
+        const uint32_t a0 = tiles + stage * STAGE2T_BYTES + half * A_TILE_BYTES;
+        const uint32_t b0 = tiles + stage * STAGE2T_BYTES + 2 * A_TILE_BYTES;
         const uint64_t da = smem_desc_k_sw128(a0);
         const uint64_t db = C::BMN ? smem_desc_mn_sw128(b0, BK) : smem_desc_k_sw128(b0);
         const uint32_t dtm = tmem_base + (uint32_t)(half * BN2);
@@ -628,39 +576,16 @@ gemm_tc2t_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         for (int ks = 0; ks < KSTEPS; ks++)
           tc_mma_pair<C::KIND>(dtm, da + (uint64_t)(ks * 2), db + ks * B_ADV, IDESC, !(first && ks == 0));
       };
-      auto hi_step = [&](int kb) -> bool {
-        if (!mbar_wait(a_full(as), aphase, abort_flag, WAIT_LIMIT_NS) ||
-            !mbar_wait(b_full(bs_hi), bphase, abort_flag, WAIT_LIMIT_NS)) {
+      auto hi_step = [&](int kb) -> bool {  // upper half of k-block kb: wait for its stage, multiply
+        if (!mbar_wait(full_bar(hi_stage), hi_phase, abort_flag, WAIT_LIMIT_NS)) {
           give_up(43);
           return false;
         }
         tc_fence_after();
-        issue(a_tiles + as * T_STAGE_BYTES, b_tiles + bs_hi * T_STAGE_BYTES, 0, kb == 0);
-        tc_commit_pair(a_empty(as));
-        if (++as == TA_STAGES) {
-          as = 0;
-          aphase ^= 1u;
-        }
-        if (++bs_hi == TB_STAGES) {
-          bs_hi = 0;
-          bphase ^= 1u;
-        }
-        return true;
-      };
-      auto lo_step = [&](int kb) -> bool {
-        if (!mbar_wait(l_full(ls), lphase, abort_flag, WAIT_LIMIT_NS)) {
-          give_up(47);
-          return false;
-        }
-        tc_fence_after();
-        // B of this k-block: the stage the upper half used d k-blocks ago (already waited for)
-        issue(l_tiles + ls * T_STAGE_BYTES, b_tiles + bs_lo * T_STAGE_BYTES, 1, kb == 0);
-        tc_commit_pair(b_empty(bs_lo));
-        tc_commit_pair(l_empty(ls));
-        if (++bs_lo == TB_STAGES) bs_lo = 0;
-        if (++ls == TL_STAGES2) {
-          ls = 0;
-          lphase ^= 1u;
+        issue(hi_stage, 0, kb == 0);
+        if (++hi_stage == STAGES2T) {
+          hi_stage = 0;
+          hi_phase ^= 1u;
         }
         return true;
       };
@@ -670,56 +595,6 @@ gemm_tc2t_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           break;
         }
         tc_fence_after();
-        if (snake) {
-          // experiment: no skew; the two halves of a k-block alternate their order from one
-          // k-block to the next (hi lo | lo hi | hi lo ...), so the accumulator changes once
-          // per k-block instead of twice
-          if (!mbar_wait(tempty_bar(1), acc_phase ^ 1u, abort_flag, WAIT_LIMIT_NS)) {
-            give_up(44);
-            break;
-          }
-          tc_fence_after();
-          for (int kb = 0; kb < num_kb; kb++) {
-            if (!mbar_wait(a_full(as), aphase, abort_flag, WAIT_LIMIT_NS) ||
-                !mbar_wait(b_full(bs_hi), bphase, abort_flag, WAIT_LIMIT_NS) ||
-                !mbar_wait(l_full(ls), lphase, abort_flag, WAIT_LIMIT_NS)) {
-              give_up(49);
-              ok = false;
-              break;
-            }
-            tc_fence_after();
-            const uint32_t a0 = a_tiles + as * T_STAGE_BYTES, a1 = l_tiles + ls * T_STAGE_BYTES;
-            const uint32_t b0 = b_tiles + bs_hi * T_STAGE_BYTES;
-            if (kb & 1) {
-              issue(a1, b0, 1, false);
-              issue(a0, b0, 0, false);
-            } else {
-              issue(a0, b0, 0, kb == 0);
-              issue(a1, b0, 1, kb == 0);
-            }
-            tc_commit_pair(a_empty(as));
-            tc_commit_pair(b_empty(bs_hi));
-            tc_commit_pair(l_empty(ls));
-            if (++as == TA_STAGES) {
-              as = 0;
-              aphase ^= 1u;
-            }
-            if (++bs_hi == TB_STAGES) {
-              bs_hi = 0;
-              bphase ^= 1u;
-            }
-            bs_lo = bs_hi;
-            if (++ls == TL_STAGES2) {
-              ls = 0;
-              lphase ^= 1u;
-            }
-          }
-          if (!ok) break;
-          tc_commit_pair(tfull_bar(0));
-          tc_commit_pair(tfull_bar(1));
-          acc_phase ^= 1u;
-          continue;
-        }
         for (int kb = 0; kb < d && ok; kb++) ok = hi_step(kb);
         if (!ok) break;
         if (d == num_kb) tc_commit_pair(tfull_bar(0));
@@ -728,13 +603,18 @@ gemm_tc2t_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           break;
         }
         tc_fence_after();
-        for (int kb = 0; kb < num_kb && ok; kb++) {
+        for (int kb = 0; kb < num_kb; kb++) {
           if (kb + d < num_kb) {
-            ok = hi_step(kb + d);
-            if (!ok) break;
+            if (!hi_step(kb + d)) {
+              ok = false;
+              break;
+            }
             if (kb + d == num_kb - 1) tc_commit_pair(tfull_bar(0));  // upper accumulator complete
           }
-          ok = lo_step(kb);
+          // the lower half's stage was waited for when the upper half used it
+          issue(lo_stage, 1, kb == 0);
+          tc_commit_pair(empty_bar(lo_stage));
+          if (++lo_stage == STAGES2T) lo_stage = 0;
         }
         if (!ok) break;
         tc_commit_pair(tfull_bar(1));
@@ -743,45 +623,14 @@ gemm_tc2t_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
     __syncwarp();
   } else {
-    // ------------------------------------------------ epilogue warps 2..9 (both CTAs)
-    // Warp w may read tensor-memory lanes 32 (w % 4) .. + 31; the two warps of a lane
-    // quarter take four 32-column chunks each.  The load of the next chunk is in flight
-    // while the current one is converted, staged (64-byte swizzle, conflict free) and
-    // handed to a TMA store, which clips at the edges of C.
-    const int q = warp & 3, part = (warp - 2) >> 2;
-    const uint32_t stg = staging + (uint32_t)(warp - 2) * 2048u;
+    // ------------------------------------------------ epilogue warps 2..5 (both CTAs)
+    const int q = warp & 3;
     uint32_t acc_phase = 0;
     bool ok = true;
-    auto pack = [&](const uint32_t (&r)[32], uint32_t (&o)[16]) {
-#pragma unroll
-      for (int i = 0; i < 16; i++) {
-        const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
-        o[i] = *reinterpret_cast<const uint32_t*>(&h);
-      }
-    };
-    // 32 rows x 32 bf16 columns: registers -> staging buffer -> TMA store
-    auto stage_store = [&](const uint32_t (&o)[16], int row0, int col) {
-      if (row0 >= M || col >= N) return;  // warp-uniform
-      if (lane == 0) bulk_wait_read();    // the previous store has read the staging buffer
-      __syncwarp();
-#pragma unroll
-      for (int j = 0; j < 4; j++) {
-        const uint32_t dst = stg + (uint32_t)lane * 64u + (uint32_t)((j ^ ((lane >> 1) & 3)) * 16);
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(o[4 * j]), "r"(o[4 * j + 1]),
-                     "r"(o[4 * j + 2]), "r"(o[4 * j + 3])
-                     : "memory");
-      }
-      fence_proxy_async();
-      __syncwarp();
-      if (lane == 0) {
-        tma_store_2d(&tmC, stg, col, row0);
-        bulk_commit();
-      }
-    };
     for (int t = pair; t < num_tiles && ok; t += num_pairs) {
       int tm, tn;
       tile_coord(t, tm, tn);
-      const int n0 = tn * BN2 + part * (BN2 / 2);
+      const int n0 = tn * BN2;
       for (int half = 0; half < 2; half++) {
         const int m0 = tm * 4 * BM + half * 2 * BM + (int)rank * BM;
         if (!mbar_wait_warp(tfull_bar(half), acc_phase, abort_flag, WAIT_LIMIT_NS)) {
@@ -790,53 +639,22 @@ gemm_tc2t_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           break;
         }
         tc_fence_after();
-        const int row0 = m0 + q * 32;
-        const uint32_t src = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(half * BN2 + part * (BN2 / 2));
-        uint32_t r0[32], r1[32];
-        if (tma_store) {
-          // Drain this warp's share of the accumulator into registers first (converting one
-          // chunk while the next is in flight) and hand the accumulator back; the stores
-          // follow off the critical path.
-          uint32_t pk[4][16];
-          tmem_ld_32x32(src, r0);
+        const int row = m0 + q * 32 + lane;
+#pragma unroll 1
+        for (int ch = 0; ch < BN2 / 32; ch++) {
+          const int col = n0 + ch * 32;
+          if (col >= N) break;
+          uint32_t r[32];
+          tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(half * BN2 + ch * 32), r);
           tmem_ld_wait();
-          tmem_ld_32x32(src + 32, r1);
-          pack(r0, pk[0]);
-          tmem_ld_wait();
-          tmem_ld_32x32(src + 64, r0);
-          pack(r1, pk[1]);
-          tmem_ld_wait();
-          tmem_ld_32x32(src + 96, r1);
-          pack(r0, pk[2]);
-          tmem_ld_wait();
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive_cluster(mapa(tempty_bar(half), 0));
-          pack(r1, pk[3]);
-#pragma unroll
-          for (int c = 0; c < 4; c++) stage_store(pk[c], row0, n0 + 32 * c);
-        } else {
-          tmem_ld_32x32(src, r0);
-          tmem_ld_wait();
-          tmem_ld_32x32(src + 32, r1);
-          store_chunk2<MODE>(ep, r0, row0 + lane, n0, M, N);
-          tmem_ld_wait();
-          tmem_ld_32x32(src + 64, r0);
-          store_chunk2<MODE>(ep, r1, row0 + lane, n0 + 32, M, N);
-          tmem_ld_wait();
-          tmem_ld_32x32(src + 96, r1);
-          store_chunk2<MODE>(ep, r0, row0 + lane, n0 + 64, M, N);
-          tmem_ld_wait();
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive_cluster(mapa(tempty_bar(half), 0));
-          store_chunk2<MODE>(ep, r1, row0 + lane, n0 + 96, M, N);
+          store_chunk2<MODE>(ep, r, row, col, M, N);
         }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(mapa(tempty_bar(half), 0));
       }
       acc_phase ^= 1u;
     }
-    if (lane == 0) bulk_wait_all();  // shared memory must outlive the stores that read it
-    __syncwarp();
   }
 
   tc_fence_before();
@@ -848,16 +666,16 @@ gemm_tc2t_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 }
 
 template <int MODE>
-cudaError_t launch_tc2t(exo_b200_Context* ctx, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc,
-                        int tma_store, int64_t M, int64_t N, int64_t K, const Epi2& ep) {
+cudaError_t launch_tc2t(exo_b200_Context* ctx, const CUtensorMap& ma, const CUtensorMap& mb, int64_t M, int64_t N,
+                        int64_t K, const Epi2& ep) {
   cudaError_t e =
-      cudaFuncSetAttribute(gemm_tc2t_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM2T_BYTES);
+      cudaFuncSetAttribute(gemm_tc2t_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM2_BYTES);
   if (e != cudaSuccess) return e;
   const int64_t tiles_m = (M + 4 * BM - 1) / (4 * BM), tiles_n = (N + BN2 - 1) / BN2;
   if (tiles_m * tiles_n > INT32_MAX || M > INT32_MAX || N > INT32_MAX || K > INT32_MAX) return cudaErrorInvalidValue;
   cudaLaunchConfig_t cfg = {};
-  cfg.blockDim = dim3(THREADS2T);
-  cfg.dynamicSmemBytes = SMEM2T_BYTES;
+  cfg.blockDim = dim3(NUM_THREADS);
+  cfg.dynamicSmemBytes = SMEM2_BYTES;
   cfg.stream = ctx->stream;
   cudaLaunchAttribute attr;
   attr.id = cudaLaunchAttributeClusterDimension;
@@ -877,24 +695,20 @@ cudaError_t launch_tc2t(exo_b200_Context* ctx, const CUtensorMap& ma, const CUte
   const int pairs = (int)std::min<int64_t>(tiles_m * tiles_n, max_clusters);
   cfg.gridDim = dim3(2 * pairs);
   static const int gm = [] {
-    const char* e = getenv("EXOB200_TC2T_GM");
-    return e ? std::max(1, atoi(e)) : 4;
+    const char* e = getenv("EXOB200_TC2T_GM");  // tile rows (of 512) per group
+    return e ? std::max(1, atoi(e)) : 6;
   }();
   static const int skew = [] {
     const char* e = getenv("EXOB200_TC2T_SKEW");
     const int n = e ? atoi(e) : 1;
-    return n >= -1 && n <= TB_STAGES - 2 ? n : 1;
+    return n >= 0 && n <= STAGES2T - 1 ? n : 1;
   }();
   static const int relax = [] {
     const char* e = getenv("EXOB200_TC2T_RELAX");  // ns the producer sleeps between polls (0: spin)
-    return e ? std::max(0, atoi(e)) : 0;
+    return e ? std::max(0, atoi(e)) : 50;
   }();
-  static const int direct = [] {
-    const char* e = getenv("EXOB200_TC2T_DIRECT");  // 1: 16-byte global stores instead of staged TMA stores
-    return e ? atoi(e) : 0;
-  }();
-  return cudaLaunchKernelEx(&cfg, gemm_tc2t_kernel<MODE>, ma, mb, mc, (int)M, (int)N, (int)K, ep, ctx->status_dev,
-                            (int)tiles_m, (int)tiles_n, gm, skew, relax, (tma_store && !direct) ? 1 : 0);
+  return cudaLaunchKernelEx(&cfg, gemm_tc2t_kernel<MODE>, ma, mb, (int)M, (int)N, (int)K, ep, ctx->status_dev,
+                            (int)tiles_m, (int)tiles_n, gm, skew, relax);
 }
 
 template <int MODE>
@@ -980,23 +794,16 @@ cudaError_t launch_gemm_bf16_tc2(exo_b200_Context* ctx, int64_t M, int64_t N, in
   if (!make_tiled_map(&ma, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, A, da, st, boxa)) return cudaErrorUnknown;
   if (!make_tiled_map(&mb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, B, db, st, boxb)) return cudaErrorUnknown;
   Epi2 ep{C, N, 0.f, 0, (N % 8 == 0 && aligned16(C)) ? 1 : 0};
+  // The tall variant (512 x 256 per pair) once every pair gets several such tiles: measured against
+  // the 256 x 256 variant on one GPU, 32768 x 16384 x 8192: +1.4 % for a single cold launch, +2-3 %
+  // over 20 launches, +7 % over 100, +6 % over 400 (1333 against 1255 TFLOP/s; the SM clock settles at
+  // 1395 instead of 1113 MHz under the 1 kW cap).  EXOB200_TC2_TALL=0 / 1 forces the choice.
   static const int tall = [] {
     const char* e = getenv("EXOB200_TC2_TALL");
-    return e ? atoi(e) : 0;
+    return e ? atoi(e) : -1;
   }();
-  if (tall) {
-    // C as 32 x 32 boxes of 64-byte rows for the staged epilogue; needs a 16-byte pitch
-    CUtensorMap mc = ma;
-    const int tma_store = ep.vec_ok;
-    if (tma_store) {
-      cuuint64_t dc[2] = {(cuuint64_t)N, (cuuint64_t)M};
-      cuuint64_t sc[1] = {(cuuint64_t)N * 2};
-      cuuint32_t boxc[2] = {32, 32};
-      if (!make_tiled_map(&mc, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, C, dc, sc, boxc, CU_TENSOR_MAP_SWIZZLE_64B))
-        return cudaErrorUnknown;
-    }
-    return launch_tc2t<M2_BF16>(ctx, ma, mb, mc, tma_store, M, N, K, ep);
-  }
+  const int64_t tall_tiles = ((M + 4 * BM - 1) / (4 * BM)) * ((N + BN2 - 1) / BN2);
+  if (tall == 1 || (tall == -1 && tall_tiles >= 4 * 74)) return launch_tc2t<M2_BF16>(ctx, ma, mb, M, N, K, ep);
   return launch_tc2<M2_BF16>(ctx, ma, mb, M, N, K, ep);
 }
 
