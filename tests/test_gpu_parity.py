@@ -432,6 +432,30 @@ def test_bounded_wait_times_out_and_context_survives(lib):
     assert lib.dll.exo_b200_synchronize(None) == 0
 
 
+def test_gemm_bf16_large_uses_tall_pair_kernel(lib, torch):
+    """Problems with at least 296 tiles of 512 x 256 run on the kernel whose CTA pairs own a
+    512 x 256 tile (two accumulators per CTA sharing each B stage).  Ragged in M, N and K;
+    every element must be written; a row sample (tile and half-tile boundaries, last rows) is
+    checked against float64 within the bf16 tolerance."""
+    M, N, K = 20 * 512 + 130, 16 * 256 + 72, 520
+    A = inputs.normal_bf16(81, (M, K))
+    Bt = inputs.normal_bf16(82, (N, K))
+    dC = torch.full((M, N), 0x7FC0, dtype=torch.int16, device="cuda")  # NaN pattern
+    lib.gemm_bf16_exo(None, M, N, K, dev(torch, A.view(np.int16)), dev(torch, Bt.view(np.int16)), dC)
+    torch.cuda.synchronize()
+    C = dC.cpu().numpy().view(np.uint16)
+    assert not (C == 0x7FC0).any()
+    rows = np.array([0, 127, 128, 255, 256, 383, 384, 511, 512, 5000, 10239, 10240, M - 2, M - 1])
+    ref = inputs.bf16_bits_to_f32(A[rows]).astype(np.float64) @ inputs.bf16_bits_to_f32(Bt).astype(np.float64).T
+    got = inputs.bf16_bits_to_f32(C[rows]).astype(np.float64)
+    assert (np.abs(got - ref) <= 2.0 ** -7 * np.abs(ref) + 1e-3 * np.sqrt(K) * 4e-4).all()
+    # and column samples over every row
+    cols = np.array([0, 255, 256, 4095, 4096, N - 1])
+    refc = inputs.bf16_bits_to_f32(A).astype(np.float64) @ inputs.bf16_bits_to_f32(Bt[cols]).astype(np.float64).T
+    gotc = inputs.bf16_bits_to_f32(C[:, cols]).astype(np.float64)
+    assert (np.abs(gotc - refc) <= 2.0 ** -7 * np.abs(refc) + 1e-3 * np.sqrt(K) * 4e-4).all()
+
+
 # ------------------------------------------------ host-pointer row pipeline
 def test_host_pointer_pipeline_matches_device_pointer_path(lib, torch):
     """Large host-pointer calls run as a chunked copy-in / multiply / copy-out pipeline;
