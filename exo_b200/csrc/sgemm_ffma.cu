@@ -385,12 +385,22 @@ sgemm_gemv_tma_kernel(const __grid_constant__ CUtensorMap tmB, int N, int K, con
       const float* bs = tiles + stage * (GT_KS * GT_W) + tid;
       const int kmax = min(GT_KS, K - st * GT_KS);
       if (kmax == GT_KS) {
+        // Groups of 16 k steps: all of a group's shared-memory loads and shuffles are issued
+        // before its multiply-adds, so the one chain per output waits for a fragment once per
+        // group instead of once per step (the chain itself, 4 clocks per step, is the floor).
 #pragma unroll
-        for (int kk = 0; kk < GT_KS; kk++) {
-          const float b = bs[kk * GT_W];
+        for (int k0 = 0; k0 < GT_KS; k0 += 16) {
+          float bv[16], av[MR][16];
+#pragma unroll
+          for (int j = 0; j < 16; j++) bv[j] = bs[(k0 + j) * GT_W];
 #pragma unroll
           for (int i = 0; i < MR; i++)
-            acc[i] = fmaf(__shfl_sync(0xffffffffu, acur[i][kk >> 5], kk & 31), b, acc[i]);
+#pragma unroll
+            for (int j = 0; j < 16; j++) av[i][j] = __shfl_sync(0xffffffffu, acur[i][(k0 + j) >> 5], (k0 + j) & 31);
+#pragma unroll
+          for (int j = 0; j < 16; j++)
+#pragma unroll
+            for (int i = 0; i < MR; i++) acc[i] = fmaf(av[i][j], bv[j], acc[i]);
         }
       } else {
         for (int kk = 0; kk < kmax; kk++) {  // ragged K tail: no padded steps
