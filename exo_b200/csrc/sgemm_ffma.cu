@@ -299,7 +299,8 @@ sgemm_gemv_kernel(int M, int N, int K, const float* __restrict__ A, const float*
 // unchanged: k ascending, starting from C.
 constexpr int GT_STAGES = 6;
 constexpr int GT_STAGE_BYTES = 16384;  // one box: W columns x (4096 / W) K-rows of fp32
-constexpr int GT_SMEM = GT_STAGES * GT_STAGE_BYTES + 1024 + 128;
+constexpr int GT_A_BYTES = 2 * 2 * 128 * 4;  // per consumer warp (<= 2) and row (<= 2): one stage's A values
+constexpr int GT_SMEM = GT_STAGES * GT_STAGE_BYTES + GT_A_BYTES + 1024 + 128;
 
 // MR = M (1 or 2), unrolled without predicates; W = strip width: 64, or 32 when N
 // is too small to give every SM a 64-column strip.
@@ -318,6 +319,7 @@ sgemm_gemv_tma_kernel(const __grid_constant__ CUtensorMap tmB, int N, int K, con
   auto empty_bar = [&](int s) { return bars + 8u * (GT_STAGES + s); };
   volatile int* abort_flag =
       reinterpret_cast<volatile int*>(gt_raw + (base - raw) + GT_STAGES * GT_STAGE_BYTES + 16 * GT_STAGES);
+  float* a_area = reinterpret_cast<float*>(gt_raw + (base - raw) + GT_STAGES * GT_STAGE_BYTES + 256);
 
   const int tid = threadIdx.x, warp = tid >> 5;
   const int n0 = blockIdx.x * GT_W;
@@ -385,22 +387,37 @@ sgemm_gemv_tma_kernel(const __grid_constant__ CUtensorMap tmB, int N, int K, con
       const float* bs = tiles + stage * (GT_KS * GT_W) + tid;
       const int kmax = min(GT_KS, K - st * GT_KS);
       if (kmax == GT_KS) {
-        // Groups of 16 k steps: all of a group's shared-memory loads and shuffles are issued
-        // before its multiply-adds, so the one chain per output waits for a fragment once per
-        // group instead of once per step (the chain itself, 4 clocks per step, is the floor).
+        // This stage's A values go through a small per-warp area of shared memory: lane l
+        // writes the values it holds, then every lane reads four consecutive k at a time
+        // as one broadcast 128-bit load.  That is 1.25 shared-memory instructions per k
+        // step instead of a load plus a shuffle (the loop is bound by that pipe and by the
+        // 4-clock chain, not by issue slots).
+        float* aw = a_area + warp * (MR * GT_KS);
+        __syncwarp();  // every lane is done with the previous stage's values
+#pragma unroll
+        for (int i = 0; i < MR; i++)
+#pragma unroll
+          for (int h = 0; h < AR; h++) aw[i * GT_KS + h * 32 + lane] = acur[i][h];
+        __syncwarp();
 #pragma unroll
         for (int k0 = 0; k0 < GT_KS; k0 += 16) {
-          float bv[16], av[MR][16];
+          float bv[16];
+          float4 av[MR][4];
 #pragma unroll
           for (int j = 0; j < 16; j++) bv[j] = bs[(k0 + j) * GT_W];
 #pragma unroll
           for (int i = 0; i < MR; i++)
 #pragma unroll
-            for (int j = 0; j < 16; j++) av[i][j] = __shfl_sync(0xffffffffu, acur[i][(k0 + j) >> 5], (k0 + j) & 31);
+            for (int j = 0; j < 4; j++) av[i][j] = *reinterpret_cast<const float4*>(aw + i * GT_KS + k0 + 4 * j);
 #pragma unroll
-          for (int j = 0; j < 16; j++)
+          for (int j = 0; j < 4; j++)
 #pragma unroll
-            for (int i = 0; i < MR; i++) acc[i] = fmaf(av[i][j], bv[j], acc[i]);
+            for (int i = 0; i < MR; i++) {
+              acc[i] = fmaf(av[i][j].x, bv[4 * j + 0], acc[i]);
+              acc[i] = fmaf(av[i][j].y, bv[4 * j + 1], acc[i]);
+              acc[i] = fmaf(av[i][j].z, bv[4 * j + 2], acc[i]);
+              acc[i] = fmaf(av[i][j].w, bv[4 * j + 3], acc[i]);
+            }
         }
       } else {
         for (int kk = 0; kk < kmax; kk++) {  // ragged K tail: no padded steps
