@@ -122,8 +122,6 @@ struct RowPipeline {
   size_t c_row_bytes;
   bool c_is_input;         // C is read by the kernel (C += ...): copy it in too
 };
-template <class Launch>
-bool run_row_pipeline(exo_b200_Context* c, const RowPipeline& p, Launch launch);
 bool pipeline_prepare(exo_b200_Context* c, size_t a_chunk_bytes, size_t c_chunk_bytes);
 
 // The same idea in two dimensions, for products whose second operand is also on the
@@ -149,7 +147,24 @@ bool block_pipeline_prepare(exo_b200_Context* c, size_t a_bytes, size_t b_bytes,
 std::vector<char> block_upload_order(const BlockPipeline& p);
 
 template <class Launch>
+bool run_block_pipeline_impl(exo_b200_Context* c, const BlockPipeline& p, Launch launch);
+template <class Launch>
 bool run_block_pipeline(exo_b200_Context* c, const BlockPipeline& p, Launch launch) {
+  if (run_block_pipeline_impl(c, p, launch)) return true;
+  const int code = last_error_code();
+  const std::string msg = last_error_msg();
+  cudaStreamSynchronize(c->stream);
+  if (c->pipe_ready) {
+    cudaStreamSynchronize(c->pipe_in);
+    cudaStreamSynchronize(c->pipe_out);
+  }
+  cudaGetLastError();
+  set_error(code, msg);
+  return false;
+}
+
+template <class Launch>
+bool run_block_pipeline_impl(exo_b200_Context* c, const BlockPipeline& p, Launch launch) {
   const int64_t na = (p.rows + p.chunk_rows - 1) / p.chunk_rows, nb = (p.cols + p.chunk_cols - 1) / p.chunk_cols;
   const size_t blk_bytes = (size_t)p.chunk_rows * p.chunk_cols * p.c_elem_bytes;
   if (!block_pipeline_prepare(c, (size_t)p.rows * p.a_row_bytes, (size_t)p.cols * p.b_col_bytes, blk_bytes))
@@ -213,12 +228,39 @@ bool run_block_pipeline(exo_b200_Context* c, const BlockPipeline& p, Launch laun
   }
   if (!check_cuda(cudaStreamSynchronize(c->pipe_out), "cudaStreamSynchronize")) return false;
   if (!check_cuda(cudaStreamSynchronize(c->pipe_in), "cudaStreamSynchronize")) return false;
-  return nblk == na * nb;
+  if (nblk != na * nb) {
+    set_error(EXO_B200_ERR_CUDA, "block pipeline: not every output block was scheduled");
+    return false;
+  }
+  return true;
 }
 
 
+// On any failure the copies already enqueued may still be writing the caller's buffers:
+// drain the three streams before reporting it.
+inline void pipeline_drain(exo_b200_Context* c) {
+  if (c->pipe_ready) {
+    cudaStreamSynchronize(c->pipe_in);
+    cudaStreamSynchronize(c->pipe_out);
+  }
+  cudaStreamSynchronize(c->stream);
+}
+
+template <class Launch>
+bool run_row_pipeline_impl(exo_b200_Context* c, const RowPipeline& p, Launch launch);
 template <class Launch>
 bool run_row_pipeline(exo_b200_Context* c, const RowPipeline& p, Launch launch) {
+  if (run_row_pipeline_impl(c, p, launch)) return true;
+  const int code = last_error_code();
+  const std::string msg = last_error_msg();
+  pipeline_drain(c);
+  cudaGetLastError();
+  set_error(code, msg);
+  return false;
+}
+
+template <class Launch>
+bool run_row_pipeline_impl(exo_b200_Context* c, const RowPipeline& p, Launch launch) {
   const size_t a_chunk = (size_t)p.chunk_rows * p.a_row_bytes, c_chunk = (size_t)p.chunk_rows * p.c_row_bytes;
   if (!pipeline_prepare(c, a_chunk, c_chunk)) return false;
   // everything enqueued on c->stream so far (the staged B operand) must be in place first
