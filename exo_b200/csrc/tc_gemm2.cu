@@ -26,6 +26,7 @@
 #include <cuda_bf16.h>
 
 #include <algorithm>
+#include <atomic>
 #include <cstdlib>
 
 #include "i8_epilogue.cuh"
@@ -684,15 +685,15 @@ cudaError_t launch_tc2t(exo_b200_Context* ctx, const CUtensorMap& ma, const CUte
   attr.val.clusterDim.z = 1;
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
-  static int max_clusters = 0;
-  if (max_clusters == 0) {
+  static std::atomic<int> max_clusters{0};  // same value whichever thread gets here first
+  if (max_clusters.load() == 0) {
     cfg.gridDim = dim3(2 * ctx->sm_count);
     int n = 0;
     e = cudaOccupancyMaxActiveClusters(&n, gemm_tc2t_kernel<MODE>, &cfg);
     if (e != cudaSuccess) return e;
-    max_clusters = std::max(1, n);
+    max_clusters.store(std::max(1, n));
   }
-  const int pairs = (int)std::min<int64_t>(tiles_m * tiles_n, max_clusters);
+  const int pairs = (int)std::min<int64_t>(tiles_m * tiles_n, max_clusters.load());
   cfg.gridDim = dim3(2 * pairs);
   static const int gm = [] {
     const char* e = getenv("EXOB200_TC2T_GM");  // tile rows (of 512) per group
@@ -732,15 +733,15 @@ cudaError_t launch_tc2(exo_b200_Context* ctx, const CUtensorMap& ma, const CUten
   attr.val.clusterDim.z = 1;
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
-  static int max_clusters = 0;
-  if (max_clusters == 0) {
+  static std::atomic<int> max_clusters{0};  // same value whichever thread gets here first
+  if (max_clusters.load() == 0) {
     cfg.gridDim = dim3(2 * ctx->sm_count);
     int n = 0;
     e = cudaOccupancyMaxActiveClusters(&n, gemm_tc2_kernel<MODE>, &cfg);
     if (e != cudaSuccess) return e;
-    max_clusters = std::max(1, n);
+    max_clusters.store(std::max(1, n));
   }
-  const int pairs = (int)std::min<int64_t>(tiles_m * tiles_n, max_clusters);
+  const int pairs = (int)std::min<int64_t>(tiles_m * tiles_n, max_clusters.load());
   cfg.gridDim = dim3(2 * pairs);
   static const int gm = [] {
     const char* e = getenv("EXOB200_TC2_GM");
