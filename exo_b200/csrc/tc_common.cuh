@@ -2,6 +2,7 @@
 // constants, the bounded-wait bookkeeping, the TF32 split, and the host-side
 // tensor-map encoder.
 #pragma once
+#include <cstdlib>
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -72,9 +73,17 @@ inline bool make_tiled_map(CUtensorMap* m, CUtensorMapDataType dt, int rank, con
     return false;
   }
   cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  // EXOB200_L2_PROMOTION=0|64|128|256: how much L2 fetches from DRAM around a missing line (experiments)
+  static const CUtensorMapL2promotion promo = [] {
+    const char* e = getenv("EXOB200_L2_PROMOTION");
+    const int v = e ? atoi(e) : 256;
+    return v == 0     ? CU_TENSOR_MAP_L2_PROMOTION_NONE
+           : v == 64  ? CU_TENSOR_MAP_L2_PROMOTION_L2_64B
+           : v == 128 ? CU_TENSOR_MAP_L2_PROMOTION_L2_128B
+                      : CU_TENSOR_MAP_L2_PROMOTION_L2_256B;
+  }();
   CUresult r = fn(m, dt, (cuuint32_t)rank, const_cast<void*>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, promo, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     set_error(EXO_B200_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult " + std::to_string((int)r));
     return false;
