@@ -439,16 +439,33 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 //
 // More elaborate versions were built and measured slower than this one: separate
 // rings for A0, A1 and B (more barrier waits and commits per k-block for the one
-// issuing thread), eight epilogue warps with staged TMA stores, and orders of the
-// MMAs that change accumulator less often.
+// issuing thread), eight epilogue warps, and orders of the MMAs that change
+// accumulator less often.
 constexpr int STAGE2T_BYTES = 2 * A_TILE_BYTES + BHALF * ROW_BYTES;  // 48 KiB per CTA
 constexpr int STAGES2T = 4;
 static_assert(STAGES2T * STAGE2T_BYTES <= STAGES2 * STAGE2_BYTES, "tall ring must fit the same allocation");
+// Epilogue staging for TMA stores: per epilogue warp two buffers of 32 rows x 64 bytes, behind the control block.
+constexpr int T_STAGING_OFFSET = STAGES2 * STAGE2_BYTES + 1024;
+constexpr int T_STAGING_BYTES = 4 * 2 * 2048;
+constexpr int SMEM2T_BYTES = T_STAGING_OFFSET + T_STAGING_BYTES + 1024;
+static_assert(SMEM2T_BYTES <= 232448, "exceeds the shared memory a CTA can opt in to");
+
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, uint32_t src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(m)),
+               "r"(src), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// all but the most recent bulk store of this thread have finished READING shared memory
+__device__ __forceinline__ void bulk_wait_read_1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
 template <int MODE>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-gemm_tc2t_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, int M, int N, int K,
-                 Epi2 ep, DeviceStatus* status, int tiles_m, int tiles_n, int GM, int skew, int relax) {
+gemm_tc2t_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const __grid_constant__ CUtensorMap tmC, int M, int N, int K, Epi2 ep, DeviceStatus* status,
+                 int tiles_m, int tiles_n, int GM, int skew, int relax, int tma_store) {
   using C = Cfg2<MODE>;
   constexpr int BK = ROW_BYTES / C::ELEM;
   constexpr uint32_t IDESC =
@@ -487,6 +504,7 @@ gemm_tc2t_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     fence_proxy_async();
     prefetch_tensormap(&tmA);
     prefetch_tensormap(&tmB);
+    prefetch_tensormap(&tmC);
   }
   if (warp == 1) {
     tmem_alloc2(smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM2_COLS);
@@ -628,6 +646,38 @@ gemm_tc2t_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int q = warp & 3;
     uint32_t acc_phase = 0;
     bool ok = true;
+    // Output through shared memory and TMA stores (bf16, 16-byte pitch): a warp's 32 x 32 chunk is
+    // written as whole 64-byte rows by the copy engine instead of as 16-byte pieces of 32 different
+    // lines per store instruction; the engine clips at the edges of C.  Two staging buffers per
+    // warp, 64-byte swizzle so that the 128-bit shared-memory writes are conflict free.
+    const uint32_t stg = tiles + T_STAGING_OFFSET + (uint32_t)(warp - 2) * 4096u;
+    int stg_buf = 0;
+    auto stage_store = [&](const uint32_t (&r)[32], int row0, int col) {
+      if (row0 >= M || col >= N) return;  // warp-uniform
+      if (lane == 0) bulk_wait_read_1();  // the store that last used this buffer has read it
+      __syncwarp();
+      const uint32_t buf = stg + (uint32_t)stg_buf * 2048u;
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+          const __nv_bfloat162 h =
+              __floats2bfloat162_rn(__uint_as_float(r[j * 8 + 2 * i]), __uint_as_float(r[j * 8 + 2 * i + 1]));
+          w[i] = *reinterpret_cast<const uint32_t*>(&h);
+        }
+        const uint32_t dst = buf + (uint32_t)lane * 64u + (uint32_t)((j ^ ((lane >> 1) & 3)) * 16);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3])
+                     : "memory");
+      }
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) {
+        tma_store_2d(&tmC, buf, col, row0);
+        bulk_commit();
+      }
+      stg_buf ^= 1;
+    };
     for (int t = pair; t < num_tiles && ok; t += num_pairs) {
       int tm, tn;
       tile_coord(t, tm, tn);
@@ -648,7 +698,10 @@ gemm_tc2t_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           uint32_t r[32];
           tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(half * BN2 + ch * 32), r);
           tmem_ld_wait();
-          store_chunk2<MODE>(ep, r, row, col, M, N);
+          if (MODE == M2_BF16 && tma_store)
+            stage_store(r, m0 + q * 32, col);
+          else
+            store_chunk2<MODE>(ep, r, row, col, M, N);
         }
         tc_fence_before();
         __syncwarp();
@@ -656,6 +709,8 @@ gemm_tc2t_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
       acc_phase ^= 1u;
     }
+    if (lane == 0) bulk_wait_all();  // shared memory must outlive the stores that read it
+    __syncwarp();
   }
 
   tc_fence_before();
@@ -667,16 +722,16 @@ gemm_tc2t_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 }
 
 template <int MODE>
-cudaError_t launch_tc2t(exo_b200_Context* ctx, const CUtensorMap& ma, const CUtensorMap& mb, int64_t M, int64_t N,
-                        int64_t K, const Epi2& ep) {
+cudaError_t launch_tc2t(exo_b200_Context* ctx, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc,
+                        int tma_store, int64_t M, int64_t N, int64_t K, const Epi2& ep) {
   cudaError_t e =
-      cudaFuncSetAttribute(gemm_tc2t_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM2_BYTES);
+      cudaFuncSetAttribute(gemm_tc2t_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM2T_BYTES);
   if (e != cudaSuccess) return e;
   const int64_t tiles_m = (M + 4 * BM - 1) / (4 * BM), tiles_n = (N + BN2 - 1) / BN2;
   if (tiles_m * tiles_n > INT32_MAX || M > INT32_MAX || N > INT32_MAX || K > INT32_MAX) return cudaErrorInvalidValue;
   cudaLaunchConfig_t cfg = {};
   cfg.blockDim = dim3(NUM_THREADS);
-  cfg.dynamicSmemBytes = SMEM2_BYTES;
+  cfg.dynamicSmemBytes = SMEM2T_BYTES;
   cfg.stream = ctx->stream;
   cudaLaunchAttribute attr;
   attr.id = cudaLaunchAttributeClusterDimension;
@@ -708,8 +763,12 @@ cudaError_t launch_tc2t(exo_b200_Context* ctx, const CUtensorMap& ma, const CUte
     const char* e = getenv("EXOB200_TC2T_RELAX");  // ns the producer sleeps between polls (0: spin)
     return e ? std::max(0, atoi(e)) : 50;
   }();
-  return cudaLaunchKernelEx(&cfg, gemm_tc2t_kernel<MODE>, ma, mb, (int)M, (int)N, (int)K, ep, ctx->status_dev,
-                            (int)tiles_m, (int)tiles_n, gm, skew, relax);
+  static const int direct = [] {
+    const char* e = getenv("EXOB200_TC2T_DIRECT");  // 1: 16-byte global stores instead of staged TMA stores
+    return e ? atoi(e) : 0;
+  }();
+  return cudaLaunchKernelEx(&cfg, gemm_tc2t_kernel<MODE>, ma, mb, mc, (int)M, (int)N, (int)K, ep, ctx->status_dev,
+                            (int)tiles_m, (int)tiles_n, gm, skew, relax, (tma_store && !direct) ? 1 : 0);
 }
 
 template <int MODE>
@@ -804,7 +863,19 @@ cudaError_t launch_gemm_bf16_tc2(exo_b200_Context* ctx, int64_t M, int64_t N, in
     return e ? atoi(e) : -1;
   }();
   const int64_t tall_tiles = ((M + 4 * BM - 1) / (4 * BM)) * ((N + BN2 - 1) / BN2);
-  if (tall == 1 || (tall == -1 && tall_tiles >= 4 * 74)) return launch_tc2t<M2_BF16>(ctx, ma, mb, M, N, K, ep);
+  if (tall == 1 || (tall == -1 && tall_tiles >= 4 * 74)) {
+    // C as 32 x 32 boxes of 64-byte rows for the staged epilogue; needs a 16-byte pitch and base
+    CUtensorMap mc = ma;
+    const int tma_store = ep.vec_ok;
+    if (tma_store) {
+      cuuint64_t dc[2] = {(cuuint64_t)N, (cuuint64_t)M};
+      cuuint64_t sc[1] = {(cuuint64_t)N * 2};
+      cuuint32_t boxc[2] = {32, 32};
+      if (!make_tiled_map(&mc, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, C, dc, sc, boxc, CU_TENSOR_MAP_SWIZZLE_64B))
+        return cudaErrorUnknown;
+    }
+    return launch_tc2t<M2_BF16>(ctx, ma, mb, mc, tma_store, M, N, K, ep);
+  }
   return launch_tc2<M2_BF16>(ctx, ma, mb, M, N, K, ep);
 }
 
