@@ -265,8 +265,8 @@ cudaError_t launch_tiles_h(cudaStream_t stream, const Policy& P) {
   return cudaGetLastError();
 }
 
-// 128 x 128 tiles unless they would leave most SMs without work; 32 x 32 when even
-// 64 x 64 tiles would.  128 x 64 tiles when the last wave of 128 x 128 tiles would be
+// 128 x 128 tiles unless they would leave more than half of the SMs without work; 32 x 32
+// when even 64 x 64 tiles would leave SMs idle.  128 x 64 tiles when the last wave of 128 x 128 tiles would be
 // less than half full (two resident CTAs per SM): the tail then costs half a tile time.
 template <class Policy>
 cudaError_t launch_tiles(cudaStream_t stream, const Policy& P, int sm_count = 148) {
@@ -279,11 +279,15 @@ cudaError_t launch_tiles(cudaStream_t stream, const Policy& P, int sm_count = 14
   int tile;
   if (force == 32 || force == 64 || force == 128 || force == 12864) {
     tile = force;
-  } else if (big_tiles > sm_count) {
+  } else if (big_tiles > sm_count || (big_tiles > sm_count / 2 && P.N > 64)) {  // N <= 64 would waste half of a 128-wide tile
+    // From half an SM count of 128 x 128 tiles on, they beat four times as many 64 x 64 tiles
+    // (1536^3, 144 tiles: 171 against 222 us; 1024^3, 64 tiles: 117 against 78 us): a lone
+    // 128 x 128 CTA takes ~112 ns per k step, two co-resident 64 x 64 CTAs ~75 ns, and more
+    // than 296 of the small ones need a second round.
     const int64_t slots = 2 * (int64_t)sm_count, tail = big_tiles % slots;
     // measured: 324 tiles 578 -> 517 us, 313 tiles 332 -> 299 us; but 1024 tiles (tail 136) 2564 -> 2654 us:
     // after a few waves the CTAs have drifted apart and the half tiles' ~4 % lower efficiency is all that is left
-    tile = (big_tiles < 2 * slots && tail != 0 && tail <= slots / 2) ? 12864 : 128;
+    tile = (big_tiles > slots && big_tiles < 2 * slots && tail <= slots / 2) ? 12864 : 128;
   } else {
     tile = mid_tiles > sm_count ? 64 : 32;
   }
