@@ -446,7 +446,9 @@ constexpr int STAGES2T = 4;
 static_assert(STAGES2T * STAGE2T_BYTES <= STAGES2 * STAGE2_BYTES, "tall ring must fit the same allocation");
 // Epilogue staging for TMA stores: per epilogue warp two buffers of 32 rows x 64 bytes, behind the control block.
 constexpr int T_STAGING_OFFSET = STAGES2 * STAGE2_BYTES + 1024;
-constexpr int T_STAGING_BYTES = 4 * 2 * 2048;
+constexpr int T_EPI_WARPS = 8;  // two per tensor-memory lane quarter: each takes half of the tile's columns
+constexpr int THREADS2T = 32 * (2 + T_EPI_WARPS);
+constexpr int T_STAGING_BYTES = T_EPI_WARPS * 2 * 2048;
 constexpr int SMEM2T_BYTES = T_STAGING_OFFSET + T_STAGING_BYTES + 1024;
 static_assert(SMEM2T_BYTES <= 232448, "exceeds the shared memory a CTA can opt in to");
 
@@ -462,7 +464,7 @@ __device__ __forceinline__ void bulk_wait_read_1() { asm volatile("cp.async.bulk
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
 template <int MODE>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__global__ void __launch_bounds__(THREADS2T, 1)
 gemm_tc2t_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmC, int M, int N, int K, Epi2 ep, DeviceStatus* status,
                  int tiles_m, int tiles_n, int GM, int skew, int relax, int tma_store) {
@@ -497,7 +499,7 @@ gemm_tc2t_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
     for (int b = 0; b < 2; b++) {
       mbar_init(tfull_bar(b), 1);
-      mbar_init(tempty_bar(b), 8);  // four epilogue warps in each CTA of the pair
+      mbar_init(tempty_bar(b), 2 * T_EPI_WARPS);  // the epilogue warps of both CTAs of the pair
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -642,8 +644,9 @@ gemm_tc2t_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
     __syncwarp();
   } else {
-    // ------------------------------------------------ epilogue warps 2..5 (both CTAs)
-    const int q = warp & 3;
+    // ------------------------------------------------ epilogue warps 2..9 (both CTAs)
+    // warp w may read tensor-memory lanes 32 (w % 4) .. + 31; the two warps of a lane quarter split the columns
+    const int q = warp & 3, part = (warp - 2) >> 2;
     uint32_t acc_phase = 0;
     bool ok = true;
     // Output through shared memory and TMA stores (bf16, 16-byte pitch): a warp's 32 x 32 chunk is
@@ -691,21 +694,30 @@ gemm_tc2t_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
         tc_fence_after();
         const int row = m0 + q * 32 + lane;
-#pragma unroll 1
-        for (int ch = 0; ch < BN2 / 32; ch++) {
-          const int col = n0 + ch * 32;
-          if (col >= N) break;
-          uint32_t r[32];
-          tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(half * BN2 + ch * 32), r);
-          tmem_ld_wait();
-          if (MODE == M2_BF16 && tma_store)
-            stage_store(r, m0 + q * 32, col);
-          else
-            store_chunk2<MODE>(ep, r, row, col, M, N);
-        }
+        const int c0 = n0 + part * (BN2 / 2);
+        const uint32_t src = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(half * BN2 + part * (BN2 / 2));
+        // this warp's four 32-column chunks: all loads in flight at once, then the accumulator
+        // goes back to the MMA thread; conversion and stores follow off the critical path
+        uint32_t r0[32], r1[32], r2[32], r3[32];
+        tmem_ld_32x32(src, r0);
+        tmem_ld_32x32(src + 32, r1);
+        tmem_ld_32x32(src + 64, r2);
+        tmem_ld_32x32(src + 96, r3);
+        tmem_ld_wait();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(mapa(tempty_bar(half), 0));
+        if (MODE == M2_BF16 && tma_store) {
+          stage_store(r0, m0 + q * 32, c0);
+          stage_store(r1, m0 + q * 32, c0 + 32);
+          stage_store(r2, m0 + q * 32, c0 + 64);
+          stage_store(r3, m0 + q * 32, c0 + 96);
+        } else {
+          store_chunk2<MODE>(ep, r0, row, c0, M, N);
+          store_chunk2<MODE>(ep, r1, row, c0 + 32, M, N);
+          store_chunk2<MODE>(ep, r2, row, c0 + 64, M, N);
+          store_chunk2<MODE>(ep, r3, row, c0 + 96, M, N);
+        }
       }
       acc_phase ^= 1u;
     }
@@ -730,7 +742,7 @@ cudaError_t launch_tc2t(exo_b200_Context* ctx, const CUtensorMap& ma, const CUte
   const int64_t tiles_m = (M + 4 * BM - 1) / (4 * BM), tiles_n = (N + BN2 - 1) / BN2;
   if (tiles_m * tiles_n > INT32_MAX || M > INT32_MAX || N > INT32_MAX || K > INT32_MAX) return cudaErrorInvalidValue;
   cudaLaunchConfig_t cfg = {};
-  cfg.blockDim = dim3(NUM_THREADS);
+  cfg.blockDim = dim3(THREADS2T);
   cfg.dynamicSmemBytes = SMEM2T_BYTES;
   cfg.stream = ctx->stream;
   cudaLaunchAttribute attr;
