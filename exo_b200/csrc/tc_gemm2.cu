@@ -439,8 +439,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 //
 // More elaborate versions were built and measured slower than this one: separate
 // rings for A0, A1 and B (more barrier waits and commits per k-block for the one
-// issuing thread), eight epilogue warps, and orders of the MMAs that change
-// accumulator less often.
+// issuing thread) and other orders of the two halves' MMAs.
 constexpr int STAGE2T_BYTES = 2 * A_TILE_BYTES + BHALF * ROW_BYTES;  // 48 KiB per CTA
 constexpr int STAGES2T = 4;
 static_assert(STAGES2T * STAGE2T_BYTES <= STAGES2 * STAGE2_BYTES, "tall ring must fit the same allocation");
