@@ -32,9 +32,11 @@ def _is_torch(x) -> bool:
     return type(x).__module__.startswith("torch") and hasattr(x, "data_ptr")
 
 
-def _convert(arg, argtype):
+def _convert(arg, argtype, keepalive):
     """One argument, the way ProcWrapper._convert does it, plus torch tensors,
-    Python floats for by-pointer scalars, and Context objects."""
+    Python floats for by-pointer scalars, and Context objects.  Temporaries that
+    the C call reads through a pointer are appended to ``keepalive``, which the
+    caller owns until the C function has returned."""
     if arg is None:
         return None
     if isinstance(arg, Context):
@@ -54,7 +56,7 @@ def _convert(arg, argtype):
     if isinstance(arg, float) and argtype is _lib.vp:
         # numeric scalars travel by pointer in Exo's ABI
         holder = np.array([arg], np.float32)
-        _convert.keepalive = holder
+        keepalive.append(holder)
         return ctypes.c_void_p(holder.ctypes.data)
     raise ValueError(f"unrecognized type {type(arg)}")
 
@@ -90,8 +92,10 @@ class ProcWrapper:
                 self._dll.exo_b200_set_default_stream(stream)
         elif ctx is None:
             self._dll.exo_b200_set_default_stream(None)
-        conv = [_convert(a, t) for a, t in zip(args, self._argtypes)]
+        keepalive = []  # per call, so concurrent callers cannot free each other's scalars
+        conv = [_convert(a, t, keepalive) for a, t in zip(args, self._argtypes)]
         self._fn(*conv)
+        del keepalive
         code = self._dll.exo_b200_last_error()
         if code != OK:
             raise ExoB200Error(code, self._dll.exo_b200_last_error_string().decode())

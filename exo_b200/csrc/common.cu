@@ -1,5 +1,6 @@
 // Context management, thread-local error state and host<->device staging.
 #include "common.cuh"
+#include "kernels.cuh"
 
 #include <cstdio>
 #include <cstdlib>
@@ -90,13 +91,28 @@ exo_b200_Context* default_context() {
   return it->second;
 }
 
-ContextUse::ContextUse(exo_b200_Context* c) : c_(c) {
+// A context belongs to one device: its stream, staging, scratch and SM count are that
+// device's.  If another device is current when an entry point is called, the context's
+// device is made current for the length of the call and the caller's choice restored
+// afterwards; if that fails the call is refused (get() returns nullptr, error set).
+ContextUse::ContextUse(exo_b200_Context* c) : c_(c), restore_device_(-1) {
   if (!c_) return;
   c_->mutex->lock();
   if (c_->is_default) c_->stream = tl_default_stream;
+  int cur = -1;
+  if (cudaGetDevice(&cur) == cudaSuccess && cur != c_->device) {
+    if (!check_cuda(cudaSetDevice(c_->device), "cudaSetDevice(context's device)")) {
+      c_->mutex->unlock();
+      c_ = nullptr;
+      return;
+    }
+    restore_device_ = cur;
+  }
 }
 ContextUse::~ContextUse() {
-  if (c_) c_->mutex->unlock();
+  if (!c_) return;
+  if (restore_device_ >= 0) cudaSetDevice(restore_device_);
+  c_->mutex->unlock();
 }
 
 exo_b200_Context* resolve_context(void* ctxt) {
@@ -119,10 +135,33 @@ bool is_device_pointer(const void* p) {
   return attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged;
 }
 
+int owning_device(const void* p) {
+  cudaPointerAttributes attr;
+  if (cudaPointerGetAttributes(&attr, p) != cudaSuccess) {
+    cudaGetLastError();
+    return -1;
+  }
+  return attr.type == cudaMemoryTypeDevice ? attr.device : -1;
+}
+
 bool stage_in(exo_b200_Context* c, int slot, const void* user, size_t bytes, bool copy_in, Operand* op) {
   op->user = user;
   op->bytes = bytes;
-  if (is_device_pointer(user)) {
+  cudaPointerAttributes attr;
+  bool on_device = false;
+  if (cudaPointerGetAttributes(&attr, user) == cudaSuccess) {
+    on_device = attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged;
+    if (attr.type == cudaMemoryTypeDevice && attr.device != c->device) {
+      // the kernels run on the context's device and would dereference memory of another GPU
+      set_error(EXO_B200_ERR_INVALID_ARGUMENT,
+                "a device pointer belongs to device " + std::to_string(attr.device) + " but the context is on device " +
+                    std::to_string(c->device));
+      return false;
+    }
+  } else {
+    cudaGetLastError();  // unregistered host memory on old drivers: clear and treat as host
+  }
+  if (on_device) {
     op->dev = const_cast<void*>(user);
     op->staged = false;
     return true;
@@ -265,9 +304,43 @@ std::vector<char> block_upload_order(const BlockPipeline& p) {
   return order;
 }
 
+bool acquire_scratch(exo_b200_Context* c, int slot, size_t bytes) {
+  if (!ensure_scratch(c, slot, bytes)) return false;
+  if (c->scratch_busy[slot] && c->scratch_stream[slot] != c->stream) {
+    // cudaStreamWaitEvent on an event that has completed costs nothing on the device
+    if (!check_cuda(cudaStreamWaitEvent(c->stream, c->scratch_ev[slot], 0), "cudaStreamWaitEvent(scratch)"))
+      return false;
+  }
+  return true;
+}
+
+void release_scratch(exo_b200_Context* c, int slot) {
+  // An event recorded while the stream is being captured belongs to the capture and cannot be
+  // waited on from outside it; a capturing caller orders its own streams.
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(c->stream, &cap) != cudaSuccess) {
+    cudaGetLastError();
+    return;
+  }
+  if (cap != cudaStreamCaptureStatusNone) return;
+  if (!c->scratch_ev[slot] &&
+      cudaEventCreateWithFlags(&c->scratch_ev[slot], cudaEventDisableTiming) != cudaSuccess) {
+    cudaGetLastError();
+    c->scratch_ev[slot] = nullptr;
+    return;
+  }
+  if (cudaEventRecord(c->scratch_ev[slot], c->stream) != cudaSuccess) {
+    cudaGetLastError();
+    return;
+  }
+  c->scratch_stream[slot] = c->stream;
+  c->scratch_busy[slot] = true;
+}
+
 bool ensure_scratch(exo_b200_Context* c, int slot, size_t bytes) {
   if (c->scratch_bytes[slot] >= bytes) return true;
   if (c->scratch[slot]) {
+    // cudaFree waits for all work on the device, other streams' readers of the slot included
     if (!check_cuda(cudaStreamSynchronize(c->stream), "cudaStreamSynchronize")) return false;
     cudaFree(c->scratch[slot]);
     c->scratch[slot] = nullptr;
@@ -293,11 +366,16 @@ exo_b200_Context* exo_b200_context_create(int device, void* stream) {
 void exo_b200_context_destroy(exo_b200_Context* c) {
   if (!c || c->magic != kContextMagic) return;
   c->mutex->lock();  // waits for a call in flight on another thread
+  int cur = -1;
+  cudaGetDevice(&cur);
+  if (cur != c->device) cudaSetDevice(c->device);  // streams, events and allocations are this device's
   cudaStreamSynchronize(c->stream);
   for (int i = 0; i < 4; i++)
     if (c->stage[i]) cudaFree(c->stage[i]);
-  for (int i = 0; i < 2; i++)
+  for (int i = 0; i < 2; i++) {
     if (c->scratch[i]) cudaFree(c->scratch[i]);
+    if (c->scratch_ev[i]) cudaEventDestroy(c->scratch_ev[i]);
+  }
   if (c->status_host) cudaFreeHost(c->status_host);
   if (c->pipe_ready) {
     cudaStreamDestroy(c->pipe_in);
@@ -321,6 +399,7 @@ void exo_b200_context_destroy(exo_b200_Context* c) {
   for (int i = 0; i < 4; i++)
     if (c->blk_c[i]) cudaFree(c->blk_c[i]);
   c->magic = 0;
+  if (cur >= 0 && cur != c->device) cudaSetDevice(cur);
   c->mutex->unlock();
   delete c->mutex;
   delete c;
@@ -345,7 +424,8 @@ int exo_b200_synchronize(exo_b200_Context* ctxt) {
   ContextUse use(resolve_context(ctxt));
   exo_b200_Context* c = use.get();
   if (!c) return exo_b200_last_error();
-  if (check_cuda(cudaStreamSynchronize(c->stream), "cudaStreamSynchronize")) read_status(c);
+  if (check_cuda(cudaStreamSynchronize(c->stream), "cudaStreamSynchronize") && read_status(c))
+    collect_static_status();
   return exo_b200_last_error();
 }
 

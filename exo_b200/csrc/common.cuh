@@ -37,6 +37,14 @@ struct exo_b200_Context {
   // device scratch for kernels that need it (repacked operands)
   void* scratch[2];
   size_t scratch_bytes[2];
+  // Each scratch slot remembers the stream of its last user and an event recorded after the
+  // last kernel that reads it, so that a call on ANOTHER stream waits for that reader before
+  // its pre-pass overwrites the slot (calls on one stream are ordered anyway).
+  cudaEvent_t scratch_ev[2];
+  cudaStream_t scratch_stream[2];
+  bool scratch_busy[2];
+  // resident CTA pairs of the two cluster kernels on this context's device (0 = not asked yet)
+  int max_pairs[4];
   exob200::DeviceStatus* status_dev;   // device word
   exob200::DeviceStatus* status_host;  // pinned mirror
   // host-pointer row pipeline: copy-in / copy-out streams, two chunk buffers each way
@@ -82,10 +90,13 @@ class ContextUse {
 
  private:
   exo_b200_Context* c_;
+  int restore_device_;  // >= 0: the device that was current before this call
 };
 
 // true if p is device-accessible memory (device or managed allocation)
 bool is_device_pointer(const void* p);
+// Device ordinal that owns p if p is a plain device allocation, -1 otherwise (host, managed, unknown).
+int owning_device(const void* p);
 
 // One operand of a call.  For host memory, `dev` points into the context's
 // staging area; inputs are copied in before the launch, outputs copied back
@@ -105,6 +116,11 @@ bool stage_out(exo_b200_Context* c, const Operand& op);
 bool finish(exo_b200_Context* c, bool any_staged);
 
 bool ensure_scratch(exo_b200_Context* c, int slot, size_t bytes);
+// Scratch slot `slot`, at least `bytes` large, safe to overwrite from c->stream: if the slot's
+// last reader ran on a different stream, c->stream is made to wait for it first.
+bool acquire_scratch(exo_b200_Context* c, int slot, size_t bytes);
+// To be called after the last kernel that reads the slot has been enqueued on c->stream.
+void release_scratch(exo_b200_Context* c, int slot);
 
 // Host-pointer calls whose output rows depend only on the matching rows of one
 // input (GEMM: C rows <- A rows) are run as a pipeline over row chunks: while

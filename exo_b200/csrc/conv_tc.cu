@@ -394,9 +394,7 @@ bool make_input_map(CUtensorMap* m, CUtensorMapDataType dt, int elem, const void
 template <int MODE, int BN>
 cudaError_t launch_conv(exo_b200_Context* ctx, const CUtensorMap& a0, const CUtensorMap& a1, const CUtensorMap& b0,
                         const CUtensorMap& b1, ConvTcParams p) {
-  cudaError_t e = cudaFuncSetAttribute(conv_tc_kernel<MODE, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       conv_smem_bytes<MODE, BN>());
-  if (e != cudaSuccess) return e;
+  EXOB200_SMEM_ATTR_ONCE((conv_tc_kernel<MODE, BN>), (conv_smem_bytes<MODE, BN>()), ctx->device);
   p.tiles_n = (p.co + BN - 1) / BN;
   const int64_t num_tiles = (int64_t)p.batch * p.tiles_h * p.tiles_w * p.tiles_n;
   if (num_tiles > INT32_MAX) return cudaErrorInvalidValue;
@@ -464,8 +462,8 @@ cudaError_t launch_conv_3xtf32_tc(exo_b200_Context* ctx, const ConvShape& s, con
   const int64_t K = (int64_t)s.kdim * s.kdim * s.in_c;
   const int64_t Kp = (K + 3) / 4 * 4;
   const int64_t w_elems = (int64_t)s.out_c * Kp;
-  if (!ensure_scratch(ctx, 0, 2 * (size_t)in_elems * sizeof(float))) return cudaErrorMemoryAllocation;
-  if (!ensure_scratch(ctx, 1, 2 * (size_t)w_elems * sizeof(float))) return cudaErrorMemoryAllocation;
+  if (!acquire_scratch(ctx, 0, 2 * (size_t)in_elems * sizeof(float))) return cudaErrorMemoryAllocation;
+  if (!acquire_scratch(ctx, 1, 2 * (size_t)w_elems * sizeof(float))) return cudaErrorMemoryAllocation;
   float* x_hi = static_cast<float*>(ctx->scratch[0]);
   float* x_lo = x_hi + in_elems;
   float* w_hi = static_cast<float*>(ctx->scratch[1]);
@@ -490,8 +488,11 @@ cudaError_t launch_conv_3xtf32_tc(exo_b200_Context* ctx, const ConvShape& s, con
     if (!make_tiled_map(&mb0, dt, 2, w_hi, dims, strides, box)) return cudaErrorUnknown;
     if (!make_tiled_map(&mb1, dt, 2, w_lo, dims, strides, box)) return cudaErrorUnknown;
   }
-  if (bn == 128) return launch_conv<CONV_TF32X3, 128>(ctx, ma0, ma1, mb0, mb1, p);
-  return launch_conv<CONV_TF32X3, 256>(ctx, ma0, ma1, mb0, mb1, p);
+  const cudaError_t e = bn == 128 ? launch_conv<CONV_TF32X3, 128>(ctx, ma0, ma1, mb0, mb1, p)
+                                  : launch_conv<CONV_TF32X3, 256>(ctx, ma0, ma1, mb0, mb1, p);
+  release_scratch(ctx, 0);
+  release_scratch(ctx, 1);
+  return e;
 }
 
 }  // namespace exob200

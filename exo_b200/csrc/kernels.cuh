@@ -45,6 +45,10 @@ cudaError_t launch_sgemm_3xtf32_tc(exo_b200_Context* ctx, int64_t M, int64_t N, 
 // one CTA waits on a barrier nobody signals; must end with EXO_B200_ERR_TIMEOUT in the status word
 cudaError_t launch_bounded_wait_selftest(exo_b200_Context* ctx, uint64_t limit_ns);
 
+// status word of matmul_on_cpu_static on the current device (tc_gemm.cu); false with the error set if a
+// timeout was recorded there
+bool collect_static_status();
+
 // ---- CTA-pair (cta_group::2) variants of the bf16 and int8 GEMMs (tc_gemm2.cu)
 bool tc2_wanted(int64_t M, int64_t N);
 cudaError_t launch_gemm_bf16_tc2(exo_b200_Context* ctx, int64_t M, int64_t N, int64_t K, const uint16_t* A,

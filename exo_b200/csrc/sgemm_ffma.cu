@@ -570,21 +570,19 @@ sgemm_tall_kernel(int M, int N, int K, const float* __restrict__ A, const float*
 }
 
 template <int NQ, int ROWS>
-cudaError_t launch_tall_r(cudaStream_t stream, int M, int N, int K, const float* A, const float* B, float* C,
-                          int a_vec, int b_vec) {
-  cudaError_t e = cudaFuncSetAttribute(sgemm_tall_kernel<NQ, ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       tl_smem<ROWS>());
-  if (e != cudaSuccess) return e;
+cudaError_t launch_tall_r(int device, cudaStream_t stream, int M, int N, int K, const float* A, const float* B,
+                          float* C, int a_vec, int b_vec) {
+  EXOB200_SMEM_ATTR_ONCE((sgemm_tall_kernel<NQ, ROWS>), tl_smem<ROWS>(), device);
   sgemm_tall_kernel<NQ, ROWS><<<(unsigned)((M + ROWS - 1) / ROWS), ROWS, tl_smem<ROWS>(), stream>>>(M, N, K, A, B, C,
                                                                                                    a_vec, b_vec);
   return cudaGetLastError();
 }
 
 template <int NQ>
-cudaError_t launch_tall(cudaStream_t stream, int M, int N, int K, const float* A, const float* B, float* C, int a_vec,
-                        int b_vec) {
+cudaError_t launch_tall(int device, cudaStream_t stream, int M, int N, int K, const float* A, const float* B, float* C,
+                        int a_vec, int b_vec) {
   // 32-row (one warp) CTAs were measured too: slower than 128-row CTAs from 8192 rows up, equal below
-  return launch_tall_r<NQ, 128>(stream, M, N, K, A, B, C, a_vec, b_vec);
+  return launch_tall_r<NQ, 128>(device, stream, M, N, K, A, B, C, a_vec, b_vec);
 }
 
 }  // namespace
@@ -599,10 +597,10 @@ cudaError_t launch_sgemm_ffma(exo_b200_Context* ctx, int64_t M, int64_t N, int64
     const int a_vec = va ? 1 : 0, b_vec = vb ? 1 : 0;
     const int m = (int)M, n = (int)N, k = (int)K;
     switch ((n + 3) / 4) {
-      case 1: return launch_tall<1>(stream, m, n, k, A, B, C, a_vec, b_vec);
-      case 2: return launch_tall<2>(stream, m, n, k, A, B, C, a_vec, b_vec);
-      case 3: return launch_tall<3>(stream, m, n, k, A, B, C, a_vec, b_vec);
-      default: return launch_tall<4>(stream, m, n, k, A, B, C, a_vec, b_vec);
+      case 1: return launch_tall<1>(ctx->device, stream, m, n, k, A, B, C, a_vec, b_vec);
+      case 2: return launch_tall<2>(ctx->device, stream, m, n, k, A, B, C, a_vec, b_vec);
+      case 3: return launch_tall<3>(ctx->device, stream, m, n, k, A, B, C, a_vec, b_vec);
+      default: return launch_tall<4>(ctx->device, stream, m, n, k, A, B, C, a_vec, b_vec);
     }
   }
   static const bool gemv_tma = [] {
@@ -620,9 +618,7 @@ cudaError_t launch_sgemm_ffma(exo_b200_Context* ctx, int64_t M, int64_t N, int64
     const unsigned grid = (unsigned)((N + W - 1) / W);
 #define EXOB200_GEMV(MR_, W_)                                                                                      \
   {                                                                                                                \
-    cudaError_t e = cudaFuncSetAttribute(sgemm_gemv_tma_kernel<MR_, W_>,                                           \
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, GT_SMEM);                    \
-    if (e != cudaSuccess) return e;                                                                                \
+    EXOB200_SMEM_ATTR_ONCE((sgemm_gemv_tma_kernel<MR_, W_>), GT_SMEM, ctx->device);                                \
     sgemm_gemv_tma_kernel<MR_, W_><<<grid, W_ + 32, GT_SMEM, stream>>>(mb, (int)N, (int)K, A, C, ctx->status_dev); \
   }
     if (M == 1 && W == 64) EXOB200_GEMV(1, 64)
@@ -634,28 +630,22 @@ cudaError_t launch_sgemm_ffma(exo_b200_Context* ctx, int64_t M, int64_t N, int64
   }
   if (M <= 4) {
     const unsigned grid = (unsigned)((N + GV_W - 1) / GV_W);
-    cudaError_t e;
     if (vb) {
-      e = cudaFuncSetAttribute(sgemm_gemv_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, GV_SMEM);
-      if (e != cudaSuccess) return e;
+      EXOB200_SMEM_ATTR_ONCE(sgemm_gemv_kernel<true>, GV_SMEM, ctx->device);
       sgemm_gemv_kernel<true><<<grid, GV_THREADS, GV_SMEM, stream>>>((int)M, (int)N, (int)K, A, B, C);
     } else {
-      e = cudaFuncSetAttribute(sgemm_gemv_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, GV_SMEM);
-      if (e != cudaSuccess) return e;
+      EXOB200_SMEM_ATTR_ONCE(sgemm_gemv_kernel<false>, GV_SMEM, ctx->device);
       sgemm_gemv_kernel<false><<<grid, GV_THREADS, GV_SMEM, stream>>>((int)M, (int)N, (int)K, A, B, C);
     }
     return cudaGetLastError();
   }
   if (M <= 32) {
     dim3 grid((unsigned)((N + SK_W - 1) / SK_W), (unsigned)((M + 31) / 32));
-    cudaError_t e;
     if (vb) {
-      e = cudaFuncSetAttribute(sgemm_skinny_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SK_SMEM);
-      if (e != cudaSuccess) return e;
+      EXOB200_SMEM_ATTR_ONCE(sgemm_skinny_kernel<true>, SK_SMEM, ctx->device);
       sgemm_skinny_kernel<true><<<grid, SK_THREADS, SK_SMEM, stream>>>((int)M, (int)N, (int)K, A, B, C);
     } else {
-      e = cudaFuncSetAttribute(sgemm_skinny_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SK_SMEM);
-      if (e != cudaSuccess) return e;
+      EXOB200_SMEM_ATTR_ONCE(sgemm_skinny_kernel<false>, SK_SMEM, ctx->device);
       sgemm_skinny_kernel<false><<<grid, SK_THREADS, SK_SMEM, stream>>>((int)M, (int)N, (int)K, A, B, C);
     }
     return cudaGetLastError();

@@ -7,6 +7,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+#include <cstring>
 #include <mutex>
 #include <string>
 
@@ -67,6 +69,40 @@ inline EncodeTiledFn encode_fn() {
 inline bool make_tiled_map(CUtensorMap* m, CUtensorMapDataType dt, int rank, const void* base,
                            const cuuint64_t* dims, const cuuint64_t* strides, const cuuint32_t* box,
                            CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
+  // Callers that repeat a call (a layer of a network, a benchmark loop) ask for the same maps
+  // again and again; the driver's encoder takes a microsecond or two per map, which is a large
+  // part of the host time of a 10 us kernel.  A map is a pure function of the arguments below,
+  // so the last few are kept per thread.
+  struct Key {
+    const void* base;
+    int dt, rank, swizzle;
+    cuuint64_t dims[5], strides[4];
+    cuuint32_t box[5];
+  };
+  struct Entry {
+    Key key;
+    CUtensorMap map;
+    bool valid;
+  };
+  constexpr int kCached = 16;
+  static thread_local Entry cache[kCached];
+  static thread_local int next_slot = 0;
+  Key key;
+  memset(&key, 0, sizeof(key));
+  key.base = base;
+  key.dt = (int)dt;
+  key.rank = rank;
+  key.swizzle = (int)swizzle;
+  for (int i = 0; i < rank; i++) {
+    key.dims[i] = dims[i];
+    key.box[i] = box[i];
+    if (i + 1 < rank) key.strides[i] = strides[i];
+  }
+  for (int i = 0; i < kCached; i++)
+    if (cache[i].valid && memcmp(&cache[i].key, &key, sizeof(Key)) == 0) {
+      *m = cache[i].map;
+      return true;
+    }
   EncodeTiledFn fn = encode_fn();
   if (!fn) {
     set_error(EXO_B200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
@@ -88,6 +124,11 @@ inline bool make_tiled_map(CUtensorMap* m, CUtensorMapDataType dt, int rank, con
     set_error(EXO_B200_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult " + std::to_string((int)r));
     return false;
   }
+  Entry& slot = cache[next_slot];
+  next_slot = (next_slot + 1) % kCached;
+  slot.key = key;
+  slot.map = *m;
+  slot.valid = true;
   return true;
 }
 
@@ -95,3 +136,18 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 
 }  // namespace tc
 }  // namespace exob200
+
+// Opt a kernel in to `bytes` of dynamic shared memory once per device instead of on every
+// launch (the attribute is per function and device; the call costs about a microsecond).
+// Used inside functions that return cudaError_t.
+#define EXOB200_SMEM_ATTR_ONCE(kernel, bytes, device)                                                         \
+  do {                                                                                                        \
+    static std::atomic<uint64_t> done_{0};                                                                    \
+    const uint64_t bit_ = 1ull << ((device) & 63);                                                            \
+    if (!(done_.load(std::memory_order_acquire) & bit_)) {                                                    \
+      cudaError_t e_ = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (bytes));    \
+      if (e_ != cudaSuccess) return e_;                                                                       \
+      done_.fetch_or(bit_, std::memory_order_release);                                                        \
+    }                                                                                                         \
+  } while (0)
+

@@ -600,11 +600,7 @@ int chunk_kb() {
 template <int MODE, bool BMN = false>
 cudaError_t launch_tc(exo_b200_Context* ctx, const CUtensorMap& a0, const CUtensorMap& a1, const CUtensorMap& b0,
                       const CUtensorMap& b1, int64_t M, int64_t N, int64_t K, const EpiParams& ep) {
-  {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<MODE, BMN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         smem_bytes<MODE>());
-    if (e != cudaSuccess) return e;
-  }
+  EXOB200_SMEM_ATTR_ONCE((gemm_tc_kernel<MODE, BMN>), smem_bytes<MODE>(), ctx->device);
   const int64_t tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
   if (tiles_m * tiles_n > INT32_MAX || M > INT32_MAX || N > INT32_MAX || K > INT32_MAX)
     return cudaErrorInvalidValue;
@@ -621,8 +617,41 @@ bool tc_supported_bf16(int64_t, int64_t, int64_t K, const void* A, const void* B
   return K % 8 == 0 && aligned16(A) && aligned16(B);
 }
 
+namespace {
+// rows x K 16-bit elements -> rows x Kp, zero in the pad columns (Kp % 8 == 0, dst 16-byte aligned)
+__global__ void pad_rows_u16_kernel(const uint16_t* __restrict__ src, int64_t rows, int K, int Kp,
+                                    uint16_t* __restrict__ dst) {
+  const int64_t total = rows * Kp;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / Kp;
+    const int k = (int)(i - r * Kp);
+    dst[i] = k < K ? __ldg(src + r * K + k) : (uint16_t)0;
+  }
+}
+}  // namespace
+
 cudaError_t launch_gemm_bf16_tc(exo_b200_Context* ctx, int64_t M, int64_t N, int64_t K, const uint16_t* A,
                                 const uint16_t* B, uint16_t* C) {
+  if (!tc_supported_bf16(M, N, K, A, B, C)) {
+    // TMA needs a 16-byte row pitch and base.  K % 8 != 0 or an odd base: copy both operands into
+    // scratch with the pitch rounded up to 8 elements (zero padding adds exact zeros to every sum)
+    // and multiply those.  Costs one extra pass over A and B; ragged K is not the fast case.
+    if (M > INT32_MAX || N > INT32_MAX || K > INT32_MAX - 8) return cudaErrorInvalidValue;
+    const int64_t Kp = (K + 7) / 8 * 8;
+    if (!acquire_scratch(ctx, 0, (size_t)(M * Kp) * 2)) return cudaErrorMemoryAllocation;
+    if (!acquire_scratch(ctx, 1, (size_t)(N * Kp) * 2)) return cudaErrorMemoryAllocation;
+    uint16_t* Ap = static_cast<uint16_t*>(ctx->scratch[0]);
+    uint16_t* Bp = static_cast<uint16_t*>(ctx->scratch[1]);
+    const int ba = (int)std::min<int64_t>((M * Kp + 255) / 256, (int64_t)ctx->sm_count * 16);
+    const int bb = (int)std::min<int64_t>((N * Kp + 255) / 256, (int64_t)ctx->sm_count * 16);
+    pad_rows_u16_kernel<<<ba, 256, 0, ctx->stream>>>(A, M, (int)K, (int)Kp, Ap);
+    pad_rows_u16_kernel<<<bb, 256, 0, ctx->stream>>>(B, N, (int)K, (int)Kp, Bp);
+    cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess) e = launch_gemm_bf16_tc(ctx, M, N, Kp, Ap, Bp, C);
+    release_scratch(ctx, 0);
+    release_scratch(ctx, 1);
+    return e;
+  }
   if (tc2_wanted(M, N)) return launch_gemm_bf16_tc2(ctx, M, N, K, A, B, C);
   CUtensorMap ma, mb;
   if (!make_kmajor_map(&ma, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, A, M, K, K * 2, BM)) return cudaErrorUnknown;
@@ -654,7 +683,7 @@ cudaError_t launch_matmul_i8_tc(exo_b200_Context* ctx, int64_t N, int64_t M, int
     EpiParams ep{C, cols, scale, act ? 1 : 0, (cols % 16 == 0 && aligned16(C)) ? 1 : 0};
     return launch_tc<MODE_I8, true>(ctx, ma, ma, mb, mb, rows, cols, K, ep);
   }
-  if (!ensure_scratch(ctx, 1, (size_t)(cols * Kp))) return cudaErrorMemoryAllocation;
+  if (!acquire_scratch(ctx, 1, (size_t)(cols * Kp))) return cudaErrorMemoryAllocation;
   int8_t* Bt = static_cast<int8_t*>(ctx->scratch[1]);
   {
     dim3 grid((unsigned)((K + 127) / 128), (unsigned)((cols + 127) / 128));
@@ -668,7 +697,9 @@ cudaError_t launch_matmul_i8_tc(exo_b200_Context* ctx, int64_t N, int64_t M, int
   if (!make_kmajor_map(&ma, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, A, rows, K, K, BM)) return cudaErrorUnknown;
   if (!make_kmajor_map(&mb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, Bt, cols, K, Kp, BN)) return cudaErrorUnknown;
   EpiParams ep{C, cols, scale, act ? 1 : 0, (cols % 16 == 0 && aligned16(C)) ? 1 : 0};
-  return launch_tc<MODE_I8>(ctx, ma, ma, mb, mb, rows, cols, K, ep);
+  const cudaError_t e = launch_tc<MODE_I8>(ctx, ma, ma, mb, mb, rows, cols, K, ep);
+  release_scratch(ctx, 1);
+  return e;
 }
 
 // -------------------------------------------------------------- 3xTF32
@@ -679,8 +710,8 @@ cudaError_t launch_sgemm_3xtf32_tc(exo_b200_Context* ctx, int64_t M, int64_t N, 
   if (M > INT32_MAX || N > INT32_MAX || K > INT32_MAX - 64) return cudaErrorInvalidValue;
   const int64_t Kp = (K + 3) / 4 * 4;  // pitch multiple of 16 bytes
   const size_t a_elems = (size_t)(M * Kp), b_elems = (size_t)(N * Kp);
-  if (!ensure_scratch(ctx, 0, 2 * a_elems * sizeof(float))) return cudaErrorMemoryAllocation;
-  if (!ensure_scratch(ctx, 1, 2 * b_elems * sizeof(float))) return cudaErrorMemoryAllocation;
+  if (!acquire_scratch(ctx, 0, 2 * a_elems * sizeof(float))) return cudaErrorMemoryAllocation;
+  if (!acquire_scratch(ctx, 1, 2 * b_elems * sizeof(float))) return cudaErrorMemoryAllocation;
   float* a_hi = static_cast<float*>(ctx->scratch[0]);
   float* a_lo = a_hi + a_elems;
   float* b_hi = static_cast<float*>(ctx->scratch[1]);
@@ -702,7 +733,10 @@ cudaError_t launch_sgemm_3xtf32_tc(exo_b200_Context* ctx, int64_t M, int64_t N, 
   if (!make_kmajor_map(&mb0, dt, 4, b_hi, N, Kp, Kp * 4, BN)) return cudaErrorUnknown;
   if (!make_kmajor_map(&mb1, dt, 4, b_lo, N, Kp, Kp * 4, BN)) return cudaErrorUnknown;
   EpiParams ep{C, N, 0.f, 0, (N % 4 == 0 && aligned16(C)) ? 1 : 0};
-  return launch_tc<MODE_TF32X3>(ctx, ma0, ma1, mb0, mb1, M, N, Kp, ep);
+  const cudaError_t e = launch_tc<MODE_TF32X3>(ctx, ma0, ma1, mb0, mb1, M, N, Kp, ep);
+  release_scratch(ctx, 0);
+  release_scratch(ctx, 1);
+  return e;
 }
 
 // --------------------------------------------------------------------------
@@ -758,12 +792,17 @@ cudaError_t launch_bounded_wait_selftest(exo_b200_Context* ctx, uint64_t limit_n
 // zero -- the transpose pre-pass overwrites every byte the GEMM then reads.
 constexpr size_t kStaticScratchBytes = 4u << 20;  // K * M <= 4 Mi int8 elements
 static __device__ __align__(256) int8_t g_static_bt_scratch[kStaticScratchBytes];
+// The status word of this entry point's kernels lives in the library image too (the regular
+// entry points use a mapped host allocation of their context).  A bounded wait that runs out
+// records EXO_B200_ERR_TIMEOUT here; exo_b200_synchronize() copies it back and reports it.
+static __device__ DeviceStatus g_static_status;
 
 namespace {
 
 struct StaticDeviceState {
   bool ready = false;
   int8_t* scratch = nullptr;  // device address of g_static_bt_scratch on this device
+  DeviceStatus* status = nullptr;  // device address of g_static_status on this device
   int sm_count = 0;
 };
 constexpr int kMaxDevices = 64;
@@ -798,12 +837,50 @@ StaticDeviceState* static_state_for_current_device() {
                                        smem_bytes<MODE_I8>()),
                   "cudaFuncSetAttribute"))
     return nullptr;
+  void* status_ptr = nullptr;
+  if (!check_cuda(cudaGetSymbolAddress(&status_ptr, g_static_status), "cudaGetSymbolAddress(static status)"))
+    return nullptr;
   st.scratch = static_cast<int8_t*>(ptr);
+  st.status = static_cast<DeviceStatus*>(status_ptr);
   st.ready = true;
   return &st;
 }
 
+// Where a device pointer lives: its device ordinal, -1 for managed memory (reachable from every
+// device), -2 for anything that is not device memory.
+int device_of(const void* p) {
+  cudaPointerAttributes attr;
+  if (cudaPointerGetAttributes(&attr, p) != cudaSuccess) {
+    cudaGetLastError();
+    return -2;
+  }
+  if (attr.type == cudaMemoryTypeManaged) return -1;
+  return attr.type == cudaMemoryTypeDevice ? attr.device : -2;
+}
+
 }  // namespace
+
+// Called by exo_b200_synchronize: reports a timeout that a kernel of matmul_on_cpu_static has
+// recorded on the current device.  A plain blocking 16-byte copy: it sees what kernels that
+// have completed wrote (the caller synchronises its own stream first), and allocates nothing.
+bool collect_static_status() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return true;
+  DeviceStatus* word = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    if (!g_static_state[dev].ready) return true;
+    word = g_static_state[dev].status;
+  }
+  DeviceStatus h;
+  if (!check_cuda(cudaMemcpy(&h, word, sizeof(h), cudaMemcpyDeviceToHost), "cudaMemcpy(static status)")) return false;
+  if (h.code == 0) return true;
+  cudaMemset(word, 0, sizeof(h));
+  set_error(h.code, "matmul_on_cpu_static: device-side wait ran out (kernel location " + std::to_string(h.where) +
+                        ", block " + std::to_string(h.block) + "); its output is incomplete");
+  return false;
+}
+
 }  // namespace exob200
 
 extern "C" __attribute__((visibility("default"))) void matmul_on_cpu_static(
@@ -826,12 +903,23 @@ extern "C" __attribute__((visibility("default"))) void matmul_on_cpu_static(
                   std::to_string(kStaticScratchBytes) + " int8 elements; use matmul_on_cpu");
     return;
   }
-  if (!is_device_pointer(A) || !is_device_pointer(B) || !is_device_pointer(C) || is_device_pointer(scale)) {
+  const int where[3] = {device_of(A), device_of(B), device_of(C)};
+  if (where[0] == -2 || where[1] == -2 || where[2] == -2 || is_device_pointer(scale)) {
     set_error(EXO_B200_ERR_INVALID_ARGUMENT,
               std::string(fn) + ": A, B, C must be device memory (host buffers would need staging allocations) "
                                 "and scale host memory (it is read when the call is made)");
     return;
   }
+  int cur = 0;
+  if (!check_cuda(cudaGetDevice(&cur), "cudaGetDevice")) return;
+  for (int i = 0; i < 3; i++)
+    if (where[i] >= 0 && where[i] != cur) {
+      // the scratch array, the SM count and the launch are the current device's
+      set_error(EXO_B200_ERR_INVALID_ARGUMENT,
+                std::string(fn) + ": operand " + "ABC"[i] + " lives on device " + std::to_string(where[i]) +
+                    " but device " + std::to_string(cur) + " is current; make the operands' device current first");
+      return;
+    }
   StaticDeviceState* st = static_state_for_current_device();
   if (!st) return;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -852,9 +940,10 @@ extern "C" __attribute__((visibility("default"))) void matmul_on_cpu_static(
   EpiParams ep{C, cols, sc, act ? 1 : 0, (cols % 16 == 0 && (reinterpret_cast<uintptr_t>(C) & 15u) == 0) ? 1 : 0};
   const int64_t tiles_m = (rows + BM - 1) / BM, tiles_n = (cols + BN - 1) / BN;
   const int grid = (int)std::min<int64_t>(tiles_m * tiles_n, st->sm_count);
-  // no status word: a bounded device-side wait that runs out ends the kernel but is not reported here
+  // a bounded device-side wait that runs out is recorded in the static status word; this call only
+  // enqueues, so the report comes from the next exo_b200_synchronize()
   gemm_tc_kernel<MODE_I8><<<grid, NUM_THREADS, smem_bytes<MODE_I8>(), s>>>(ma, ma, mb, mb, (int)rows, (int)cols,
-                                                                           (int)K, ep, nullptr, (int)tiles_m,
+                                                                           (int)K, ep, st->status, (int)tiles_m,
                                                                            (int)tiles_n, 1 << 30);
   check_cuda(cudaGetLastError(), fn);
 }

@@ -735,9 +735,8 @@ gemm_tc2t_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 template <int MODE>
 cudaError_t launch_tc2t(exo_b200_Context* ctx, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc,
                         int tma_store, int64_t M, int64_t N, int64_t K, const Epi2& ep) {
-  cudaError_t e =
-      cudaFuncSetAttribute(gemm_tc2t_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM2T_BYTES);
-  if (e != cudaSuccess) return e;
+  EXOB200_SMEM_ATTR_ONCE((gemm_tc2t_kernel<MODE>), SMEM2T_BYTES, ctx->device);
+  cudaError_t e;
   const int64_t tiles_m = (M + 4 * BM - 1) / (4 * BM), tiles_n = (N + BN2 - 1) / BN2;
   if (tiles_m * tiles_n > INT32_MAX || M > INT32_MAX || N > INT32_MAX || K > INT32_MAX) return cudaErrorInvalidValue;
   cudaLaunchConfig_t cfg = {};
@@ -751,15 +750,15 @@ cudaError_t launch_tc2t(exo_b200_Context* ctx, const CUtensorMap& ma, const CUte
   attr.val.clusterDim.z = 1;
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
-  static std::atomic<int> max_clusters{0};  // same value whichever thread gets here first
-  if (max_clusters.load() == 0) {
+  int& max_clusters = ctx->max_pairs[2 + MODE];  // per context, i.e. per device; the caller holds the context's mutex
+  if (max_clusters == 0) {
     cfg.gridDim = dim3(2 * ctx->sm_count);
     int n = 0;
     e = cudaOccupancyMaxActiveClusters(&n, gemm_tc2t_kernel<MODE>, &cfg);
     if (e != cudaSuccess) return e;
-    max_clusters.store(std::max(1, n));
+    max_clusters = std::max(1, n);
   }
-  const int pairs = (int)std::min<int64_t>(tiles_m * tiles_n, max_clusters.load());
+  const int pairs = (int)std::min<int64_t>(tiles_m * tiles_n, max_clusters);
   cfg.gridDim = dim3(2 * pairs);
   static const int gm = [] {
     const char* e = getenv("EXOB200_TC2T_GM");  // tile rows (of 512) per group
@@ -785,9 +784,8 @@ cudaError_t launch_tc2t(exo_b200_Context* ctx, const CUtensorMap& ma, const CUte
 template <int MODE>
 cudaError_t launch_tc2(exo_b200_Context* ctx, const CUtensorMap& ma, const CUtensorMap& mb, int64_t M, int64_t N,
                        int64_t K, const Epi2& ep) {
-  cudaError_t e =
-      cudaFuncSetAttribute(gemm_tc2_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM2_BYTES);
-  if (e != cudaSuccess) return e;
+  EXOB200_SMEM_ATTR_ONCE((gemm_tc2_kernel<MODE>), SMEM2_BYTES, ctx->device);
+  cudaError_t e;
   const int64_t tiles_m = (M + 2 * BM - 1) / (2 * BM), tiles_n = (N + BN2 - 1) / BN2;
   if (tiles_m * tiles_n > INT32_MAX || M > INT32_MAX || N > INT32_MAX || K > INT32_MAX) return cudaErrorInvalidValue;
   // launched as clusters of two CTAs; size the grid to the number of pairs that
@@ -803,15 +801,15 @@ cudaError_t launch_tc2(exo_b200_Context* ctx, const CUtensorMap& ma, const CUten
   attr.val.clusterDim.z = 1;
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
-  static std::atomic<int> max_clusters{0};  // same value whichever thread gets here first
-  if (max_clusters.load() == 0) {
+  int& max_clusters = ctx->max_pairs[MODE];  // per context, i.e. per device; the caller holds the context's mutex
+  if (max_clusters == 0) {
     cfg.gridDim = dim3(2 * ctx->sm_count);
     int n = 0;
     e = cudaOccupancyMaxActiveClusters(&n, gemm_tc2_kernel<MODE>, &cfg);
     if (e != cudaSuccess) return e;
-    max_clusters.store(std::max(1, n));
+    max_clusters = std::max(1, n);
   }
-  const int pairs = (int)std::min<int64_t>(tiles_m * tiles_n, max_clusters.load());
+  const int pairs = (int)std::min<int64_t>(tiles_m * tiles_n, max_clusters);
   cfg.gridDim = dim3(2 * pairs);
   static const int gm = [] {
     const char* e = getenv("EXOB200_TC2_GM");

@@ -156,7 +156,9 @@ void conv_nhwc_exo_3xtf32( void *ctxt, int_fast32_t batch_size, int_fast32_t in_
  * as matmul_on_cpu.
  *   - The first parameter is the cudaStream_t to launch on (NULL = default
  *     stream), not a context: contexts own allocations.
- *   - A, B, C must be device memory; scale is host memory, read during the call.
+ *   - A, B, C must be device memory of the CURRENT device (the scratch array and
+ *     the launch are the current device's; operands of another device are
+ *     rejected); scale is host memory, read during the call.
  *   - Scratch for the K-major copy of B is a fixed array in the library image,
  *     EXO_B200_STATIC_SCRATCH_BYTES per GPU for the life of the process;
  *     K * M beyond it is rejected (EXO_B200_ERR_UNSUPPORTED, output untouched).
@@ -164,6 +166,11 @@ void conv_nhwc_exo_3xtf32( void *ctxt, int_fast32_t batch_size, int_fast32_t in_
  *     loads the kernels: make that call before any stream capture begins.
  *   - All calls share the array: calls whose kernels may overlap on the GPU
  *     race; order them on one stream or with events.
+ *   - The call only enqueues.  If a bounded device-side wait of its kernel ever
+ *     runs out, the kernel ends with C partly written and records that in a
+ *     status word that also lives in the library image; the call itself cannot
+ *     report it.  exo_b200_synchronize() picks it up (EXO_B200_ERR_TIMEOUT), so
+ *     call that after synchronising your stream where you need to know.
  *   - Calls no cudaMalloc / cudaFree / cudaHostAlloc and creates no context. */
 #define EXO_B200_STATIC_SCRATCH_BYTES (4u << 20)
 void matmul_on_cpu_static( void *stream, int_fast32_t N, int_fast32_t M, int_fast32_t K, const float* scale, bool act, const int8_t* A, const int8_t* B, int8_t* C );

@@ -48,3 +48,10 @@ def ref():
     if not oracle.ref_available():
         pytest.skip("compiled reference (oracle/_ref) not available on this machine")
     return oracle.ref()
+
+
+@pytest.fixture(scope="session")
+def torch_mod():
+    import torch
+
+    return torch

@@ -49,11 +49,22 @@ def _rank_body(rank, world, port, M, N, K, q):
     dist.all_gather(parts, c.view(torch.uint8))
     if rank == 0:
         import exo_b200
+        import oracle
 
         full = torch.empty((M, N), dtype=torch.int16, device="cuda")
         exo_b200.library().gemm_bf16_exo(None, M, N, K, A, B, full)
         torch.cuda.synchronize()
-        q.put(bool(torch.equal(torch.cat(parts, 0), full.view(torch.uint8))))
+        same = bool(torch.equal(torch.cat(parts, 0), full.view(torch.uint8)))
+        # and the gathered result against the oracle on a row sample that touches every rank's block
+        rows = sorted({b.start for b in sg.blocks} | {b.stop - 1 for b in sg.blocks} | {M // 2 + 77})
+        idx = torch.tensor(rows, device="cuda")
+        got = inputs.bf16_bits_to_f32(torch.cat(parts, 0).view(torch.int16)[idx].cpu().numpy().view(np.uint16))
+        port = oracle.port()
+        port.set_threads(os.cpu_count() or 1)
+        ref = inputs.bf16_bits_to_f32(port.gemm_bf16(A[idx].cpu().numpy().view(np.uint16),
+                                                     B.cpu().numpy().view(np.uint16)))
+        close = bool((np.abs(got - ref) <= 2.0 ** -7 * np.abs(ref) + 1e-3 * np.sqrt(K) * 4e-4).all())
+        q.put(True if same and close else f"bitwise equal to one GPU: {same}; within tolerance of the oracle: {close}")
     dist.barrier()
     dist.destroy_process_group()
 
@@ -65,7 +76,9 @@ def test_sharded_bf16_gemm_is_bitwise_equal_to_one_gpu():
     world = min(torch.cuda.device_count(), 4)
     if world < 2:
         pytest.skip("needs at least two GPUs")
-    M, N, K = 1024 * world, 1024, 512
+    # 5120 x 8192 per rank = 10 x 32 tiles of 512 x 256: every rank (and the one-GPU run) takes the
+    # CTA-pair kernel that the scaling benchmark times, not the single-CTA kernel of small problems
+    M, N, K = 5120 * world, 8192, 512
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()

@@ -94,9 +94,10 @@ def test_sgemm_ffma_signed_zero_and_specials(lib, port):
 
 
 def test_sgemm_ffma_full_size_rows_against_oracle(lib, port, torch):
-    """8192^3 is beyond what the CPU oracle finishes in seconds; because every
+    """4096^3 is beyond what the CPU oracle finishes in seconds; because every
     output row depends only on its own row of A, a sample of rows run through
-    the oracle at full N and K checks the full-size launch bit for bit."""
+    the oracle at full N and K checks the full-size launch bit for bit.  (8192^3:
+    tests/test_gpu_kernel_variants.py.)"""
     M = N = K = 4096
     g = torch.Generator(device="cuda").manual_seed(7)
     dA = torch.rand((M, K), generator=g, device="cuda") * 2 - 1
@@ -380,7 +381,8 @@ def test_conv_3xtf32_within_tolerance(lib, port, torch, cfg):
 # Tolerance, stated: |C_gpu - C_ref| <= 2^-7 |C_ref| + 1e-3 * sqrt(K) * 4e-4 where C_ref is
 # the reference fp32 SGEMM chain on the widened inputs rounded once to bf16 (one bf16 ulp
 # of slack for a different fp32 accumulation order plus an absolute floor near zero).
-@pytest.mark.parametrize("shape", [(128, 256, 64), (256, 512, 512), (384, 300, 1000), (130, 70, 72), (2048, 2048, 2048)])
+@pytest.mark.parametrize("shape", [(128, 256, 64), (256, 512, 512), (384, 300, 1000), (130, 70, 72), (2048, 2048, 2048),
+                                   (130, 70, 71), (257, 129, 1001), (3, 5, 1)])  # K % 8 != 0: padded operand copies
 def test_gemm_bf16_against_reference_sgemm(lib, port, torch, shape):
     M, N, K = shape
     A = inputs.normal_bf16(51, (M, K))
@@ -399,6 +401,94 @@ def test_gemm_bf16_against_reference_sgemm(lib, port, torch, shape):
     assert (err <= tol).all(), f"max err {err.max():.3e} at ref {ref.reshape(-1)[err.argmax()]:.3e}"
     # and most outputs are bit-identical to the reference rounding
     assert (C == ref).mean() > 0.9
+
+
+def test_gemm_bf16_unaligned_bases(lib, port, torch):
+    """A, B and C that start 2 bytes into an allocation (not 16-byte aligned): TMA cannot
+    address them, so the operands go through the padded copy and C through scalar stores."""
+    M, N, K = 200, 136, 264
+    A = inputs.normal_bf16(53, (M, K))
+    Bt = inputs.normal_bf16(54, (N, K))
+
+    def shifted(a):
+        flat = torch.full((a.size + 1,), 0x7FC0, dtype=torch.int16, device="cuda")
+        view = flat[1:].view(a.shape)
+        view.copy_(torch.from_numpy(a.view(np.int16)))
+        assert view.data_ptr() % 16 != 0
+        return view
+
+    dC = torch.full((M * N + 1,), 0x7FC0, dtype=torch.int16, device="cuda")[1:].view(M, N)
+    lib.gemm_bf16_exo(None, M, N, K, shifted(A), shifted(Bt), dC)
+    torch.cuda.synchronize()
+    C = inputs.bf16_bits_to_f32(dC.cpu().numpy().view(np.uint16))
+    ref = inputs.bf16_bits_to_f32(port.gemm_bf16(A, Bt))
+    assert (np.abs(C - ref) <= 2.0 ** -7 * np.abs(ref) + 1e-3 * np.sqrt(K) * 4e-4).all()
+
+
+def test_two_streams_share_the_default_context_scratch(lib, port, torch):
+    """Two device-pointer calls that both use the default context's scratch (the 3xTF32 split
+    copies; the K-major copy of B for an int8 matmul whose B pitch TMA cannot read in place),
+    issued back to back on two different streams: the second call's pre-pass must wait for the
+    first call's GEMM to finish reading the scratch.  Both results are checked."""
+    s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+    M, N, K = 1024, 1024, 2048
+    A1, B1, C1 = cases.sgemm_inputs(M, N, K, seed=601)
+    A2, B2, C2 = cases.sgemm_inputs(M, N, K, seed=602)
+    d = [dev(torch, x) for x in (A1, B1, C1, A2, B2, C2)]
+    n, m, k = 2048, 1000, 2048  # m % 16 != 0: B goes through the transposing pre-pass into scratch
+    A8a, B8a = inputs.int8(611, (n, k), -20, 20), inputs.int8(612, (k, m), -20, 20)
+    A8b, B8b = inputs.int8(613, (n, k), -20, 20), inputs.int8(614, (k, m), -20, 20)
+    d8 = [dev(torch, x) for x in (A8a, B8a, A8b, B8b)]
+    o1 = torch.empty((n, m), dtype=torch.int8, device="cuda")
+    o2 = torch.empty((n, m), dtype=torch.int8, device="cuda")
+    torch.cuda.synchronize()
+    for _ in range(3):  # a few rounds: the race, if present, is a matter of timing
+        d[2].copy_(torch.from_numpy(C1))
+        d[5].copy_(torch.from_numpy(C2))
+        torch.cuda.synchronize()
+        with torch.cuda.stream(s1):
+            lib.sgemm_exo_3xtf32(None, M, N, K, d[0], d[1], d[2])
+        with torch.cuda.stream(s2):
+            lib.sgemm_exo_3xtf32(None, M, N, K, d[3], d[4], d[5])
+        with torch.cuda.stream(s1):
+            lib.matmul_on_cpu(None, n, m, k, 1.0 / 64, True, d8[0], d8[1], o1)
+        with torch.cuda.stream(s2):
+            lib.matmul_on_cpu(None, n, m, k, 1.0 / 64, True, d8[2], d8[3], o2)
+        torch.cuda.synchronize()
+        for (A, B, C0, got) in ((A1, B1, C1, d[2]), (A2, B2, C2, d[5])):
+            ref = C0.astype(np.float64) + A.astype(np.float64) @ B.astype(np.float64)
+            bound = tf32x3_bound(K) * (np.abs(C0) + np.abs(A).astype(np.float64) @ np.abs(B).astype(np.float64))
+            assert (np.abs(got.cpu().numpy() - ref) <= bound).all()
+        port.set_threads(os.cpu_count() or 1)
+        try:
+            assert np.array_equal(o1.cpu().numpy(), port.matmul_i8(A8a, B8a, 1.0 / 64, True))
+            assert np.array_equal(o2.cpu().numpy(), port.matmul_i8(A8b, B8b, 1.0 / 64, True))
+        finally:
+            port.set_threads(1)
+
+
+def test_context_of_another_device_is_made_current(lib, port, torch):
+    """A context created for device 1 used while device 0 is current: the call switches to the
+    context's device for its duration (and back), so the kernel runs where the operands are."""
+    import exo_b200
+
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    M, N, K = 130, 200, 64
+    A, B, C0 = cases.sgemm_inputs(M, N, K, seed=71)
+    ctx = exo_b200.Context(device=1)
+    dA, dB, dC = (torch.from_numpy(x).to("cuda:1") for x in (A, B, C0))
+    torch.cuda.set_device(0)
+    lib.dll.sgemm_exo(ctx.handle, M, N, K, dA.data_ptr(), dB.data_ptr(), dC.data_ptr())
+    assert lib.dll.exo_b200_last_error() == 0
+    assert torch.cuda.current_device() == 0
+    lib.synchronize(ctx)
+    assert np.array_equal(bits(dC.cpu().numpy()), bits(port.sgemm(A, B, C0.copy())))
+    # operands of device 0 through the device-1 context are refused, not dereferenced
+    d0 = torch.from_numpy(C0).to("cuda:0")
+    lib.dll.sgemm_exo(ctx.handle, M, N, K, dA.data_ptr(), dB.data_ptr(), d0.data_ptr())
+    assert lib.dll.exo_b200_last_error() == exo_b200.ERR_INVALID_ARGUMENT
+    ctx.close()
 
 
 def test_error_side_channel_on_gpu(lib):
@@ -615,7 +705,13 @@ def test_concurrent_host_threads_share_the_default_context(lib, port):
         work.append((M, N, K, A, B, C, want))
     errors = []
 
-    def run(item):
+    # by-pointer scalars (the int8 scale given as a Python float) are per-call temporaries of the
+    # wrapper: concurrent callers must not free each other's
+    A8, B8 = inputs.int8(51, (64, 48), -20, 20), inputs.int8(52, (48, 80), -20, 20)
+    scales = [1.0 / 64, 0.3, 2.0, 0.011]
+    want8 = [port.matmul_i8(A8, B8, s, True) for s in scales]
+
+    def run(mine, item):
         M, N, K, A, B, C, want = item
         try:
             for _ in range(5):
@@ -623,10 +719,14 @@ def test_concurrent_host_threads_share_the_default_context(lib, port):
                 lib.sgemm_exo_ffma(None, M, N, K, A, B, got)
                 if not np.array_equal(bits(got), bits(want)):
                     errors.append((M, N, K))
+                got8 = np.empty((64, 80), np.int8)
+                lib.matmul_on_cpu(None, 64, 80, 48, scales[mine], True, A8, B8, got8)
+                if not np.array_equal(got8, want8[mine]):
+                    errors.append(("i8", scales[mine]))
         except Exception as e:  # noqa: BLE001 - reported through the list
             errors.append(repr(e))
 
-    threads = [threading.Thread(target=run, args=(w,)) for w in work]
+    threads = [threading.Thread(target=run, args=(i, w)) for i, w in enumerate(work)]
     for t in threads:
         t.start()
     for t in threads:

@@ -8,7 +8,7 @@ scratch of one kernel (the K-major copy of B) in a fixed array inside the
 library image.  This test calls that entry point through the C ABI twice in a
 row (different shapes, so the second call sees the first call's leftovers in
 the shared array) and requires bit-identical results to the regular entry
-point, which is itself checked against the oracle elsewhere.
+point and to the CPU oracle.
 
 The file name sorts last on purpose: a run that stops at the first failure has
 already run every other test by the time it gets here.
@@ -18,6 +18,7 @@ import ctypes
 import numpy as np
 import pytest
 
+import oracle
 from tests import inputs
 
 pytestmark = pytest.mark.gpu
@@ -51,6 +52,8 @@ def test_static_scratch_matches_regular_entry_point_twice():
             lib.dll.exo_b200_last_error_string()
         torch.cuda.synchronize()
         assert torch.equal(got, want)
+        assert np.array_equal(got.cpu().numpy(), oracle.port().matmul_i8(A, B, scale, act))
+        assert lib.dll.exo_b200_synchronize(None) == 0  # no device-side timeout was recorded
 
 
 def test_static_scratch_rejects_what_does_not_fit():
@@ -73,3 +76,23 @@ def test_static_scratch_rejects_what_does_not_fit():
     s = np.array([1.0], np.float32)
     lib.dll.matmul_on_cpu_static(None, 16, 16, 16, s.ctypes.data, False, hA.ctypes.data, hA.ctypes.data, hA.ctypes.data)
     assert lib.dll.exo_b200_last_error() == exo_b200.ERR_INVALID_ARGUMENT
+
+
+def test_static_scratch_rejects_operands_of_another_device():
+    """The scratch array and the launch belong to the current device, so operands that live
+    on a different GPU are refused instead of being dereferenced from the wrong device."""
+    import torch
+
+    import exo_b200
+
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    lib = exo_b200.library()
+    with torch.cuda.device(1):
+        dA = torch.zeros((16, 16), dtype=torch.int8, device="cuda:1")
+        dC = torch.full((16, 16), 5, dtype=torch.int8, device="cuda:1")
+    torch.cuda.set_device(0)
+    code = _call_static(lib, 0, 16, 16, 16, 1.0, False, dA, dA, dC)
+    assert code == exo_b200.ERR_INVALID_ARGUMENT
+    assert b"device" in lib.dll.exo_b200_last_error_string()
+    assert bool((dC == 5).all())
