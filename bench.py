@@ -189,6 +189,9 @@ def run_reference_arm(args):
     cores = len(os.sched_getaffinity(0))
     A, B = _cpu_inputs()
     _W["A"], _W["B"] = A, B
+    # load the checker library in this process too (the workers are forks and inherit the mapping),
+    # so that a loader hook on the parent sees which shared object the arm runs
+    _worker_init(kind)
     ctx = mp.get_context("fork")
     blocks = [(i * SUBBLOCK // cores, (i + 1) * SUBBLOCK // cores) for i in range(cores)]
     with ctx.Pool(cores, initializer=_worker_init, initargs=(kind,)) as pool:
@@ -222,7 +225,10 @@ def workload_config(name, gpus, shape=None):
         M, N, K = BF16_SHAPE
         return {"workload": f"bf16 GEMM M={M} N={N} K={K}, A row-major, B column-major, fp32 accumulate, bf16 out",
                 "sharding": f"A/C row blocks over {gpus} GPU(s), B broadcast once (NCCL) outside the timed region",
-                "l2": "inputs (768 MB) larger than L2; no flush needed"}
+                "l2": "inputs (768 MB) larger than L2; no flush needed",
+                # the same text in both arms, so that their configs compare equal and neither claims more than it ran
+                "reference_arm_sample": f"--impl reference times the {SUBBLOCK}^3 fp32 sub-block per step on the host "
+                                        "cores (a rate comparison: the full problem is not run on the CPU)"}
     return {"workload": name}
 
 
@@ -263,11 +269,35 @@ class Workload:
         self.sharded.step(self.A, self.B, self.C)
 
     def host_bf16(self):
+        """Pinned host copies of this rank's operands.  Returns the bytes THIS rank moves per
+        step: its rows of A and, with several ranks, only its 1/world slice of B (the rest
+        arrives over NVLink, exo_b200/shard.py), and its rows of C back."""
         t = self.torch
         self.hA = t.empty(self.A.shape, dtype=self.A.dtype, pin_memory=True).copy_(self.A)
         self.hB = t.empty(self.B.shape, dtype=self.B.dtype, pin_memory=True).copy_(self.B)
         self.hC = t.empty(self.C.shape, dtype=self.C.dtype, pin_memory=True)
-        return (self.hA.numel() + self.hB.numel()) * 2, self.hC.numel() * 2
+        lo, hi = self.sharded.b_slices(self.B.shape[0])[self.rank]
+        b_rows = self.B.shape[0] if self.world == 1 else hi - lo
+        return (self.hA.numel() + b_rows * self.B.shape[1]) * 2, self.hC.numel() * 2
+
+    def verify_bf16(self, C, nrows=16):
+        """Row sample of a result against an fp32 reference of the same rows (torch, on the
+        GPU: a checker, not the product path): |delta| <= one bf16 ulp of the reference plus a
+        floor near zero.  Returns the number of rows checked; raises on a mismatch."""
+        t = self.torch
+        rows = self.A.shape[0]
+        pick = sorted({0, 1, 127, 128, 255, 256, 511, 512, rows // 2, rows - 129, rows - 2, rows - 1} |
+                      {(i * 2654435761) % rows for i in range(4)})
+        pick = [r for r in pick if 0 <= r < rows][:max(nrows, 1)]
+        idx = t.tensor(pick, device=self.A.device)
+        ref = self.A[idx].float() @ self.B.float().t()
+        got = C[idx].float() if C.is_cuda else C[idx.cpu()].to(self.A.device).float()
+        K = self.A.shape[1]
+        tol = ref.abs() * 2.0 ** -7 + 1e-3 * K ** 0.5 * 4e-4
+        bad = int(((got - ref).abs() > tol).sum().item())
+        if bad:
+            raise SystemExit(f"bench: {bad} elements of the verified rows are outside the bf16 tolerance")
+        return len(pick)
 
     def e2e_bf16(self):
         self.sharded.step(self.hA, self.hB, self.hC)
@@ -497,10 +527,28 @@ def run_ours(args):
     if rank == 0:
         sampler.start()
         time.sleep(0.3)
+    if args.workload == "bf16":
+        wl.C.zero_()  # so that the check below cannot pass on a stale result
     ms, t0, t1 = time_steps(torch, wl.step, args.steps, args.warmup, dist)
     clocks = sampler.stop(t0, t1) if rank == 0 else None
     lib.synchronize()
     value = wl.flops_total / (ms / 1e3) / 1e12
+    verified_rows = wl.verify_bf16(wl.C) if args.workload == "bf16" else 0
+
+    # the same launch back to back for a few seconds: the power-capped regime, with the SM clock it settles at
+    sustained = None
+    if args.workload == "bf16" and args.sustained_seconds > 0:
+        n = max(args.steps, int(args.sustained_seconds * 1e3 / max(ms, 1e-3)) + 1)
+        s2 = ClockSampler(local)
+        if rank == 0:
+            s2.start()
+            time.sleep(0.2)
+        sms, st0, st1 = time_steps(torch, wl.step, n, 1, dist)
+        sclk = s2.stop(st0, st1) if rank == 0 else None
+        sustained = {"value": wl.flops_total / (sms / 1e3) / 1e12, "unit": UNIT, "launches": n, "seconds": sms * n / 1e3,
+                     "ms_per_step": sms, "clocks": sclk}
+        if sclk and sclk.get("sm_mhz"):
+            sustained["ms_times_sm_mhz"] = sms * sclk["sm_mhz"]
 
     # Optional same-GPU, same-minute denominator: the vendor library's GEMM (torch.matmul ->
     # cuBLAS) on the same buffers with the same timing loop.  A library call, reported for
@@ -523,9 +571,17 @@ def run_ours(args):
         e2e_steps, e2e_ms, e2e_value = 0, None, None
     else:
         h2d, d2h = wl.host()
+        if dist is not None:  # whole-job bytes: every rank's share
+            tb = torch.tensor([h2d, d2h], device="cuda", dtype=torch.float64)
+            dist.all_reduce(tb)
+            h2d, d2h = int(tb[0].item()), int(tb[1].item())
         e2e_steps = max(1, min(args.steps, 5))
+        if args.workload == "bf16":
+            wl.hC.zero_()
         e2e_ms, _, _ = time_steps(torch, wl.e2e_step, e2e_steps, 1, dist)
         e2e_value = wl.flops_total / (e2e_ms / 1e3) / 1e12
+        if args.workload == "bf16":
+            verified_rows += wl.verify_bf16(wl.hC, 8)
 
     if rank != 0:
         if dist is not None:
@@ -549,11 +605,22 @@ def run_ours(args):
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic",
         "config": workload_config(args.workload, world, shape), "clocks": clocks,
-        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": d2h * world,
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_ms, "steps": e2e_steps},
         "gpu_launches": wl.launches_per_step * args.steps,
         "roofline": roofline,
+        "verified_rows": verified_rows,
     }
+    if sustained is not None:
+        line["sustained"] = sustained
+    if e2e_ms and d2h:
+        # how much of the end-to-end step the device-to-host copy of C alone accounts for at the
+        # pinned-copy rate of this box (measured below with one large copy each way)
+        line["e2e"]["pcie"] = pinned_copy_rates(torch, args.workload == "bf16" and wl.hC or None)
+        if line["e2e"]["pcie"]:
+            rate = line["e2e"]["pcie"]["d2h_gbs"]
+            line["e2e"]["d2h_bound_ms"] = d2h / world / (rate * 1e6)
+            line["e2e"]["d2h_bound_frac"] = line["e2e"]["d2h_bound_ms"] / e2e_ms
     if bcast_ms is not None:
         line["b_broadcast_ms"] = bcast_ms
     if library is not None:
@@ -573,6 +640,27 @@ def run_ours(args):
     print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()
+
+
+def pinned_copy_rates(torch, host_buf):
+    """GB/s of one large pinned-memory copy each way on this GPU (CUDA events): the ceiling the
+    end-to-end number sits under."""
+    if host_buf is None:
+        return None
+    n = min(host_buf.numel(), 256 << 20)
+    h = host_buf.view(-1)[:n]
+    d = torch.empty(n, dtype=h.dtype, device="cuda")
+    out = {}
+    for name, (dst, src) in (("h2d_gbs", (d, h)), ("d2h_gbs", (h, d))):
+        dst.copy_(src, non_blocking=True)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        dst.copy_(src, non_blocking=True)
+        e1.record()
+        torch.cuda.synchronize()
+        out[name] = n * h.element_size() / (e0.elapsed_time(e1) * 1e6)
+    return out
 
 
 def run_sweep(lib, torch, peaks, skip):
@@ -689,6 +777,8 @@ def main():
     ap.add_argument("--shape", default=None, help="MxNxK override for small profiling cases")
     ap.add_argument("--library-gemm", action="store_true",
                     help="bf16, 1 GPU: also time torch.matmul (cuBLAS) on the same buffers, for comparison")
+    ap.add_argument("--sustained-seconds", type=float, default=2.0,
+                    help="bf16: also time the launch back to back for about this long (0: skip)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")

@@ -30,6 +30,14 @@ PROTOTYPES = {
     "conv_on_cpu_stride_1": [vp] + [i64] * 6 + [vp] * 4 + [cbool, vp],
     "gemm_bf16_exo": [vp, i64, i64, i64, vp, vp, vp],
     "matmul_on_cpu_static": [vp, i64, i64, i64, vp, cbool, vp, vp, vp],
+    "ssyrk_exo": [vp, i64, i64, vp, vp],
+    "ssyrk_exo_ffma": [vp, i64, i64, vp, vp],
+    "ssyrk_exo_3xtf32": [vp, i64, i64, vp, vp],
+    # the Gemmini library's "auto" entry points (include/exo_b200_gemmini_shim.h)
+    "tiled_matmul_auto": [ctypes.c_size_t] * 3 + [vp] * 4 + [ctypes.c_size_t] * 4 + [ctypes.c_float] * 3
+                         + [ctypes.c_int, ctypes.c_float, ctypes.c_float] + [cbool] * 5 + [ctypes.c_uint8, ctypes.c_int],
+    "tiled_conv_auto": [ctypes.c_int] * 12 + [cbool] * 5 + [vp] * 4 + [ctypes.c_int, ctypes.c_float]
+                       + [ctypes.c_int] * 4,
 }
 for _n in _MM_INSTANCES:
     PROTOTYPES[f"cpu_matmul_{_n}"] = [vp, vp, cbool, vp, vp, vp]

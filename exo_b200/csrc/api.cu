@@ -5,6 +5,7 @@
 #include <cstdlib>
 #include <cstring>
 
+#include "../../include/exo_b200_gemmini_shim.h"
 #include "common.cuh"
 #include "kernels.cuh"
 
@@ -98,6 +99,28 @@ void sgemm_dispatch(const char* fn, void* ctxt, int path, int_fast32_t M, int_fa
   if (!check_cuda(e, fn)) return;
   if (!stage_out(c, cc)) return;
   finish(c, a.staged || b.staged || cc.staged);
+}
+
+// ---------------------------------------------------------------- SSYRK
+void ssyrk_dispatch(const char* fn, void* ctxt, int path, int_fast32_t N, int_fast32_t K, const float* A, float* C) {
+  clear_error();
+  if (bad_args(fn, N < 1 || K < 1, "N, K must be >= 1")) return;
+  if (bad_args(fn, !A || !C, "NULL tensor")) return;
+  ContextUse use(resolve_context(ctxt));
+  exo_b200_Context* c = use.get();
+  if (!c) return;
+  if (path < 0) path = c->sgemm_path;
+  Operand a, cc;
+  if (!stage_in(c, 0, A, sizeof(float) * (size_t)N * K, true, &a)) return;
+  if (!stage_in(c, 2, C, sizeof(float) * (size_t)N * N, true, &cc)) return;  // read (+=) and written
+  const float* dA = static_cast<const float*>(a.dev);
+  float* dC = static_cast<float*>(cc.dev);
+  const cudaError_t e = path == EXO_B200_SGEMM_3XTF32 ? launch_ssyrk_3xtf32_tc(c, N, K, dA, dC)
+                                                      : launch_ssyrk_ffma(c, N, K, dA, dC);
+  if (!check_cuda(e, fn)) return;
+  // a staged C travels back whole: its lower triangle went up unchanged and comes back unchanged
+  if (!stage_out(c, cc)) return;
+  finish(c, a.staged || cc.staged);
 }
 
 // ----------------------------------------------------------------- conv
@@ -270,6 +293,16 @@ void sgemm_exo_3xtf32(void* ctxt, int_fast32_t M, int_fast32_t N, int_fast32_t K
   sgemm_dispatch("sgemm_exo_3xtf32", ctxt, EXO_B200_SGEMM_3XTF32, M, N, K, A, B, C, true);
 }
 
+void ssyrk_exo(void* ctxt, int_fast32_t N, int_fast32_t K, const float* A, float* C) {
+  ssyrk_dispatch("ssyrk_exo", ctxt, EXO_B200_SGEMM_FFMA, N, K, A, C);
+}
+void ssyrk_exo_ffma(void* ctxt, int_fast32_t N, int_fast32_t K, const float* A, float* C) {
+  ssyrk_dispatch("ssyrk_exo_ffma", ctxt, EXO_B200_SGEMM_FFMA, N, K, A, C);
+}
+void ssyrk_exo_3xtf32(void* ctxt, int_fast32_t N, int_fast32_t K, const float* A, float* C) {
+  ssyrk_dispatch("ssyrk_exo_3xtf32", ctxt, EXO_B200_SGEMM_3XTF32, N, K, A, C);
+}
+
 void conv_specialized(void* ctxt, const float* inp, float* output, const float* weights, const float* bias) {
   // inp f32[5,82,102,128], output f32[5,80,100,128], weights f32[128,3,3,128], bias f32[128]
   clear_error();
@@ -380,6 +413,106 @@ EXOB200_CONV_INSTANCE(3, 4, 56, 64, 3, 64, 58)
 EXOB200_CONV_INSTANCE(17, 4, 28, 128, 3, 128, 30)
 EXOB200_CONV_INSTANCE(30, 4, 14, 256, 3, 256, 16)
 #undef EXOB200_CONV_INSTANCE
+
+// ---------------------------------------------------------------------------
+// The Gemmini software library's two "auto" entry points, as the reference's shim
+// overrides them (apps/gemmini/test/bare-metal/shims/gemmini.c): shape switch to the
+// generated instances; other shapes run on the generic kernels when the call asks for
+// nothing beyond what those compute, and are refused otherwise.
+void tiled_matmul_auto(size_t dim_I, size_t dim_J, size_t dim_K, const elem_t* A, const elem_t* B, const void* D,
+                       void* C, size_t stride_A, size_t stride_B, size_t stride_D, size_t stride_C,
+                       scale_t A_scale_factor, scale_t B_scale_factor, scale_acc_t D_scale_factor, int act,
+                       acc_scale_t scale, acc_scale_t bert_scale, bool repeating_bias, bool transpose_A,
+                       bool transpose_B, bool full_C, bool low_D, uint8_t weightA,
+                       exo_b200_tiled_matmul_type tiled_matmul_type) {
+  (void)stride_D, (void)D_scale_factor, (void)bert_scale, (void)repeating_bias, (void)low_D, (void)weightA,
+      (void)tiled_matmul_type;
+  const float c_scale = (float)scale;
+  const bool act_ = act != 0;
+  int8_t* out = static_cast<int8_t*>(C);
+  struct Instance {
+    size_t i, j, k;
+    const char* name;
+  };
+  // shapes: gemmini.c:20-51
+  static const Instance instances[] = {{512, 512, 512, "tiled_matmul_auto -> matmul_512x512x512"},
+                                       {12544, 256, 64, "tiled_matmul_auto -> matmul_4"},
+                                       {12544, 64, 256, "tiled_matmul_auto -> matmul_6"},
+                                       {3136, 512, 128, "tiled_matmul_auto -> matmul_14"},
+                                       {3136, 128, 512, "tiled_matmul_auto -> matmul_16"},
+                                       {784, 1024, 256, "tiled_matmul_auto -> matmul_27"}};
+  for (const Instance& in : instances)
+    if (dim_I == in.i && dim_J == in.j && dim_K == in.k) {
+      // like the reference shim, an instance takes A, B, C as dense and ignores D and the strides
+      matmul_i8_dispatch(in.name, (int_fast32_t)dim_I, (int_fast32_t)dim_J, (int_fast32_t)dim_K, &c_scale, act_, A, B,
+                         out);
+      return;
+    }
+  clear_error();
+  const char* why = nullptr;
+  if (D != nullptr) why = "a bias matrix D";
+  else if (transpose_A || transpose_B) why = "transposed operands";
+  else if (full_C) why = "full-width (int32) output";
+  else if (stride_A != dim_K || stride_B != dim_J || stride_C != dim_J) why = "strided operands";
+  else if (act != 0 && act != 1) why = "an activation other than none / ReLU";
+  else if (A_scale_factor != 1.0f || B_scale_factor != 1.0f) why = "input scale factors other than 1";
+  if (why) {
+    set_error(EXO_B200_ERR_UNSUPPORTED, std::string("tiled_matmul_auto: no generated instance for ") +
+                                            std::to_string(dim_I) + " x " + std::to_string(dim_J) + " x " +
+                                            std::to_string(dim_K) + ", and the generic kernel does not take " + why);
+    return;
+  }
+  matmul_i8_dispatch("tiled_matmul_auto -> matmul_on_cpu", (int_fast32_t)dim_I, (int_fast32_t)dim_J,
+                     (int_fast32_t)dim_K, &c_scale, act_, A, B, out);
+}
+
+void tiled_conv_auto(int batch_size, int in_row_dim, int in_col_dim, int in_channels, int out_channels,
+                     int out_row_dim, int out_col_dim, int stride, int input_dilation, int kernel_dilation,
+                     int padding, int kernel_dim, bool wrot180, bool trans_output_1203, bool trans_input_3120,
+                     bool trans_weight_1203, bool trans_weight_0132, const elem_t* input, const elem_t* weights,
+                     const acc_t* bias, elem_t* output, int act, acc_scale_t scale, int pool_size, int pool_stride,
+                     int pool_padding, exo_b200_tiled_matmul_type tiled_conv_type) {
+  (void)pool_stride, (void)pool_padding, (void)tiled_conv_type;
+  clear_error();
+  // the restrictions the reference shim enforces by exiting (gemmini.c:73-90), reported instead
+  const char* why = nullptr;
+  if (input_dilation != 1 || kernel_dilation != 1) why = "dilation must be 1";
+  else if (wrot180 || trans_output_1203 || trans_input_3120 || trans_weight_1203 || trans_weight_0132)
+    why = "transposed / rotated tensors are not supported";
+  else if (out_row_dim != out_col_dim || in_row_dim != in_col_dim) why = "images must be square";
+  if (why) {
+    set_error(EXO_B200_ERR_UNSUPPORTED, std::string("tiled_conv_auto: ") + why);
+    return;
+  }
+  const float c_scale = (float)scale;
+  const bool act_ = act != 0;
+  // shape switch of gemmini.c:120-131 (it tests only these three fields; an instance then
+  // takes its other sizes from its own definition, as there)
+  if (stride == 1 && out_row_dim == 56 && out_channels == 64) {
+    conv_i8_dispatch("tiled_conv_auto -> conv_3", 4, 56, 64, 3, 64, 58, output, bias, input, weights, act_, &c_scale);
+    return;
+  }
+  if (stride == 1 && out_row_dim == 28 && out_channels == 128) {
+    conv_i8_dispatch("tiled_conv_auto -> conv_17", 4, 28, 128, 3, 128, 30, output, bias, input, weights, act_,
+                     &c_scale);
+    return;
+  }
+  if (stride == 1 && out_row_dim == 14 && out_channels == 256) {
+    conv_i8_dispatch("tiled_conv_auto -> conv_30", 4, 14, 256, 3, 256, 16, output, bias, input, weights, act_,
+                     &c_scale);
+    return;
+  }
+  if (stride != 1) why = "stride must be 1";
+  else if (padding != 0) why = "padding must be 0 (pad the input, as the generated instances expect)";
+  else if (pool_size > 1) why = "pooling is not supported";
+  else if (out_row_dim != in_row_dim - kernel_dim + 1) why = "out_dim must equal in_dim - kernel_dim + 1";
+  if (why) {
+    set_error(EXO_B200_ERR_UNSUPPORTED, std::string("tiled_conv_auto: no generated instance for this shape, and ") + why);
+    return;
+  }
+  conv_i8_dispatch("tiled_conv_auto -> conv_on_cpu_stride_1", batch_size, out_row_dim, out_channels, kernel_dim,
+                   in_channels, in_row_dim, output, bias, input, weights, act_, &c_scale);
+}
 
 int exo_b200_selftest_bounded_wait(exo_b200_Context* ctxt, int limit_us) {
   clear_error();

@@ -304,9 +304,21 @@ std::vector<char> block_upload_order(const BlockPipeline& p) {
   return order;
 }
 
+static bool stream_is_capturing(cudaStream_t s) {
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(s, &cap) != cudaSuccess) {
+    cudaGetLastError();
+    return false;
+  }
+  return cap != cudaStreamCaptureStatusNone;
+}
+
 bool acquire_scratch(exo_b200_Context* c, int slot, size_t bytes) {
   if (!ensure_scratch(c, slot, bytes)) return false;
   if (c->scratch_busy[slot] && c->scratch_stream[slot] != c->stream) {
+    // A stream that is being captured may not depend on work outside its capture; a caller who
+    // captures orders the captured graph against earlier uses of the context themselves.
+    if (stream_is_capturing(c->stream)) return true;
     // cudaStreamWaitEvent on an event that has completed costs nothing on the device
     if (!check_cuda(cudaStreamWaitEvent(c->stream, c->scratch_ev[slot], 0), "cudaStreamWaitEvent(scratch)"))
       return false;
@@ -317,12 +329,7 @@ bool acquire_scratch(exo_b200_Context* c, int slot, size_t bytes) {
 void release_scratch(exo_b200_Context* c, int slot) {
   // An event recorded while the stream is being captured belongs to the capture and cannot be
   // waited on from outside it; a capturing caller orders its own streams.
-  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
-  if (cudaStreamIsCapturing(c->stream, &cap) != cudaSuccess) {
-    cudaGetLastError();
-    return;
-  }
-  if (cap != cudaStreamCaptureStatusNone) return;
+  if (stream_is_capturing(c->stream)) return;
   if (!c->scratch_ev[slot] &&
       cudaEventCreateWithFlags(&c->scratch_ev[slot], cudaEventDisableTiming) != cudaSuccess) {
     cudaGetLastError();

@@ -34,6 +34,9 @@ struct ConvPolicy {
   const float* __restrict__ bias;
   float* __restrict__ out;
 
+  static constexpr bool kTransposedB = false;
+  __device__ __forceinline__ bool tile_live(int, int, int, int) const { return true; }
+
   struct RowCtx {
     int64_t base;  // element offset of inp[n, 0, 0, 0]
     int iy0, ix0;  // input coordinates of tap (0, 0)

@@ -22,6 +22,10 @@
 //   void copy_b(float* smem, int k, int n)   cp.async of B(k, n..n+3) into smem, zero outside
 //   float4 init(int m, int n)          chain start for (m, n..n+3)
 //   void store(int m, int n, float4)   applies the epilogue and writes (bounds-checked)
+//   static constexpr bool kTransposedB B(k, n) is stored with k contiguous (an N x K row-major array):
+//                                      the B tile then takes the A tile's route through registers,
+//                                      with  float4 load_bt(int n, int k)  = B(k..k+3, n), zero outside
+//   bool tile_live(m0, n0, bm, bn)     false: the CTA of this tile has nothing to do and leaves at once
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -78,16 +82,27 @@ __device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
   return d;
 }
 
+// Resident CTAs per SM that the register budget is sized for.  8 x 8 outputs per thread need about
+// 190 registers to keep a k step's fragments and the next tile's operands in flight without spilling:
+// the 128-thread 128 x 64 configuration gets that (two CTAs per SM); the 256-thread 128 x 128 one is
+// held to 128 registers so that two CTAs (16 warps) share an SM, which is worth more there than the
+// few spilled values cost (measured at 8192^3: 55.3 against 48.4 TFLOP/s with one CTA per SM).
+template <int H, int THREADS>
+__host__ __device__ constexpr int min_ctas() {
+  return (H == 2 && THREADS == 128) ? 2 : 512 / THREADS;
+}
+
 template <class Policy, bool PACKED, int H, int TDY, int TDX>
-__global__ void __launch_bounds__(TDY * TDX, 512 / (TDY * TDX))
+__global__ void __launch_bounds__(TDY * TDX, min_ctas<H, TDY * TDX>())
 tile_kernel(const Policy P, int tiles_m, int tiles_n) {
   constexpr int THREADS = TDY * TDX;
   constexpr int QSM = 4 * TDY, QSN = 4 * TDX;  // rows / columns per quadrant
   constexpr int BM = QSM * H, BN = QSN * H;
   constexpr int AS_PITCH = BM + 4;  // floats; keeps 16-byte alignment, spreads the transposing stores
   constexpr int R = 4 * H;          // rows (and columns) per thread
+  constexpr int BS_PITCH = Policy::kTransposedB ? BN + 4 : BN;  // the transposing stores want the same skew as A's
   __shared__ __align__(16) float As[2][BK][AS_PITCH];
-  __shared__ __align__(16) float Bs[2][BK][BN];
+  __shared__ __align__(16) float Bs[2][BK][BS_PITCH];
 
   // CTA -> tile, grouped 8 tile-rows at a time so that CTAs resident together
   // share A rows and B columns in L2.
@@ -102,6 +117,7 @@ tile_kernel(const Policy P, int tiles_m, int tiles_n) {
   const int tn = in_group / gm;
   const int m0 = tm * BM, n0 = tn * BN;
   const int K = P.K;
+  if (!P.tile_live(m0, n0, BM, BN)) return;  // uniform over the CTA, before any barrier
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
@@ -125,14 +141,31 @@ tile_kernel(const Policy P, int tiles_m, int tiles_n) {
   // A goes through registers (it is transposed on the way into shared memory);
   // B is copied global -> shared asynchronously, 16 bytes (or 4 x 4) per thread.
   float4 pa[PA];
+  constexpr int PBT = Policy::kTransposedB ? BN / A_RSTEP : 1;  // passes over a k-contiguous B tile
+  float4 pbt[PBT];
   auto load_tile = [&](int k0, int buf) {
 #pragma unroll
     for (int h = 0; h < PA; h++) pa[h] = P.load_a(rc[h], m0 + a_row + h * A_RSTEP, k0 + a_kq);
+    if constexpr (Policy::kTransposedB) {
 #pragma unroll
-    for (int h = 0; h < PB; h++)
-      P.copy_b(&Bs[buf][b_k + h * B_KSTEP][b_c4], k0 + b_k + h * B_KSTEP, n0 + b_c4);
+      for (int h = 0; h < PBT; h++) pbt[h] = P.load_bt(n0 + a_row + h * A_RSTEP, k0 + a_kq);
+    } else {
+#pragma unroll
+      for (int h = 0; h < PB; h++)
+        P.copy_b(&Bs[buf][b_k + h * B_KSTEP][b_c4], k0 + b_k + h * B_KSTEP, n0 + b_c4);
+    }
   };
   auto store_tile = [&](int buf) {
+    if constexpr (Policy::kTransposedB) {
+#pragma unroll
+      for (int h = 0; h < PBT; h++) {
+        const int r = a_row + h * A_RSTEP;
+        Bs[buf][a_kq + 0][r] = pbt[h].x;
+        Bs[buf][a_kq + 1][r] = pbt[h].y;
+        Bs[buf][a_kq + 2][r] = pbt[h].z;
+        Bs[buf][a_kq + 3][r] = pbt[h].w;
+      }
+    }
 #pragma unroll
     for (int h = 0; h < PA; h++) {
       const int r = a_row + h * A_RSTEP;
@@ -276,9 +309,16 @@ cudaError_t launch_tiles(cudaStream_t stream, const Policy& P, int sm_count = 14
     const char* e = getenv("EXOB200_FFMA_TILE");  // 32, 64, 128 or 12864 forces a tile size (timing experiments)
     return e ? atoi(e) : 0;
   }();
+  const int64_t half_tiles = ((int64_t)(P.M + 127) / 128) * ((P.N + 63) / 64);
   int tile;
   if (force == 32 || force == 64 || force == 128 || force == 12864) {
     tile = force;
+  } else if (big_tiles <= sm_count && half_tiles >= (2 * sm_count) / 3) {
+    // Medium problems: not enough 128 x 128 tiles for every SM, but enough 128 x 64 ones for most.
+    // One or two four-warp CTAs per SM, each thread with the full 8 x 8 register tile (twice the FMAs
+    // per shared-memory load of the 4 x 4 tiles below).  1024^3: 63 us against 78 us with 64 x 64
+    // tiles and 107 us with 128 x 128; 1000^3: 61 against 77 us.
+    tile = 12864;
   } else if (big_tiles > sm_count || (big_tiles > sm_count / 2 && P.N > 64)) {  // N <= 64 would waste half of a 128-wide tile
     // From half an SM count of 128 x 128 tiles on, they beat four times as many 64 x 64 tiles
     // (1536^3, 144 tiles: 171 against 222 us; 1024^3, 64 tiles: 117 against 78 us): a lone

@@ -12,6 +12,10 @@ namespace exob200 {
 cudaError_t launch_sgemm_ffma(exo_b200_Context* ctx, int64_t M, int64_t N, int64_t K, const float* A,
                               const float* B, float* C);
 
+// C += A * A^T on the upper triangle (ssyrk_ffma.cu); the 3xTF32 variant is in tc_gemm.cu
+cudaError_t launch_ssyrk_ffma(exo_b200_Context* ctx, int64_t N, int64_t K, const float* A, float* C);
+cudaError_t launch_ssyrk_3xtf32_tc(exo_b200_Context* ctx, int64_t N, int64_t K, const float* A, float* C);
+
 struct ConvShape {
   int batch, in_h, in_w, in_c, out_h, out_w, out_c, kdim, pad;
   // element strides of the weight tensor for (ky, kx, ci); co is contiguous

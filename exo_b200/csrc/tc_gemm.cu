@@ -100,6 +100,7 @@ struct EpiParams {
   float scale;   // I8
   int act;       // I8
   int vec_ok;    // 16-byte stores allowed
+  int tri;       // TF32X3: 1 = only the upper triangle (col >= row) of a square C is updated (SSYRK)
 };
 
 // ------------------------------------------------------------- epilogues
@@ -259,6 +260,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
         int tm, tn;
         tile_coord(t, tm, tn);
         const int m0 = tm * BM, n0 = tn * BN;
+        if (ep.tri && n0 + BN <= m0) continue;  // entirely below the diagonal: every role skips it
         for (int kb = 0; kb < num_kb; kb++) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, WAIT_LIMIT_NS)) {
             report_timeout(status, abort_flag, 1);
@@ -306,6 +308,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
       uint32_t acc_phase = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        if (ep.tri) {
+          int tm, tn;
+          tile_coord(t, tm, tn);
+          if (tn * BN + BN <= tm * BM) continue;
+        }
         for (int kb0 = 0; kb0 < num_kb && ok; kb0 += chunk_kb) {
           const int kb1 = min(num_kb, kb0 + chunk_kb);
           if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, WAIT_LIMIT_NS)) {
@@ -368,6 +375,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
       int tm, tn;
       tile_coord(t, tm, tn);
       const int m0 = tm * BM, n0 = tn * BN;
+      if (ep.tri && n0 + BN <= m0) continue;
       const int row = m0 + q * 32 + lane;
       bool ok = true;
       const int half = (warp - 2) >> 2;  // 3xTF32 only: which 128 columns of the tile this warp owns
@@ -444,9 +452,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
             const int r = idx >> 2, c4 = (idx & 3) * 4;
             p4[it] = *reinterpret_cast<const float4*>(patch + r * EPI_PITCH + c4);
             gptr[it] = static_cast<float*>(ep.C) + (int64_t)(row0 + r) * ep.ldc + col0 + c4;
-            okk[it] = row0 + r < M && col0 + c4 < N;
+            okk[it] = row0 + r < M && col0 + c4 < N && !(ep.tri && col0 + c4 + 3 < row0 + r);
+            // a quad that straddles the diagonal takes the element-wise path below
+            const bool whole = ep.vec_ok && !(ep.tri && col0 + c4 < row0 + r);
             if (okk[it]) {
-              if (ep.vec_ok) {
+              if (whole) {
                 c[it] = *reinterpret_cast<const float4*>(gptr[it]);
               } else {
                 c[it].x = gptr[it][0];
@@ -464,13 +474,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
             c[it].y += p4[it].y;
             c[it].z += p4[it].z;
             c[it].w += p4[it].w;
-            if (ep.vec_ok) {
+            const int rr = row0 + ((it * 32 + lane) >> 2);
+            const int lim = ep.tri ? rr : -1;  // columns below lim are not part of the update
+            if (ep.vec_ok && col0 + c4 >= lim) {
               *reinterpret_cast<float4*>(gptr[it]) = c[it];
             } else {
-              gptr[it][0] = c[it].x;
-              if (col0 + c4 + 1 < N) gptr[it][1] = c[it].y;
-              if (col0 + c4 + 2 < N) gptr[it][2] = c[it].z;
-              if (col0 + c4 + 3 < N) gptr[it][3] = c[it].w;
+              if (col0 + c4 + 0 >= lim) gptr[it][0] = c[it].x;
+              if (col0 + c4 + 1 < N && col0 + c4 + 1 >= lim) gptr[it][1] = c[it].y;
+              if (col0 + c4 + 2 < N && col0 + c4 + 2 >= lim) gptr[it][2] = c[it].z;
+              if (col0 + c4 + 3 < N && col0 + c4 + 3 >= lim) gptr[it][3] = c[it].w;
             }
           }
           __syncwarp();
@@ -736,6 +748,34 @@ cudaError_t launch_sgemm_3xtf32_tc(exo_b200_Context* ctx, int64_t M, int64_t N, 
   const cudaError_t e = launch_tc<MODE_TF32X3>(ctx, ma0, ma1, mb0, mb1, M, N, Kp, ep);
   release_scratch(ctx, 0);
   release_scratch(ctx, 1);
+  return e;
+}
+
+// ---------------------------------------------------------------- SSYRK (3xTF32)
+// C += A * A^T on the upper triangle.  Both operands of the product are rows of A with k
+// contiguous -- the layout the kernel wants for either side -- so ONE hi/lo split of A serves
+// as the A operand (boxes of 128 rows) and as the B operand (boxes of 256 rows); tiles below
+// the diagonal are skipped by every role and the epilogue masks the diagonal tiles.
+cudaError_t launch_ssyrk_3xtf32_tc(exo_b200_Context* ctx, int64_t N, int64_t K, const float* A, float* C) {
+  if (N > INT32_MAX || K > INT32_MAX - 64) return cudaErrorInvalidValue;
+  const int64_t Kp = (K + 3) / 4 * 4;
+  const size_t a_elems = (size_t)(N * Kp);
+  if (!acquire_scratch(ctx, 0, 2 * a_elems * sizeof(float))) return cudaErrorMemoryAllocation;
+  float* a_hi = static_cast<float*>(ctx->scratch[0]);
+  float* a_lo = a_hi + a_elems;
+  const int blocks = (int)std::min<int64_t>((N * Kp + 255) / 256, (int64_t)ctx->sm_count * 16);
+  split_rows_kernel<<<blocks, 256, 0, ctx->stream>>>(A, N, (int)K, (int)Kp, a_hi, a_lo);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  CUtensorMap ma0, ma1, mb0, mb1;
+  const CUtensorMapDataType dt = CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  if (!make_kmajor_map(&ma0, dt, 4, a_hi, N, Kp, Kp * 4, BM)) return cudaErrorUnknown;
+  if (!make_kmajor_map(&ma1, dt, 4, a_lo, N, Kp, Kp * 4, BM)) return cudaErrorUnknown;
+  if (!make_kmajor_map(&mb0, dt, 4, a_hi, N, Kp, Kp * 4, BN)) return cudaErrorUnknown;
+  if (!make_kmajor_map(&mb1, dt, 4, a_lo, N, Kp, Kp * 4, BN)) return cudaErrorUnknown;
+  EpiParams ep{C, N, 0.f, 0, (N % 4 == 0 && aligned16(C)) ? 1 : 0, 1};
+  e = launch_tc<MODE_TF32X3>(ctx, ma0, ma1, mb0, mb1, N, N, Kp, ep);
+  release_scratch(ctx, 0);
   return e;
 }
 

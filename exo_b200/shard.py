@@ -5,7 +5,15 @@
 is split into contiguous row blocks of A and C, one per rank; B is broadcast
 once from rank 0 (NCCL over NVLink when the tensors are CUDA tensors) and then
 every rank runs the same single-GPU kernel on its block.  There is no
-collective inside a step.
+collective inside a step when the operands are resident in device memory.
+
+When a step is given HOST buffers (the reference's calling convention) on more
+than one rank, B would otherwise cross PCIe once per rank.  Instead every rank
+uploads only its 1/world slice of B, the slices are all-gathered over NVLink
+into each rank's own copy (NCCL on local buffers: no peer loads), and the rank's
+rows of A and C stream through the library's host-pointer row pipeline while
+that happens.  Host-to-device bytes per step then stay at |A| + |B| for the
+whole job however many ranks take part.
 
 Failure handling stays on the host: before the one collective, every rank
 checks in through the process group's key-value store with a deadline.  A rank
@@ -93,6 +101,7 @@ class ShardedGemm:
         self.store = store
         self._gemm = gemm or _default_bf16_gemm
         self._round = 0
+        self._dev_b = None  # this rank's device copy of B for host-operand steps
 
     def broadcast_b(self, b):
         """The only exchange: B from rank 0 into every rank's own memory."""
@@ -111,14 +120,65 @@ class ShardedGemm:
         """This rank's row block of a full M-row tensor."""
         return full[self.block.start:self.block.stop]
 
+    def b_slices(self, n_cols: int) -> list[tuple[int, int]]:
+        """Column ranges of B (rows of its [N, K] array), one per rank, for the
+        upload-a-slice-then-all-gather exchange; equal sizes when world divides N."""
+        base, extra = divmod(n_cols, self.world)
+        out, start = [], 0
+        for r in range(self.world):
+            n = base + (1 if r < extra else 0)
+            out.append((start, start + n))
+            start += n
+        return out
+
+    def gather_b_from_host(self, b_host, device=None):
+        """Every rank uploads its slice of the host copy of B and receives the other
+        slices from its peers.  Returns this rank's full device copy (kept and reused
+        across steps).  ``device`` None: CPU tensors stay on the CPU (gloo ranks)."""
+        import torch
+
+        if self._dev_b is None or self._dev_b.shape != b_host.shape or self._dev_b.dtype != b_host.dtype:
+            self._dev_b = torch.empty(b_host.shape, dtype=b_host.dtype, device=device or b_host.device)
+        full = self._dev_b
+        slices = self.b_slices(b_host.shape[0])
+        lo, hi = slices[self.rank]
+        if hi > lo:
+            full[lo:hi].copy_(b_host[lo:hi], non_blocking=True)
+        if self.world == 1:
+            return full
+        if self.store is not None:
+            self._round += 1
+            check_in(self.store, self.rank, self.world, f"gather{self._round}", self.timeout_s)
+        flat = full.view(torch.uint8) if full.dtype != torch.uint8 else full
+        if len({h - l for (l, h) in slices}) == 1 and hasattr(self.dist, "all_gather_into_tensor") \
+                and flat.is_cuda:
+            self.dist.all_gather_into_tensor(flat, flat[lo:hi])
+        else:  # ragged split (or a backend without the fused form): one broadcast per slice
+            for r, (l, h) in enumerate(slices):
+                if h > l:
+                    self.dist.broadcast(flat[l:h], src=r)
+        return full
+
     def step(self, a_rows, b, c_rows):
-        if self.block.rows == 0:
+        if self.block.rows == 0 and self.world == 1:
             return c_rows
         if a_rows.shape[0] != self.block.rows or c_rows.shape[0] != self.block.rows:
             raise ShardError(f"rank {self.rank}: expected {self.block.rows} rows, got "
                              f"A {a_rows.shape[0]} / C {c_rows.shape[0]}")
+        if self.world > 1 and not getattr(b, "is_cuda", False) and self._wants_device():
+            # host operands on several ranks: B crosses PCIe once per job, not once per rank
+            import torch
+
+            b = self.gather_b_from_host(b, device=torch.device("cuda", torch.cuda.current_device()))
+        if self.block.rows == 0:
+            return c_rows
         self._gemm(a_rows, b, c_rows)
         return c_rows
+
+    def _wants_device(self) -> bool:
+        """True when the GEMM runs on a GPU (the default kernel call); a test-supplied
+        ``gemm`` on CPU ranks keeps every tensor where it is."""
+        return self._gemm is _default_bf16_gemm
 
 
 def _default_bf16_gemm(a_rows, b, c_rows):

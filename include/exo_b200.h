@@ -2,10 +2,11 @@
  * exo_b200 -- B200 (sm_100a) GEMM / convolution kernels behind the C ABI that
  * Exo's compiler `exocc` writes into its generated headers.
  *
- * Every "reference-identical" prototype below is character-for-character the
- * one exocc emits for the corresponding Exo procedure, so this library links
- * wherever the generated C was linked (the `add_exo_library` CMake target,
- * src/exo/cmake/AddExoLibrary.cmake:29-31).  ABI rules, from
+ * Every "reference-identical" prototype below is the one exocc emits for the
+ * corresponding Exo procedure (sgemm_exo and conv_specialized character for
+ * character; the Gemmini-typed ones up to the type of the context pointer, see
+ * EXO_B200_GEMMINI_CONTEXT), so this library links wherever the generated C was
+ * linked (the `add_exo_library` CMake target, src/exo/cmake/AddExoLibrary.cmake:29-31).  ABI rules, from
  * src/exo/backend/LoopIR_compiler.py:524-619 and src/exo/core/LoopIR.py:436-466:
  *   - first parameter `ctxt`; sizes are int_fast32_t by value; bool by value;
  *   - numeric scalars (e.g. `scale : f32`) are passed BY POINTER;
@@ -80,23 +81,34 @@ void conv( void *ctxt, int_fast32_t out_h, int_fast32_t out_w, int_fast32_t out_
  * tests/golden/asplos25/test_gemmini_matmul_old/test_matmul.txt:92. */
 void matmul_on_cpu( void *ctxt, int_fast32_t N, int_fast32_t M, int_fast32_t K, const float* scale, bool act, const int8_t* A, const int8_t* B, int8_t* C );
 
+/* Type of the context pointer in the Gemmini-typed prototypes.  exocc names it after
+ * the library stem (`gemmini_lib_Context` in the app build, apps/gemmini/src/CMakeLists.txt:10-13;
+ * `test_case_Context` in tests/golden/test_apps/test_gemmini_matmul.txt:32-56).  The pointer is
+ * never dereferenced here, so the default is void; a translation unit that also includes the
+ * generated header defines EXO_B200_GEMMINI_CONTEXT to that header's type first
+ * (-DEXO_B200_GEMMINI_CONTEXT=gemmini_lib_Context) and the declarations below then repeat the
+ * generated ones token for token instead of conflicting with them. */
+#ifndef EXO_B200_GEMMINI_CONTEXT
+#define EXO_B200_GEMMINI_CONTEXT void
+#endif
+
 /* The size-specialised instances the Gemmini app exports
  * (tests/golden/test_apps/test_gemmini_matmul.txt:99-198): `cpu_matmul_*` is the
  * plain-C twin, `matmul_*` the accelerator version; both compute the same
  * result (apps/gemmini/test/run_matmul.c:63 asserts equality) and both map to
  * the same GPU kernel here.  ctxt is never dereferenced. */
-void cpu_matmul_512x512x512( void *ctxt, const float* scale, bool act, const int8_t* A, const int8_t* B, int8_t* C );
-void matmul_512x512x512( void *ctxt, const float* scale, bool act, const int8_t* A, const int8_t* B, int8_t* C );
-void cpu_matmul_4( void *ctxt, const float* scale, bool act, const int8_t* A, const int8_t* B, int8_t* C );   /* 12544 x 256, K = 64 */
-void matmul_4( void *ctxt, const float* scale, bool act, const int8_t* A, const int8_t* B, int8_t* C );
-void cpu_matmul_6( void *ctxt, const float* scale, bool act, const int8_t* A, const int8_t* B, int8_t* C );   /* 12544 x 64, K = 256 */
-void matmul_6( void *ctxt, const float* scale, bool act, const int8_t* A, const int8_t* B, int8_t* C );
-void cpu_matmul_14( void *ctxt, const float* scale, bool act, const int8_t* A, const int8_t* B, int8_t* C );  /* 3136 x 512, K = 128 */
-void matmul_14( void *ctxt, const float* scale, bool act, const int8_t* A, const int8_t* B, int8_t* C );
-void cpu_matmul_16( void *ctxt, const float* scale, bool act, const int8_t* A, const int8_t* B, int8_t* C );  /* 3136 x 128, K = 512 */
-void matmul_16( void *ctxt, const float* scale, bool act, const int8_t* A, const int8_t* B, int8_t* C );
-void cpu_matmul_27( void *ctxt, const float* scale, bool act, const int8_t* A, const int8_t* B, int8_t* C );  /* 784 x 1024, K = 256 */
-void matmul_27( void *ctxt, const float* scale, bool act, const int8_t* A, const int8_t* B, int8_t* C );
+void cpu_matmul_512x512x512( EXO_B200_GEMMINI_CONTEXT *ctxt, const float* scale, bool act, const int8_t* A, const int8_t* B, int8_t* C );
+void matmul_512x512x512( EXO_B200_GEMMINI_CONTEXT *ctxt, const float* scale, bool act, const int8_t* A, const int8_t* B, int8_t* C );
+void cpu_matmul_4( EXO_B200_GEMMINI_CONTEXT *ctxt, const float* scale, bool act, const int8_t* A, const int8_t* B, int8_t* C );   /* 12544 x 256, K = 64 */
+void matmul_4( EXO_B200_GEMMINI_CONTEXT *ctxt, const float* scale, bool act, const int8_t* A, const int8_t* B, int8_t* C );
+void cpu_matmul_6( EXO_B200_GEMMINI_CONTEXT *ctxt, const float* scale, bool act, const int8_t* A, const int8_t* B, int8_t* C );   /* 12544 x 64, K = 256 */
+void matmul_6( EXO_B200_GEMMINI_CONTEXT *ctxt, const float* scale, bool act, const int8_t* A, const int8_t* B, int8_t* C );
+void cpu_matmul_14( EXO_B200_GEMMINI_CONTEXT *ctxt, const float* scale, bool act, const int8_t* A, const int8_t* B, int8_t* C );  /* 3136 x 512, K = 128 */
+void matmul_14( EXO_B200_GEMMINI_CONTEXT *ctxt, const float* scale, bool act, const int8_t* A, const int8_t* B, int8_t* C );
+void cpu_matmul_16( EXO_B200_GEMMINI_CONTEXT *ctxt, const float* scale, bool act, const int8_t* A, const int8_t* B, int8_t* C );  /* 3136 x 128, K = 512 */
+void matmul_16( EXO_B200_GEMMINI_CONTEXT *ctxt, const float* scale, bool act, const int8_t* A, const int8_t* B, int8_t* C );
+void cpu_matmul_27( EXO_B200_GEMMINI_CONTEXT *ctxt, const float* scale, bool act, const int8_t* A, const int8_t* B, int8_t* C );  /* 784 x 1024, K = 256 */
+void matmul_27( EXO_B200_GEMMINI_CONTEXT *ctxt, const float* scale, bool act, const int8_t* A, const int8_t* B, int8_t* C );
 
 /* Gemmini-style int8 NHWC convolution (apps/gemmini/src/exo/conv.py:6-55):
  * weights i8[kernel_dim,kernel_dim,in_channel,out_channel], bias i32[1,out_channel]
@@ -107,12 +119,12 @@ void conv_on_cpu_stride_1( void *ctxt, int_fast32_t batch_size, int_fast32_t out
 /* Size-specialised instances, tests/golden/test_apps/test_gemmini_conv.txt:96-146:
  * conv_3: batch 4, 58->56, 64->64, 3x3;  conv_17: batch 4, 30->28, 128->128;
  * conv_30: batch 4, 16->14, 256->256. */
-void conv_3_cpu( void *ctxt, int8_t* output, const int32_t* bias, const int8_t* inp, const int8_t* weights, bool act, const float* scale );
-void conv_3( void *ctxt, int8_t* output, const int32_t* bias, const int8_t* inp, const int8_t* weights, bool act, const float* scale );
-void conv_17_cpu( void *ctxt, int8_t* output, const int32_t* bias, const int8_t* inp, const int8_t* weights, bool act, const float* scale );
-void conv_17( void *ctxt, int8_t* output, const int32_t* bias, const int8_t* inp, const int8_t* weights, bool act, const float* scale );
-void conv_30_cpu( void *ctxt, int8_t* output, const int32_t* bias, const int8_t* inp, const int8_t* weights, bool act, const float* scale );
-void conv_30( void *ctxt, int8_t* output, const int32_t* bias, const int8_t* inp, const int8_t* weights, bool act, const float* scale );
+void conv_3_cpu( EXO_B200_GEMMINI_CONTEXT *ctxt, int8_t* output, const int32_t* bias, const int8_t* inp, const int8_t* weights, bool act, const float* scale );
+void conv_3( EXO_B200_GEMMINI_CONTEXT *ctxt, int8_t* output, const int32_t* bias, const int8_t* inp, const int8_t* weights, bool act, const float* scale );
+void conv_17_cpu( EXO_B200_GEMMINI_CONTEXT *ctxt, int8_t* output, const int32_t* bias, const int8_t* inp, const int8_t* weights, bool act, const float* scale );
+void conv_17( EXO_B200_GEMMINI_CONTEXT *ctxt, int8_t* output, const int32_t* bias, const int8_t* inp, const int8_t* weights, bool act, const float* scale );
+void conv_30_cpu( EXO_B200_GEMMINI_CONTEXT *ctxt, int8_t* output, const int32_t* bias, const int8_t* inp, const int8_t* weights, bool act, const float* scale );
+void conv_30( EXO_B200_GEMMINI_CONTEXT *ctxt, int8_t* output, const int32_t* bias, const int8_t* inp, const int8_t* weights, bool act, const float* scale );
 
 /* ------------------------------------------------------------------------
  * Entry points with no generated counterpart, same conventions
@@ -174,6 +186,18 @@ void conv_nhwc_exo_3xtf32( void *ctxt, int_fast32_t batch_size, int_fast32_t in_
  *   - Calls no cudaMalloc / cudaFree / cudaHostAlloc and creates no context. */
 #define EXO_B200_STATIC_SCRATCH_BYTES (4u << 20)
 void matmul_on_cpu_static( void *stream, int_fast32_t N, int_fast32_t M, int_fast32_t K, const float* scale, bool act, const int8_t* A, const int8_t* B, int8_t* C );
+
+/* SSYRK: C += A * A^T on the upper triangle (j >= i), A : f32[N,K], C : f32[N,N] row-major; the
+ * strict lower triangle of C is not modified.  The computation that the reference's
+ * MKL comparison benchmark measures (apps/x86/ssyrk/bench_ssyrk.cpp:11-13,49-65: cblas_ssyrk,
+ * CblasRowMajor, CblasUpper, CblasNoTrans, alpha = beta = 1); there is no Exo procedure for it in
+ * the reference, so the name and signature follow sgemm_exo's conventions.  Arithmetic as in
+ * sgemm_exo: per element one fused-multiply-add chain in increasing k from the incoming C value
+ * (_ffma, which ssyrk_exo always takes: bit-identical to sgemm_exo(N, N, K, A, A^T, C) on the
+ * triangle), or 3xTF32 tensor cores (_3xtf32; error bound of sgemm_exo_3xtf32). */
+void ssyrk_exo( void *ctxt, int_fast32_t N, int_fast32_t K, const float* A, float* C );
+void ssyrk_exo_ffma( void *ctxt, int_fast32_t N, int_fast32_t K, const float* A, float* C );
+void ssyrk_exo_3xtf32( void *ctxt, int_fast32_t N, int_fast32_t K, const float* A, float* C );
 
 /* ------------------------------------------------------------------------
  * Context and error side channel (additions; the reference has neither)

@@ -63,6 +63,7 @@ class Port:
         L.oracle_set_threads.argtypes = [ctypes.c_int]
         L.oracle_sgemm.argtypes = [_i64] * 3 + [_vp] * 3
         L.oracle_sgemm_naive.argtypes = [_i64] * 3 + [_vp] * 3
+        L.oracle_ssyrk.argtypes = [_i64] * 2 + [_vp] * 2
         L.oracle_conv.argtypes = [_i64] * 8 + [_vp] * 4
         L.oracle_conv_nhwc.argtypes = [_i64] * 7 + [ctypes.c_bool] + [_vp] * 4
         L.oracle_im2col_nhwc.argtypes = [_i64] * 6 + [_vp] * 2
@@ -71,7 +72,7 @@ class Port:
         L.oracle_gemm_bf16.argtypes = [_i64] * 3 + [_vp] * 3
         L.oracle_bf16_widen.argtypes = [_i64, _vp, _vp]
         L.oracle_bf16_round.argtypes = [_i64, _vp, _vp]
-        for name in ("oracle_sgemm", "oracle_sgemm_naive", "oracle_conv", "oracle_conv_nhwc",
+        for name in ("oracle_sgemm", "oracle_sgemm_naive", "oracle_ssyrk", "oracle_conv", "oracle_conv_nhwc",
                      "oracle_im2col_nhwc", "oracle_matmul_i8", "oracle_conv_i8",
                      "oracle_gemm_bf16", "oracle_bf16_widen", "oracle_bf16_round",
                      "oracle_set_threads"):
@@ -88,6 +89,13 @@ class Port:
         assert A.dtype == B.dtype == C.dtype == np.float32
         fn = self.lib.oracle_sgemm_naive if naive else self.lib.oracle_sgemm
         fn(M, N, K, _ptr(A), _ptr(B), _ptr(C))
+        return C
+
+    def ssyrk(self, A, C):
+        """C += A @ A.T on the upper triangle (j >= i), in place; returns C."""
+        N, K = A.shape
+        assert C.shape == (N, N) and A.dtype == C.dtype == np.float32
+        self.lib.oracle_ssyrk(N, K, _ptr(A), _ptr(C))
         return C
 
     def conv(self, inp, weights, bias):

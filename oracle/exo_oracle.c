@@ -72,6 +72,26 @@ void oracle_sgemm_naive(int64_t M, int64_t N, int64_t K, const float *A, const f
     }
 }
 
+/* ------------------------------------------------------------------ SSYRK
+ * The reference holds no Exo procedure for SSYRK, only the comparison benchmark
+ * apps/x86/ssyrk/bench_ssyrk.cpp:49-58: cblas_ssyrk(CblasRowMajor, CblasUpper,
+ * CblasNoTrans, n, k, 1.0, a, k, 1.0, c, n), i.e.  C[i,j] += sum_k A[i,k] * A[j,k]
+ * for j >= i; the strict lower triangle of C is not referenced.  The BLAS call does
+ * not fix an accumulation order; this restatement (and the kernels checked against
+ * it) use the order of the reference's SGEMM, one fmaf chain in increasing k that
+ * starts from the incoming C -- parity for SSYRK is therefore pinned to
+ * oracle_sgemm on (A, A^T), not to a reference kernel. */
+void oracle_ssyrk(int64_t N, int64_t K, const float *A, float *C) {
+#pragma omp parallel for num_threads(g_threads) schedule(dynamic, 8)
+  for (int64_t i = 0; i < N; i++)
+    for (int64_t j = i; j < N; j++) {
+      float c = C[i * N + j];
+      const float *a = A + i * K, *b = A + j * K;
+      for (int64_t k = 0; k < K; k++) c = fmaf(a[k], b[k], c);
+      C[i * N + j] = c;
+    }
+}
+
 /* ------------------------------------------------------------------- conv
  * apps/x86/conv/conv.py:10-45: NHWC input, weights f32[Ci,Kh,Kw,Co], bias,
  * stride 1, no padding, ReLU via select(0, x, x, 0)  (= x > 0 ? x : 0).

@@ -27,6 +27,17 @@ def test_harnesses_compile_and_link(tmp_path):
     build(tmp_path, "sgemm_check.cpp", "g++", ["-std=c++17"])
     build(tmp_path, "matmul_check.c", "gcc", ["-std=gnu11"])
     build(tmp_path, "conv_check.cpp", "g++", ["-std=c++17"])
+    build(tmp_path, "shim_check.c", "gcc", ["-std=gnu11"])
+
+
+@pytest.mark.gpu
+def test_gemmini_shim_c_caller(tmp_path):
+    """tiled_matmul_auto / tiled_conv_auto with the upstream parameter lists: generated
+    instances, generic shapes, and refused requests."""
+    exe = build(tmp_path, "shim_check.c", "gcc", ["-std=gnu11"])
+    r = subprocess.run([exe], capture_output=True, text=True)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "Correct" in r.stdout
 
 
 @pytest.mark.gpu

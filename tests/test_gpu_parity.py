@@ -115,6 +115,52 @@ def test_sgemm_ffma_full_size_rows_against_oracle(lib, port, torch):
     assert np.array_equal(bits(dC[rows].cpu().numpy()), bits(want))
 
 
+# -------------------------------------------------------------------- SSYRK
+# sizes of the reference's comparison benchmark (apps/x86/ssyrk/bench_ssyrk.cpp:60-65: n = 64 .. 2048,
+# k = 16 .. 2048, powers of two) plus ragged ones
+SSYRK_CASES = [(64, 16), (64, 2048), (100, 33), (129, 7), (256, 512), (1000, 77), (1024, 1024), (2048, 16), (2048, 2048)]
+
+
+@pytest.mark.parametrize("shape", SSYRK_CASES)
+def test_ssyrk_ffma_bit_exact_on_the_upper_triangle(lib, port, torch, shape):
+    """C += A A^T for j >= i, one fmaf chain per element in increasing k: bit-identical to
+    the oracle (itself equal to the SGEMM oracle on (A, A^T)); the strict lower triangle of
+    C keeps its bits."""
+    N, K = shape
+    A = inputs.uniform_f32(1000 + N + K, (N, K))
+    C0 = inputs.uniform_f32(2000 + N, (N, N))
+    dC = dev(torch, C0)
+    lib.ssyrk_exo(None, N, K, dev(torch, A), dC)
+    torch.cuda.synchronize()
+    port.set_threads(os.cpu_count() or 1)
+    try:
+        want = port.ssyrk(A, C0.copy())
+    finally:
+        port.set_threads(1)
+    assert np.array_equal(bits(dC.cpu().numpy()), bits(want))
+    if N <= 256:  # host pointers too
+        C = C0.copy()
+        lib.ssyrk_exo_ffma(None, N, K, A, C)
+        assert np.array_equal(bits(C), bits(want))
+
+
+@pytest.mark.parametrize("shape", [(64, 16), (100, 33), (256, 512), (1000, 77), (2048, 2048), (300, 4100)])
+def test_ssyrk_3xtf32_within_tolerance(lib, torch, shape):
+    N, K = shape
+    A = inputs.uniform_f32(1000 + N + K, (N, K))
+    C0 = inputs.uniform_f32(2000 + N, (N, N))
+    dC = dev(torch, C0)
+    lib.ssyrk_exo_3xtf32(None, N, K, dev(torch, A), dC)
+    torch.cuda.synchronize()
+    C = dC.cpu().numpy()
+    A64 = A.astype(np.float64)
+    ref = C0.astype(np.float64) + A64 @ A64.T
+    bound = tf32x3_bound(K) * (np.abs(C0).astype(np.float64) + np.abs(A64) @ np.abs(A64).T)
+    up = np.triu(np.ones((N, N), bool))
+    assert (np.abs(C - ref)[up] <= bound[up] + 1e-30).all()
+    assert np.array_equal(bits(C)[~up], bits(C0)[~up])  # the strict lower triangle is untouched
+
+
 # ------------------------------------------------------------ SGEMM (3xTF32)
 # Tolerance, stated: per element, with S = |C0| + sum_k |a_ik| |b_kj|,
 #     |C_gpu - C_fp64| <= (1.5e-6 + 1e-6 * min(K, 1024) / 1024 + 1e-7 * K / 1024) * S.

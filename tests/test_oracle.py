@@ -58,6 +58,18 @@ def test_sgemm_threads_do_not_change_bits(port):
     assert np.array_equal(bits(one), bits(four))
 
 
+def test_ssyrk_port_equals_sgemm_port_on_the_triangle(port):
+    """The reference has no SSYRK kernel (only an MKL benchmark); the restatement is pinned
+    to the SGEMM restatement on (A, A^T), which is itself pinned to the reference."""
+    A = inputs.uniform_f32(31, (97, 130))
+    C0 = inputs.uniform_f32(32, (97, 97))
+    got = port.ssyrk(A, C0.copy())
+    full = port.sgemm(A, np.ascontiguousarray(A.T), C0.copy())
+    up = np.triu(np.ones((97, 97), bool))
+    assert np.array_equal(bits(got)[up], bits(full)[up])
+    assert np.array_equal(bits(got)[~up], bits(C0)[~up])
+
+
 def test_sgemm_close_to_fp64(port):
     """The reference's own tolerance for SGEMM is 3 decimals (tests/test_x86.py:151-161)."""
     A, B, C0 = cases.sgemm_inputs(100, 100, 1000)

@@ -89,6 +89,44 @@ def test_sharded_gemm_equals_single_rank(world, M):
     assert np.array_equal(got, full)
 
 
+def _gather_worker(rank, world, port, N, K, q):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from exo_b200.shard import ShardedGemm
+    from tests import inputs
+
+    true_b = torch.from_numpy(inputs.normal_bf16(9, (N, K)).view(np.int16))
+    sg = ShardedGemm(dist, 256, N, K, gemm=_cpu_gemm)
+    lo, hi = sg.b_slices(N)[rank]
+    mine = torch.full((N, K), 0x7FC0, dtype=torch.int16)  # only this rank's slice is valid on this rank
+    mine[lo:hi] = true_b[lo:hi]
+    for _ in range(2):  # second round reuses the rank's buffer
+        full = sg.gather_b_from_host(mine)
+        q.put((rank, bool(torch.equal(full, true_b)), (lo, hi)))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,N", [(2, 40), (3, 40)])
+def test_b_is_uploaded_in_slices_and_gathered(world, N):
+    """The host-operand exchange of the sharded GEMM: every rank contributes only its own
+    slice of B (equal slices at world 2, ragged 14/13/13 at world 3) and ends with all of it."""
+    port = free_port()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_gather_worker, args=(r, world, port, N, 16, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    out = [q.get(timeout=120) for _ in range(2 * world)]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert all(ok for (_, ok, _) in out), out
+    slices = sorted({s for (_, _, s) in out})
+    assert slices[0][0] == 0 and slices[-1][1] == N and all(a[1] == b[0] for a, b in zip(slices, slices[1:]))
+
+
 def _late_worker(rank, world, port, q):
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
