@@ -40,9 +40,9 @@ def test_header_repeats_the_generated_prototypes_token_for_token():
     (tests/golden/generated_prototypes.txt, extracted from the reference's golden files by
     tests/golden/make_prototypes.py) appears in include/exo_b200.h as the same line, once
     the context type macro is set to the generated header's own type."""
-    r = subprocess.run(["gcc", "-E", "-P", "-DEXO_B200_GEMMINI_CONTEXT=test_case_Context", HEADER],
-                       capture_output=True, text=True, check=True)
-    lines = {l.strip() for l in r.stdout.splitlines()}
+    # expand the one macro by hand (the preprocessor would also rewrite bool to _Bool)
+    text = re.sub(r"/\*.*?\*/", "", open(HEADER).read(), flags=re.S)
+    lines = {l.strip().replace("EXO_B200_GEMMINI_CONTEXT", "test_case_Context") for l in text.splitlines()}
     want = [l.split(": ", 1)[1].strip() for l in open(PROTOTYPES).read().splitlines() if l.strip()]
     assert len(want) == 20
     missing = [w for w in want if w not in lines]
