@@ -616,7 +616,7 @@ def run_ours(args):
     if e2e_ms and d2h:
         # how much of the end-to-end step the device-to-host copy of C alone accounts for at the
         # pinned-copy rate of this box (measured below with one large copy each way)
-        line["e2e"]["pcie"] = pinned_copy_rates(torch, args.workload == "bf16" and wl.hC or None)
+        line["e2e"]["pcie"] = pinned_copy_rates(torch, wl.hC if args.workload == "bf16" else None)
         if line["e2e"]["pcie"]:
             rate = line["e2e"]["pcie"]["d2h_gbs"]
             line["e2e"]["d2h_bound_ms"] = d2h / world / (rate * 1e6)
@@ -629,10 +629,14 @@ def run_ours(args):
         del wl
         torch.cuda.empty_cache()
         if not args.no_sweep:
-            line["sweep"] = run_sweep(lib, torch, peaks, args.workload)
+            probes = probe_peaks(lib, torch)
+            line["measured_peaks"] = probes
+            line["sweep"] = run_sweep(lib, torch, peaks, args.workload, probes)
             try:
-                line["sgemm_shapes"] = run_shapes(lib, torch, peaks)
-                line["sgemm_aspect_k512"] = run_shapes(lib, torch, peaks, ASPECT_SHAPES, ("ffma",))
+                line["sgemm_shapes"] = run_shapes(lib, torch, peaks, probes=probes)
+                line["sgemm_aspect_k512"] = run_shapes(lib, torch, peaks, ASPECT_SHAPES, ("ffma",), probes)
+                line["sgemm_squares"] = run_shapes(lib, torch, peaks, SQUARE_SHAPES, ("ffma",), probes)
+                line["ssyrk"] = run_ssyrk(lib, torch, probes)
             except Exception as e:
                 line["sgemm_shapes"] = {"error": str(e)[:200]}
         if not args.no_cpu:
@@ -663,11 +667,27 @@ def pinned_copy_rates(torch, host_buf):
     return out
 
 
-def run_sweep(lib, torch, peaks, skip):
+def probe_peaks(lib, torch):
+    """Ceilings measured on this GPU by the library's probe kernels (packed fp32 FMA from registers;
+    tcgen05.mma with operands resident in shared memory), ~40 ms each; the computed SIMT figure
+    (SMs x 128 lanes x 2 x max clock) is kept beside the measured one."""
+    sm_count = torch.cuda.get_device_properties(0).multi_processor_count
+    out = {"fp32_simt_computed": sm_count * 128 * 2 * 1.965e9 / 1e12}
+    for key, what in (("fp32_simt", 0), ("int8_tensor", 1), ("bf16_tensor", 2), ("tf32_tensor", 3)):
+        v = lib.dll.exo_b200_measure_peak(what, 40)
+        out[key] = v if v > 0 else None
+    return out
+
+
+def run_sweep(lib, torch, peaks, skip, probes=None):
     """Short device-resident timings of the other workloads (5 steps each)."""
     out = {}
-    sm_count = torch.cuda.get_device_properties(0).multi_processor_count
-    simt_peak = sm_count * 128 * 2 * 1.965e9 / 1e12  # fp32 FFMA at max SM clock
+    probes = probes or {}
+    simt_peak = probes.get("fp32_simt") or probes.get("fp32_simt_computed")
+    simt_name = "fp32 SIMT measured (packed FMA probe)" if probes.get("fp32_simt") else "fp32 SIMT at max SM clock (computed)"
+    i8_peak = probes.get("int8_tensor") or peaks["bf16_tflops"] * 2
+    i8_name = "int8 tensor measured (tcgen05.mma probe)" if probes.get("int8_tensor") else "2 x bf16 measured (nominal int8 ratio)"
+    tf32_peak = probes.get("tf32_tensor") or peaks["bf16_tflops"] / 2
     for name in ("sgemm_ffma", "sgemm_3xtf32", "i8", "i8_512", "conv", "conv_3xtf32", "conv1x1", "conv1x1_3xtf32", "conv_ref", "conv_ref_3xtf32",
                  "conv_i8", "bf16"):
         if name == skip:
@@ -678,11 +698,11 @@ def run_sweep(lib, torch, peaks, skip):
             lib.synchronize()
             tf = wl.flops_total / (ms / 1e3) / 1e12
             if name in ("sgemm_ffma", "conv", "conv1x1", "conv_ref"):
-                peak, pname = simt_peak, "fp32 SIMT at max SM clock (computed)"
+                peak, pname = simt_peak, simt_name
             elif name in ("sgemm_3xtf32", "conv_3xtf32", "conv1x1_3xtf32", "conv_ref_3xtf32"):
-                peak, pname = peaks["bf16_tflops"] / 2 / 3, "bf16 measured / 2 (tf32) / 3 (three MMAs per product)"
+                peak, pname = tf32_peak / 3, "tf32 tensor peak / 3 (three MMAs per product)"
             elif name in ("i8", "i8_512", "conv_i8"):
-                peak, pname = peaks["bf16_tflops"] * 2, "2 x bf16 measured (nominal int8 ratio)"
+                peak, pname = i8_peak, i8_name
             else:
                 peak, pname = peaks["bf16_tflops"], "bf16 measured"
             out[name] = {"tflops": tf, "ms": ms, "peak": peak, "frac": tf / peak, "peak_is": pname,
@@ -704,13 +724,50 @@ ASPECT_SHAPES = [(32768, 8, 512), (16384, 16, 512), (8192, 32, 512), (4096, 64, 
                  (16, 16384, 512), (8, 32768, 512)]
 
 
-def run_shapes(lib, torch, peaks, shapes=None, paths=("ffma", "3xtf32")):
+# the square sizes of the reference's SGEMM bench (apps/x86/sgemm/bench_sgemm.cpp:58-84: 64 .. 1984 in steps of 64 up
+# to 512, then coarser), every fourth of them here to keep the sweep short
+SQUARE_SHAPES = [(n, n, n) for n in (64, 128, 192, 256, 320, 384, 448, 512, 640, 768, 896, 1024, 1152, 1280, 1408, 1536,
+                                     1664, 1792, 1920, 2048)]
+
+
+def run_ssyrk(lib, torch, probes):
+    """SSYRK at sizes of the reference's comparison benchmark (apps/x86/ssyrk/bench_ssyrk.cpp:60-65),
+    flops counted its way: k n (n + 1)."""
+    out = []
+    gen = torch.Generator(device="cuda").manual_seed(4)
+    simt_peak = probes.get("fp32_simt") or probes.get("fp32_simt_computed")
+    for (n, k) in ((256, 256), (1024, 1024), (2048, 512), (2048, 2048)):
+        A = torch.rand((n, k), generator=gen, device="cuda") * 2 - 1
+        C = torch.zeros((n, n), device="cuda")
+        row = {"shape": [n, k]}
+        for path, fn in (("ffma", lib.ssyrk_exo_ffma), ("3xtf32", lib.ssyrk_exo_3xtf32)):
+            for _ in range(3):
+                fn(None, n, k, A, C)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(20):
+                fn(None, n, k, A, C)
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / 20
+            tf = k * n * (n + 1.0) / ms / 1e9
+            row[path] = {"us": ms * 1e3, "tflops": tf}
+            if path == "ffma":
+                row[path]["frac_of_simt"] = tf / simt_peak
+        out.append(row)
+    lib.synchronize()
+    return out
+
+
+def run_shapes(lib, torch, peaks, shapes=None, paths=("ffma", "3xtf32"), probes=None):
     """The SGEMM shape sweep (squares and ragged / skinny shapes) on both fp32
     paths, device time per launch.  Small shapes finish faster than the host can
     launch them, so launches are replayed from a CUDA graph: R x [L2 flush (a
     256 MB write), GEMM], minus a graph of R flushes alone; median of 5 replays."""
-    sm_count = torch.cuda.get_device_properties(0).multi_processor_count
-    simt_peak = sm_count * 128 * 2 * 1.965e9 / 1e12
+    probes = probes or {}
+    simt_peak = probes.get("fp32_simt") or probes.get("fp32_simt_computed")
+    tf32_peak = probes.get("tf32_tensor") or peaks["bf16_tflops"] / 2
     hbm = peaks["hbm_gbs"]
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
     R = 10
@@ -756,7 +813,7 @@ def run_shapes(lib, torch, peaks, shapes=None, paths=("ffma", "3xtf32")):
 
             ms = max(replay_ms(body) - flush_ms, 1e-6)
             tf, gbs = flops / ms / 1e9, nbytes / ms / 1e6
-            peak_tf = simt_peak if path == "ffma" else peaks["bf16_tflops"] / 6
+            peak_tf = simt_peak if path == "ffma" else tf32_peak / 3
             # the roofline that binds: min(compute peak, bandwidth x arithmetic intensity)
             ceiling = min(peak_tf, hbm * row["flop_per_byte"] / 1e3)
             row[path] = {"us": ms * 1e3, "tflops": tf, "gbs": gbs, "bound": "hbm" if ceiling < peak_tf else "compute",

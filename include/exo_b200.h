@@ -232,6 +232,15 @@ int exo_b200_synchronize( exo_b200_Context* ctxt );
  * it shows that a wait that cannot complete ends as an error code, not a hang. */
 int exo_b200_selftest_bounded_wait( exo_b200_Context* ctxt, int limit_us );
 
+/* Measures a ceiling of the GPU that the default context is on, for roofline fractions: a probe
+ * kernel that issues nothing but the instruction in question (packed fp32 FMA from registers;
+ * tcgen05.mma with operands resident in shared memory) runs for about `milliseconds` (1..500) and
+ * the achieved rate is returned in TFLOP/s (int8: Tera-ops/s), or a negative value on failure
+ * (see last_error).  Allocates a few bytes and synchronises the default stream. */
+enum { EXO_B200_PEAK_FP32_SIMT = 0, EXO_B200_PEAK_INT8_TENSOR = 1, EXO_B200_PEAK_BF16_TENSOR = 2,
+       EXO_B200_PEAK_TF32_TENSOR = 3 };
+double exo_b200_measure_peak( int what, int milliseconds );
+
 /* Error of the most recent call on this thread (EXO_B200_OK if it succeeded). */
 int exo_b200_last_error( void );
 const char* exo_b200_last_error_string( void );

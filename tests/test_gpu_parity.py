@@ -537,6 +537,23 @@ def test_context_of_another_device_is_made_current(lib, port, torch):
     ctx.close()
 
 
+def test_measured_peaks_are_plausible(lib):
+    """The probe kernels behind the roofline denominators: packed fp32 FMA from registers and
+    tcgen05.mma with operands resident in shared memory.  Bounds are loose physical ones for a
+    B200 (148 SMs x 128 lanes x 2 x 1.965 GHz = 74.4 TFLOP/s fp32; int8 about twice bf16)."""
+    simt = lib.dll.exo_b200_measure_peak(0, 20)
+    i8 = lib.dll.exo_b200_measure_peak(1, 20)
+    bf16 = lib.dll.exo_b200_measure_peak(2, 20)
+    tf32 = lib.dll.exo_b200_measure_peak(3, 20)
+    assert lib.dll.exo_b200_last_error() == 0, lib.dll.exo_b200_last_error_string()
+    print(f"measured peaks: fp32 SIMT {simt:.1f}, int8 {i8:.0f}, bf16 {bf16:.0f}, tf32 {tf32:.0f} T(FL)OP/s")
+    assert 45.0 < simt < 80.0
+    assert 1000.0 < bf16 < 2600.0
+    assert 1.5 * bf16 < i8 < 2.5 * bf16
+    assert 0.35 * bf16 < tf32 < 0.65 * bf16
+    assert lib.dll.exo_b200_measure_peak(9, 20) < 0 and lib.dll.exo_b200_last_error() != 0
+
+
 def test_error_side_channel_on_gpu(lib):
     import exo_b200
 
