@@ -480,7 +480,9 @@ cudaError_t launch_conv_3xtf32_tc(exo_b200_Context* ctx, const ConvShape& s, con
   const CUtensorMapDataType dt = CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
   if (!make_input_map(&ma0, dt, 4, x_hi, s, p)) return cudaErrorUnknown;
   if (!make_input_map(&ma1, dt, 4, x_lo, s, p)) return cudaErrorUnknown;
-  const int bn = s.out_c <= 128 ? 128 : 256;
+  // the narrowest instruction shape that covers Co: with Co = 64 a 128-wide MMA would spend half of
+  // its columns on padding
+  const int bn = s.out_c <= 64 ? 64 : s.out_c <= 128 ? 128 : 256;
   {
     cuuint64_t dims[2] = {(cuuint64_t)Kp, (cuuint64_t)s.out_c};
     cuuint64_t strides[1] = {(cuuint64_t)Kp * 4};
@@ -488,8 +490,9 @@ cudaError_t launch_conv_3xtf32_tc(exo_b200_Context* ctx, const ConvShape& s, con
     if (!make_tiled_map(&mb0, dt, 2, w_hi, dims, strides, box)) return cudaErrorUnknown;
     if (!make_tiled_map(&mb1, dt, 2, w_lo, dims, strides, box)) return cudaErrorUnknown;
   }
-  const cudaError_t e = bn == 128 ? launch_conv<CONV_TF32X3, 128>(ctx, ma0, ma1, mb0, mb1, p)
-                                  : launch_conv<CONV_TF32X3, 256>(ctx, ma0, ma1, mb0, mb1, p);
+  const cudaError_t e = bn == 64    ? launch_conv<CONV_TF32X3, 64>(ctx, ma0, ma1, mb0, mb1, p)
+                        : bn == 128 ? launch_conv<CONV_TF32X3, 128>(ctx, ma0, ma1, mb0, mb1, p)
+                                    : launch_conv<CONV_TF32X3, 256>(ctx, ma0, ma1, mb0, mb1, p);
   release_scratch(ctx, 0);
   release_scratch(ctx, 1);
   return e;
