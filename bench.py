@@ -582,6 +582,12 @@ def run_ours(args):
         e2e_value = wl.flops_total / (e2e_ms / 1e3) / 1e12
         if args.workload == "bf16":
             verified_rows += wl.verify_bf16(wl.hC, 8)
+    pcie = None
+    if not args.no_e2e and args.workload == "bf16":
+        hsave = wl.hC.clone()  # the copies below overwrite it
+        pcie = pinned_copy_rates(torch, wl.hC, dist)
+        wl.hC.copy_(hsave)
+        del hsave
 
     if rank != 0:
         if dist is not None:
@@ -613,14 +619,16 @@ def run_ours(args):
     }
     if sustained is not None:
         line["sustained"] = sustained
-    if e2e_ms and d2h:
-        # how much of the end-to-end step the device-to-host copy of C alone accounts for at the
-        # pinned-copy rate of this box (measured below with one large copy each way)
-        line["e2e"]["pcie"] = pinned_copy_rates(torch, wl.hC if args.workload == "bf16" else None)
-        if line["e2e"]["pcie"]:
-            rate = line["e2e"]["pcie"]["d2h_gbs"]
-            line["e2e"]["d2h_bound_ms"] = d2h / world / (rate * 1e6)
-            line["e2e"]["d2h_bound_frac"] = line["e2e"]["d2h_bound_ms"] / e2e_ms
+    if e2e_ms and d2h and pcie:
+        # The floor PCIe sets for the step: both directions busy at once, at the rates this box gave when
+        # every rank copied both ways at the same time.  bound_frac near 1 = the step is the copies.
+        line["e2e"]["pcie"] = pcie
+        sfx = "_sum_over_ranks" if world > 1 else ""
+        rate = pcie["bidir_each_way_gbs" + sfx]
+        line["e2e"]["pcie_bound_ms"] = max(d2h, h2d) / (rate * 1e6)
+        line["e2e"]["pcie_bound_frac"] = line["e2e"]["pcie_bound_ms"] / e2e_ms
+        line["e2e"]["limiter"] = ("device-to-host copy of C" if d2h >= h2d else "host-to-device copy of A and B") + \
+            " over PCIe with both directions busy"
     if bcast_ms is not None:
         line["b_broadcast_ms"] = bcast_ms
     if library is not None:
@@ -646,24 +654,54 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
-def pinned_copy_rates(torch, host_buf):
-    """GB/s of one large pinned-memory copy each way on this GPU (CUDA events): the ceiling the
-    end-to-end number sits under."""
+def pinned_copy_rates(torch, host_buf, dist=None):
+    """GB/s of large pinned-memory copies on this box (CUDA events): one direction at a time, and both
+    directions at once on two streams (what an end-to-end step does).  With several ranks all of them
+    copy at the same time -- their links may share a PCIe switch or a host memory controller -- and the
+    per-rank minimum and the sum over ranks are reported: the ceiling the end-to-end number sits under."""
     if host_buf is None:
         return None
     n = min(host_buf.numel(), 256 << 20)
     h = host_buf.view(-1)[:n]
+    h2 = torch.empty(n, dtype=h.dtype, pin_memory=True)
     d = torch.empty(n, dtype=h.dtype, device="cuda")
-    out = {}
-    for name, (dst, src) in (("h2d_gbs", (d, h)), ("d2h_gbs", (h, d))):
-        dst.copy_(src, non_blocking=True)
+    d2 = torch.empty(n, dtype=h.dtype, device="cuda")
+    side = torch.cuda.Stream()
+    nbytes = n * h.element_size()
+
+    def timed(fn):
+        fn()
         torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+            torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        dst.copy_(src, non_blocking=True)
+        fn()
         e1.record()
         torch.cuda.synchronize()
-        out[name] = n * h.element_size() / (e0.elapsed_time(e1) * 1e6)
+        return nbytes / (e0.elapsed_time(e1) * 1e6)
+
+    def both():
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            h2.copy_(d2, non_blocking=True)
+        d.copy_(h, non_blocking=True)
+        torch.cuda.current_stream().wait_stream(side)
+
+    out = {"h2d_gbs": timed(lambda: d.copy_(h, non_blocking=True)),
+           "d2h_gbs": timed(lambda: h.copy_(d, non_blocking=True)),
+           "bidir_each_way_gbs": timed(both)}
+    if dist is not None:
+        keys = sorted(out)
+        t = torch.tensor([out[k] for k in keys], device="cuda", dtype=torch.float64)
+        tmin = t.clone()
+        dist.all_reduce(t)
+        dist.all_reduce(tmin, op=dist.ReduceOp.MIN)
+        out = {"ranks_copy_concurrently": dist.get_world_size()}
+        for i, k in enumerate(keys):
+            out[k + "_sum_over_ranks"] = float(t[i].item())
+            out[k + "_min_rank"] = float(tmin[i].item())
     return out
 
 

@@ -52,6 +52,8 @@ SUPPORT = {
     "exo_b200_context_set_stream": ([vp, vp], None),
     "exo_b200_context_set_sgemm_path": ([vp, ctypes.c_int], None),
     "exo_b200_set_default_stream": ([vp], None),
+    "exo_b200_context_cache_weights": ([vp, ctypes.c_int], None),
+    "exo_b200_context_invalidate": ([vp], None),
     "exo_b200_synchronize": ([vp], ctypes.c_int),
     "exo_b200_selftest_bounded_wait": ([vp, ctypes.c_int], ctypes.c_int),
     "exo_b200_measure_peak": ([ctypes.c_int, ctypes.c_int], ctypes.c_double),

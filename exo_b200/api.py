@@ -12,6 +12,7 @@ the library's error side channel after each call and raises ``ExoB200Error``.
 from __future__ import annotations
 
 import ctypes
+import threading
 
 import numpy as np
 
@@ -55,20 +56,30 @@ def _convert(arg, argtype, keepalive):
         return int(arg)
     if isinstance(arg, float) and argtype is _lib.vp:
         # numeric scalars travel by pointer in Exo's ABI
-        holder = np.array([arg], np.float32)
+        holder = ctypes.c_float(arg)
         keepalive.append(holder)
-        return ctypes.c_void_p(holder.ctypes.data)
+        return ctypes.cast(ctypes.pointer(holder), ctypes.c_void_p)
     raise ValueError(f"unrecognized type {type(arg)}")
+
+
+_raw_stream = None  # torch._C._cuda_getCurrentRawStream where available: the stream handle without a Stream object
 
 
 def _sync_stream_for(args):
     """Device tensors run on torch's current stream."""
+    global _raw_stream
     for a in args:
         if _is_torch(a) and a.is_cuda:
-            import torch
+            if _raw_stream is None:
+                import torch
 
-            return torch.cuda.current_stream(a.device).cuda_stream
+                fast = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+                _raw_stream = fast if fast is not None else (lambda i: torch.cuda.current_stream(i).cuda_stream)
+            return _raw_stream(a.device.index)
     return None
+
+
+_last_default_stream = threading.local()  # what this thread last installed as the library's default stream
 
 
 class ProcWrapper:
@@ -85,13 +96,13 @@ class ProcWrapper:
             raise TypeError(f"{self._name} takes {len(self._argtypes)} arguments ({len(args)} given)")
         stream = _sync_stream_for(args)
         ctx = args[0] if isinstance(args[0], Context) else None
-        if stream is not None:
-            if ctx is not None:
+        if ctx is not None:
+            if stream is not None:
                 self._dll.exo_b200_context_set_stream(ctx.handle, stream)
-            else:
-                self._dll.exo_b200_set_default_stream(stream)
-        elif ctx is None:
-            self._dll.exo_b200_set_default_stream(None)
+        elif getattr(_last_default_stream, "value", -1) != stream:
+            # the library keeps the default stream per host thread; tell it only when it changes
+            self._dll.exo_b200_set_default_stream(stream)
+            _last_default_stream.value = stream
         keepalive = []  # per call, so concurrent callers cannot free each other's scalars
         conv = [_convert(a, t, keepalive) for a, t in zip(args, self._argtypes)]
         self._fn(*conv)

@@ -352,6 +352,7 @@ bool ensure_scratch(exo_b200_Context* c, int slot, size_t bytes) {
     cudaFree(c->scratch[slot]);
     c->scratch[slot] = nullptr;
     c->scratch_bytes[slot] = 0;
+    if (slot == 2) c->wkey_valid = false;
   }
   if (!check_cuda(cudaMalloc(&c->scratch[slot], bytes), "cudaMalloc(scratch)")) return false;
   c->scratch_bytes[slot] = bytes;
@@ -379,7 +380,7 @@ void exo_b200_context_destroy(exo_b200_Context* c) {
   cudaStreamSynchronize(c->stream);
   for (int i = 0; i < 4; i++)
     if (c->stage[i]) cudaFree(c->stage[i]);
-  for (int i = 0; i < 2; i++) {
+  for (int i = 0; i < 3; i++) {
     if (c->scratch[i]) cudaFree(c->scratch[i]);
     if (c->scratch_ev[i]) cudaEventDestroy(c->scratch_ev[i]);
   }
@@ -422,6 +423,22 @@ void exo_b200_context_set_sgemm_path(exo_b200_Context* c, int path) {
   if (!c || c->magic != kContextMagic) return;
   ContextUse use(c);
   c->sgemm_path = path;
+}
+
+void exo_b200_context_cache_weights(exo_b200_Context* ctxt, int enable) {
+  clear_error();
+  ContextUse use(resolve_context(ctxt));
+  exo_b200_Context* c = use.get();
+  if (!c) return;
+  c->cache_weights = enable != 0;
+  c->wkey_valid = false;
+}
+
+void exo_b200_context_invalidate(exo_b200_Context* ctxt) {
+  clear_error();
+  ContextUse use(resolve_context(ctxt));
+  exo_b200_Context* c = use.get();
+  if (c) c->wkey_valid = false;
 }
 
 void exo_b200_set_default_stream(void* stream) { tl_default_stream = static_cast<cudaStream_t>(stream); }

@@ -25,6 +25,15 @@ struct DeviceStatus {
 
 }  // namespace exob200
 
+namespace exob200 {
+// identity of a weight tensor whose TF32 split is held in the context (tensor-core convolution)
+struct WeightKey {
+  const void* ptr;
+  int in_c, out_c, kdim;
+  int64_t stride_ky, stride_kx, stride_ci;
+};
+}  // namespace exob200
+
 struct exo_b200_Context {
   uint32_t magic;
   int device;
@@ -35,14 +44,17 @@ struct exo_b200_Context {
   void* stage[4];
   size_t stage_bytes[4];
   // device scratch for kernels that need it (repacked operands)
-  void* scratch[2];
-  size_t scratch_bytes[2];
+  void* scratch[3];  // 0, 1: per-call operand copies; 2: the split weights of the tensor-core convolution
+  size_t scratch_bytes[3];
   // Each scratch slot remembers the stream of its last user and an event recorded after the
   // last kernel that reads it, so that a call on ANOTHER stream waits for that reader before
   // its pre-pass overwrites the slot (calls on one stream are ordered anyway).
-  cudaEvent_t scratch_ev[2];
-  cudaStream_t scratch_stream[2];
-  bool scratch_busy[2];
+  cudaEvent_t scratch_ev[3];
+  cudaStream_t scratch_stream[3];
+  bool scratch_busy[3];
+  // weight cache (off unless exo_b200_context_cache_weights switched it on)
+  bool cache_weights, wkey_valid;
+  exob200::WeightKey wkey;
   // resident CTA pairs of the two cluster kernels on this context's device (0 = not asked yet)
   int max_pairs[4];
   exob200::DeviceStatus* status_dev;   // device word

@@ -29,6 +29,7 @@
 #include <cuda.h>
 
 #include <algorithm>
+#include <cstring>
 
 #include "i8_epilogue.cuh"
 #include "kernels.cuh"
@@ -132,6 +133,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  grid_dep_wait();  // the fp32 path's operands come from the split pre-pass that this launch may overlap
 
   const int tiles_per_image = p.tiles_h * p.tiles_w;
   const int num_tiles = p.batch * tiles_per_image * p.tiles_n;
@@ -345,23 +347,27 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
   }
 }
 
-// fp32 pre-pass: elementwise hi/lo split of the input (layout unchanged)
-__global__ void split_elementwise_kernel(const float* __restrict__ x, int64_t n, float* __restrict__ hi,
-                                         float* __restrict__ lo) {
-  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
-    float h, l;
-    split_tf32(__ldg(x + i), h, l);
-    hi[i] = h;
-    lo[i] = l;
+// fp32 pre-pass, one launch for both operands.  Blocks [0, x_blocks): elementwise hi/lo split of the input
+// (layout unchanged).  The remaining blocks: weights (either layout, given as strides) -> hi, lo as a
+// K-major [Co][Kp] matrix with K ordered (ky, kx, ci), zero in the pad columns; skipped (w_blocks = 0)
+// when the context still holds the split of these weights.
+__global__ void conv_split_kernel(const float* __restrict__ x, int64_t n, float* __restrict__ x_hi,
+                                  float* __restrict__ x_lo, int x_blocks, const float* __restrict__ w, ConvShape s,
+                                  int K, int Kp, float* __restrict__ w_hi, float* __restrict__ w_lo) {
+  grid_dep_launch();
+  if ((int)blockIdx.x < x_blocks) {
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)x_blocks * blockDim.x) {
+      float h, l;
+      split_tf32(__ldg(x + i), h, l);
+      x_hi[i] = h;
+      x_lo[i] = l;
+    }
+    return;
   }
-}
-
-// fp32 pre-pass: weights (either layout, given as strides) -> hi, lo as a K-major
-// [Co][Kp] matrix with K ordered (ky, kx, ci); zero in the pad columns.
-__global__ void split_weights_kernel(const float* __restrict__ w, ConvShape s, int K, int Kp, float* __restrict__ hi,
-                                     float* __restrict__ lo) {
+  const int w_blocks = (int)gridDim.x - x_blocks;
   const int64_t total = (int64_t)s.out_c * Kp;
-  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+  for (int64_t i = (blockIdx.x - x_blocks) * (int64_t)blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)w_blocks * blockDim.x) {
     const int co = (int)(i / Kp), k = (int)(i - (int64_t)co * Kp);
     float h = 0.f, l = 0.f;
     if (k < K) {
@@ -369,8 +375,8 @@ __global__ void split_weights_kernel(const float* __restrict__ w, ConvShape s, i
       const int ky = tap / s.kdim, kx = tap - ky * s.kdim;
       split_tf32(__ldg(w + ky * s.w_stride_ky + kx * s.w_stride_kx + ci * s.w_stride_ci + co), h, l);
     }
-    hi[i] = h;
-    lo[i] = l;
+    w_hi[i] = h;
+    w_lo[i] = l;
   }
 }
 
@@ -393,12 +399,15 @@ bool make_input_map(CUtensorMap* m, CUtensorMapDataType dt, int elem, const void
 
 template <int MODE, int BN>
 cudaError_t launch_conv(exo_b200_Context* ctx, const CUtensorMap& a0, const CUtensorMap& a1, const CUtensorMap& b0,
-                        const CUtensorMap& b1, ConvTcParams p) {
+                        const CUtensorMap& b1, ConvTcParams p, bool after_prepass = false) {
   EXOB200_SMEM_ATTR_ONCE((conv_tc_kernel<MODE, BN>), (conv_smem_bytes<MODE, BN>()), ctx->device);
   p.tiles_n = (p.co + BN - 1) / BN;
   const int64_t num_tiles = (int64_t)p.batch * p.tiles_h * p.tiles_w * p.tiles_n;
   if (num_tiles > INT32_MAX) return cudaErrorInvalidValue;
   const int grid = (int)std::min<int64_t>(num_tiles, ctx->sm_count);
+  if (after_prepass)
+    return launch_dependent(conv_tc_kernel<MODE, BN>, dim3(grid), dim3(NUM_THREADS), conv_smem_bytes<MODE, BN>(),
+                            ctx->stream, a0, a1, b0, b1, p, ctx->status_dev);
   conv_tc_kernel<MODE, BN><<<grid, NUM_THREADS, conv_smem_bytes<MODE, BN>(), ctx->stream>>>(a0, a1, b0, b1, p,
                                                                                            ctx->status_dev);
   return cudaGetLastError();
@@ -463,18 +472,24 @@ cudaError_t launch_conv_3xtf32_tc(exo_b200_Context* ctx, const ConvShape& s, con
   const int64_t Kp = (K + 3) / 4 * 4;
   const int64_t w_elems = (int64_t)s.out_c * Kp;
   if (!acquire_scratch(ctx, 0, 2 * (size_t)in_elems * sizeof(float))) return cudaErrorMemoryAllocation;
-  if (!acquire_scratch(ctx, 1, 2 * (size_t)w_elems * sizeof(float))) return cudaErrorMemoryAllocation;
+  if (!acquire_scratch(ctx, 2, 2 * (size_t)w_elems * sizeof(float))) return cudaErrorMemoryAllocation;
   float* x_hi = static_cast<float*>(ctx->scratch[0]);
   float* x_lo = x_hi + in_elems;
-  float* w_hi = static_cast<float*>(ctx->scratch[1]);
+  float* w_hi = static_cast<float*>(ctx->scratch[2]);  // a slot of its own: it may outlive the call (weight cache)
   float* w_lo = w_hi + w_elems;
   {
+    // With the weight cache switched on (exo_b200_context_cache_weights) the split of these weights is
+    // reused while the pointer, the shape and the layout stay the same.
+    WeightKey key{weights, s.in_c, s.out_c, s.kdim, s.w_stride_ky, s.w_stride_kx, s.w_stride_ci};
+    const bool cached = ctx->cache_weights && ctx->wkey_valid && memcmp(&ctx->wkey, &key, sizeof(key)) == 0;
     const int b1 = (int)std::min<int64_t>((in_elems + 255) / 256, (int64_t)ctx->sm_count * 16);
-    split_elementwise_kernel<<<b1, 256, 0, ctx->stream>>>(inp, in_elems, x_hi, x_lo);
-    const int b2 = (int)std::min<int64_t>((w_elems + 255) / 256, (int64_t)ctx->sm_count * 16);
-    split_weights_kernel<<<b2, 256, 0, ctx->stream>>>(weights, s, (int)K, (int)Kp, w_hi, w_lo);
+    const int b2 = cached ? 0 : (int)std::min<int64_t>((w_elems + 255) / 256, (int64_t)ctx->sm_count * 4);
+    conv_split_kernel<<<b1 + b2, 256, 0, ctx->stream>>>(inp, in_elems, x_hi, x_lo, b1, weights, s, (int)K, (int)Kp,
+                                                       w_hi, w_lo);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
+    ctx->wkey = key;
+    ctx->wkey_valid = ctx->cache_weights;
   }
   CUtensorMap ma0, ma1, mb0, mb1;
   const CUtensorMapDataType dt = CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
@@ -490,11 +505,11 @@ cudaError_t launch_conv_3xtf32_tc(exo_b200_Context* ctx, const ConvShape& s, con
     if (!make_tiled_map(&mb0, dt, 2, w_hi, dims, strides, box)) return cudaErrorUnknown;
     if (!make_tiled_map(&mb1, dt, 2, w_lo, dims, strides, box)) return cudaErrorUnknown;
   }
-  const cudaError_t e = bn == 64    ? launch_conv<CONV_TF32X3, 64>(ctx, ma0, ma1, mb0, mb1, p)
-                        : bn == 128 ? launch_conv<CONV_TF32X3, 128>(ctx, ma0, ma1, mb0, mb1, p)
-                                    : launch_conv<CONV_TF32X3, 256>(ctx, ma0, ma1, mb0, mb1, p);
+  const cudaError_t e = bn == 64    ? launch_conv<CONV_TF32X3, 64>(ctx, ma0, ma1, mb0, mb1, p, true)
+                        : bn == 128 ? launch_conv<CONV_TF32X3, 128>(ctx, ma0, ma1, mb0, mb1, p, true)
+                                    : launch_conv<CONV_TF32X3, 256>(ctx, ma0, ma1, mb0, mb1, p, true);
   release_scratch(ctx, 0);
-  release_scratch(ctx, 1);
+  release_scratch(ctx, 2);
   return e;
 }
 

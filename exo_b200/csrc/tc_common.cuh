@@ -134,6 +134,29 @@ inline bool make_tiled_map(CUtensorMap* m, CUtensorMapDataType dt, int rank, con
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// Launches `kernel` so that it may begin before the preceding kernel of the stream has finished (the
+// kernel calls grid_dep_wait() before it touches that kernel's output).  EXOB200_PDL=0 turns the
+// attribute off (plain stream order).
+template <class... KArgs, class... Args>
+cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                             Args&&... args) {
+  static const bool pdl = [] {
+    const char* e = getenv("EXOB200_PDL");
+    return !(e && e[0] == '0');
+  }();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 }  // namespace tc
 }  // namespace exob200
 

@@ -235,6 +235,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  grid_dep_wait();  // operands may come from a pre-pass kernel that this launch was allowed to overlap
 
   const int num_tiles = tiles_m * tiles_n;
   const int num_kb = (K + BK - 1) / BK;
@@ -503,6 +504,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
 // A (M x K row-major) -> hi, lo (M x Kp), zero in the pad columns.
 __global__ void split_rows_kernel(const float* __restrict__ A, int64_t M, int K, int Kp, float* __restrict__ hi,
                                   float* __restrict__ lo) {
+  grid_dep_launch();
   const int64_t total = M * Kp;
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
        i += (int64_t)gridDim.x * blockDim.x) {
@@ -519,6 +521,7 @@ __global__ void split_rows_kernel(const float* __restrict__ A, int64_t M, int K,
 __global__ void split_transpose_kernel(const float* __restrict__ B, int K, int N, int Kp, float* __restrict__ hi,
                                        float* __restrict__ lo) {
   __shared__ float th[32][33], tl[32][33];
+  grid_dep_launch();
   const int k0 = blockIdx.x * 32, n0 = blockIdx.y * 32;
   const int tx = threadIdx.x, ty = threadIdx.y;  // 32 x 8
   for (int r = ty; r < 32; r += 8) {
@@ -543,6 +546,7 @@ __global__ void split_transpose_kernel(const float* __restrict__ B, int K, int N
 __global__ void __launch_bounds__(256) transpose_i8_kernel(const int8_t* __restrict__ B, int K, int N, int Kp,
                                                            int8_t* __restrict__ Bt, int vec_in) {
   __shared__ int8_t t[128][128 + 4];
+  grid_dep_launch();
   const int k0 = blockIdx.x * 128, n0 = blockIdx.y * 128;
   const int tid = threadIdx.x;
   // read: 128 k rows x 32 words
@@ -611,15 +615,20 @@ int chunk_kb() {
 
 template <int MODE, bool BMN = false>
 cudaError_t launch_tc(exo_b200_Context* ctx, const CUtensorMap& a0, const CUtensorMap& a1, const CUtensorMap& b0,
-                      const CUtensorMap& b1, int64_t M, int64_t N, int64_t K, const EpiParams& ep, int chunk_override = 0) {
+                      const CUtensorMap& b1, int64_t M, int64_t N, int64_t K, const EpiParams& ep, int chunk_override = 0,
+                      bool after_prepass = false) {
   EXOB200_SMEM_ATTR_ONCE((gemm_tc_kernel<MODE, BMN>), smem_bytes<MODE>(), ctx->device);
   const int64_t tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
   if (tiles_m * tiles_n > INT32_MAX || M > INT32_MAX || N > INT32_MAX || K > INT32_MAX)
     return cudaErrorInvalidValue;
   const int grid = (int)std::min<int64_t>(tiles_m * tiles_n, ctx->sm_count);
+  const int chunk = chunk_override > 0 ? chunk_override : chunk_kb<MODE>();
+  if (after_prepass)  // set-up overlaps the tail of the pre-pass that was enqueued just before
+    return launch_dependent(gemm_tc_kernel<MODE, BMN>, dim3(grid), dim3(tc_threads<MODE>()), smem_bytes<MODE>(),
+                            ctx->stream, a0, a1, b0, b1, (int)M, (int)N, (int)K, ep, ctx->status_dev, (int)tiles_m,
+                            (int)tiles_n, chunk);
   gemm_tc_kernel<MODE, BMN><<<grid, tc_threads<MODE>(), smem_bytes<MODE>(), ctx->stream>>>(
-      a0, a1, b0, b1, (int)M, (int)N, (int)K, ep, ctx->status_dev, (int)tiles_m, (int)tiles_n,
-      chunk_override > 0 ? chunk_override : chunk_kb<MODE>());
+      a0, a1, b0, b1, (int)M, (int)N, (int)K, ep, ctx->status_dev, (int)tiles_m, (int)tiles_n, chunk);
   return cudaGetLastError();
 }
 
@@ -710,7 +719,7 @@ cudaError_t launch_matmul_i8_tc(exo_b200_Context* ctx, int64_t N, int64_t M, int
   if (!make_kmajor_map(&ma, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, A, rows, K, K, BM)) return cudaErrorUnknown;
   if (!make_kmajor_map(&mb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, Bt, cols, K, Kp, BN)) return cudaErrorUnknown;
   EpiParams ep{C, cols, scale, act ? 1 : 0, (cols % 16 == 0 && aligned16(C)) ? 1 : 0};
-  const cudaError_t e = launch_tc<MODE_I8>(ctx, ma, ma, mb, mb, rows, cols, K, ep);
+  const cudaError_t e = launch_tc<MODE_I8>(ctx, ma, ma, mb, mb, rows, cols, K, ep, 0, true);
   release_scratch(ctx, 1);
   return e;
 }
@@ -746,7 +755,7 @@ cudaError_t launch_sgemm_3xtf32_tc(exo_b200_Context* ctx, int64_t M, int64_t N, 
   if (!make_kmajor_map(&mb0, dt, 4, b_hi, N, Kp, Kp * 4, BN)) return cudaErrorUnknown;
   if (!make_kmajor_map(&mb1, dt, 4, b_lo, N, Kp, Kp * 4, BN)) return cudaErrorUnknown;
   EpiParams ep{C, N, 0.f, 0, (N % 4 == 0 && aligned16(C)) ? 1 : 0};
-  const cudaError_t e = launch_tc<MODE_TF32X3>(ctx, ma0, ma1, mb0, mb1, M, N, Kp, ep);
+  const cudaError_t e = launch_tc<MODE_TF32X3>(ctx, ma0, ma1, mb0, mb1, M, N, Kp, ep, 0, true);
   release_scratch(ctx, 0);
   release_scratch(ctx, 1);
   return e;
@@ -778,7 +787,7 @@ cudaError_t launch_ssyrk_3xtf32_tc(exo_b200_Context* ctx, int64_t N, int64_t K, 
   // The tensor core adds into its accumulator without round-to-nearest; on the diagonal of A A^T every
   // product has the same sign, so that bias is coherent there instead of averaging out.  Draining the
   // accumulator every 8 k-blocks (256 elements of K) instead of every 32 keeps it four times smaller.
-  e = launch_tc<MODE_TF32X3>(ctx, ma0, ma1, mb0, mb1, N, N, Kp, ep, 8);
+  e = launch_tc<MODE_TF32X3>(ctx, ma0, ma1, mb0, mb1, N, N, Kp, ep, 8, true);
   release_scratch(ctx, 0);
   return e;
 }

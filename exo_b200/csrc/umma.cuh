@@ -43,6 +43,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// The same test with a suspend-time hint: the thread may be parked by the hardware for up to about
+// `hint_ns` and is woken when the phase completes, instead of returning at once to be polled again.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
 __device__ __forceinline__ uint64_t globaltimer_ns() {
   uint64_t t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -57,8 +72,10 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = globaltimer_ns();
   for (uint32_t it = 1;; ++it) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((it & 63u) == 0) {
+    // parked between tests rather than spinning: a spinning waiter spends issue slots -- and power, which is
+    // what a tensor-core kernel under the power cap runs out of -- on instructions that do nothing
+    if (mbar_try_wait_hint(bar, parity, 2000u)) return true;
+    if ((it & 7u) == 0) {
       if (*abort) return false;
       if (globaltimer_ns() - t0 > limit_ns) return false;
     }
@@ -106,6 +123,15 @@ __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, vo
   ok = __shfl_sync(0xffffffffu, ok, 0);
   return ok != 0;
 }
+
+// ------------------------------------------- programmatic dependent launch
+// A kernel launched with the programmatic-stream-serialization attribute may start while the kernel
+// before it in the stream is still running; grid_dep_wait() then blocks until that kernel has finished
+// and its writes are visible.  Everything before the wait (barrier and tensor-memory set-up, tensor-map
+// prefetch) overlaps the predecessor's tail.  Without the attribute the wait returns at once.
+// grid_dep_launch() in the predecessor lets the dependent grid be scheduled from that point on.
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // ------------------------------------------------------------------ TMA
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* m) {

@@ -221,6 +221,15 @@ exo_b200_Context* exo_b200_context_create( int device, void* stream );
 void exo_b200_context_destroy( exo_b200_Context* ctxt );
 void exo_b200_context_set_stream( exo_b200_Context* ctxt, void* stream );
 void exo_b200_context_set_sgemm_path( exo_b200_Context* ctxt, int path );
+/* Weight cache of the tensor-core fp32 convolution (conv_nhwc_exo_3xtf32, and conv / conv_specialized /
+ * conv_nhwc_exo on a 3xTF32 context).  That path multiplies TF32 hi + lo copies of both operands; the
+ * copy of the weights is the same from call to call while the weights are.  With the cache on
+ * (enable != 0; it is OFF by default) the context keeps the copy of the last weight tensor and reuses it
+ * when a call passes the same pointer, shape and layout -- so the caller promises not to rewrite that
+ * memory in place, or calls exo_b200_context_invalidate() after doing so.  ctxt == NULL: the default
+ * context of the current device. */
+void exo_b200_context_cache_weights( exo_b200_Context* ctxt, int enable );
+void exo_b200_context_invalidate( exo_b200_Context* ctxt );
 /* Stream used by calls that pass ctxt == NULL (and by the Gemmini-typed calls). */
 void exo_b200_set_default_stream( void* stream );
 /* Wait for the context's stream (NULL: default context) and collect device-side status. */

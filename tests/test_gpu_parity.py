@@ -759,6 +759,44 @@ def test_conv_reference_layout_on_tensor_path(lib, port, torch):
     ctx.close()
 
 
+def test_conv_weight_cache_is_opt_in_and_invalidated(lib, port, torch):
+    """With exo_b200_context_cache_weights on, the TF32 split of the weights is reused while the same
+    weight tensor is passed; after an in-place update the caller invalidates.  Results stay within the
+    3xTF32 bound in every phase, and the cache is off unless asked for."""
+    import exo_b200
+
+    b, h, w, ci, co, k, pad = 2, 14, 14, 32, 64, 3, 1
+    inp = inputs.uniform_f32(131, (b, h, w, ci))
+    w1 = inputs.uniform_f32(132, (k, k, ci, co))
+    w2 = inputs.uniform_f32(133, (k, k, ci, co))
+    bias = inputs.uniform_f32(134, (co,))
+    ctx = exo_b200.Context(sgemm_path=exo_b200.SGEMM_3XTF32)
+    d_in, d_w, d_b = dev(torch, inp), dev(torch, w1), dev(torch, bias)
+    out = torch.empty((b, h, w, co), dtype=torch.float32, device="cuda")
+
+    def check(weights):
+        lib.conv_nhwc_exo(ctx, b, h, w, ci, co, k, pad, True, d_in, out, d_w, d_b)
+        lib.synchronize(ctx)
+        want = port.conv_nhwc(inp, weights, bias, pad, True)
+        S = port.conv_nhwc(np.abs(inp), np.abs(weights), np.abs(bias), pad, False).astype(np.float64)
+        err = np.abs(out.cpu().numpy().astype(np.float64) - want)
+        return bool((err <= (tf32x3_bound(k * k * ci) + 2e-7) * S).all())
+
+    assert check(w1)                       # cache off (default): every call splits the weights
+    d_w.copy_(torch.from_numpy(w2))
+    assert check(w2)                       # ... so an in-place update is simply seen
+    lib.dll.exo_b200_context_cache_weights(ctx.handle, 1)
+    assert check(w2) and check(w2)         # second call reuses the split
+    d_w.copy_(torch.from_numpy(w1))        # in-place update: the caller's promise is to invalidate
+    lib.dll.exo_b200_context_invalidate(ctx.handle)
+    assert check(w1)
+    d_w2 = dev(torch, w2)                  # another tensor: a different key, no invalidation needed
+    d_w = d_w2
+    assert check(w2)
+    lib.dll.exo_b200_context_cache_weights(ctx.handle, 0)
+    ctx.close()
+
+
 @pytest.mark.gpu
 def test_concurrent_host_threads_share_the_default_context(lib, port):
     """Host threads calling with host buffers and ctxt = NULL at the same time (what an
