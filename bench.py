@@ -52,6 +52,22 @@ def measured_peaks():
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
 
 
+def recorded_dram_traffic():
+    """dram read + write bytes of one headline launch, from the ncu summary under profiles/."""
+    path = os.path.join(ROOT, "profiles", "gemm_tc2t_bf16_dram_traffic.txt")
+    vals = {}
+    try:
+        with open(path) as f:
+            for line in f:
+                if line.startswith("#") or ":" not in line:
+                    continue
+                k, v = line.split(":", 1)
+                vals[k.strip()] = float(v)
+        return vals["dram_bytes_read_per_launch"] + vals["dram_bytes_write_per_launch"]
+    except (OSError, KeyError, ValueError):
+        return None
+
+
 # ------------------------------------------------------------------ clocks
 class ClockSampler:
     """Samples SM clock and throttle reasons with nvidia-smi while a timed region runs."""
@@ -596,11 +612,12 @@ def run_ours(args):
 
     peak = peaks["bf16_tflops"]
     per_launch_tflops = wl.flops_local / (ms / 1e3) / 1e12
-    # DRAM bytes per launch of the headline shape from a one-pass ncu capture of one full-size
-    # launch (6.28 GB read + 1.06 GB written); scaled by the rows a rank owns
+    # DRAM bytes per launch of the headline shape: from the committed one-pass ncu capture of one
+    # full-size launch (profiles/gemm_tc2t_bf16_dram_traffic.txt), scaled by the rows a rank owns
     traffic = None
     if args.workload == "bf16" and shape is None:
-        traffic = 7.34e9 * wl.shape[0] / BF16_SHAPE[0]
+        per_launch = recorded_dram_traffic()
+        traffic = per_launch * wl.shape[0] / BF16_SHAPE[0] if per_launch else None
     roofline = {"bound": "tensor", "achieved": per_launch_tflops, "peak": peak, "unit": "TFLOP/s",
                 "frac": per_launch_tflops / peak, "traffic": traffic,
                 "frac_of_sustained_peak": per_launch_tflops / peaks.get("bf16_tflops_sustained", peak),

@@ -35,7 +35,7 @@ struct ConvPolicy {
   float* __restrict__ out;
 
   static constexpr bool kTransposedB = false;
-  __device__ __forceinline__ bool tile_live(int, int, int, int) const { return true; }
+  static constexpr bool kUpperTriangle = false;
 
   struct RowCtx {
     int64_t base;  // element offset of inp[n, 0, 0, 0]

@@ -25,11 +25,14 @@
 //   static constexpr bool kTransposedB B(k, n) is stored with k contiguous (an N x K row-major array):
 //                                      the B tile then takes the A tile's route through registers,
 //                                      with  float4 load_bt(int n, int k)  = B(k..k+3, n), zero outside
-//   bool tile_live(m0, n0, bm, bn)     false: the CTA of this tile has nothing to do and leaves at once
+//   static constexpr bool kUpperTriangle  only tiles that hold an element with n >= m exist: the grid
+//                                      enumerates just those (a square problem, M == N)
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdlib.h>
+
+#include <algorithm>
 
 namespace exob200 {
 namespace ffma {
@@ -82,6 +85,18 @@ __device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
   return d;
 }
 
+// First tile column of tile row tm that holds an element on or above the diagonal (n >= m).
+__host__ __device__ constexpr int first_live_tile_col(int tm, int bm, int bn) { return (tm * bm) / bn; }
+// Number of tiles of an M x N problem; for an upper-triangular one only those that reach the diagonal.
+template <class Policy>
+inline int64_t count_tiles(const Policy& P, int bm, int bn) {
+  const int64_t tiles_m = (P.M + bm - 1) / bm, tiles_n = (P.N + bn - 1) / bn;
+  if (!Policy::kUpperTriangle) return tiles_m * tiles_n;
+  int64_t n = 0;
+  for (int64_t tm = 0; tm < tiles_m; tm++) n += std::max<int64_t>(0, tiles_n - first_live_tile_col((int)tm, bm, bn));
+  return n;
+}
+
 // Resident CTAs per SM that the register budget is sized for.  8 x 8 outputs per thread need about
 // 190 registers to keep a k step's fragments and the next tile's operands in flight without spilling:
 // the 128-thread 128 x 64 configuration gets that (two CTAs per SM); the 256-thread 128 x 128 one is
@@ -104,20 +119,38 @@ tile_kernel(const Policy P, int tiles_m, int tiles_n) {
   __shared__ __align__(16) float As[2][BK][AS_PITCH];
   __shared__ __align__(16) float Bs[2][BK][BS_PITCH];
 
-  // CTA -> tile, grouped 8 tile-rows at a time so that CTAs resident together
-  // share A rows and B columns in L2.
-  constexpr int GM = 8;
-  const int bid = blockIdx.x;
-  const int per_group = GM * tiles_n;
-  const int group = bid / per_group;
-  const int first_m = group * GM;
-  const int gm = min(GM, tiles_m - first_m);
-  const int in_group = bid - group * per_group;
-  const int tm = first_m + in_group % gm;
-  const int tn = in_group / gm;
+  int tm, tn;
+  if constexpr (Policy::kUpperTriangle) {
+    // CTA -> the bid-th tile that reaches the diagonal or lies above it, row by row: tile row tm holds
+    // tile columns first_live_tile_col(tm) .. tiles_n - 1.  Enumerating only those keeps the block
+    // scheduler's one-CTA-per-SM-first placement balanced (skipping dead CTAs of a full grid does not:
+    // the live ones then share SMs at random).
+    int rest = blockIdx.x;
+    for (tm = 0; tm < tiles_m; tm++) {
+      const int first = first_live_tile_col(tm, BM, BN);
+      const int count = tiles_n > first ? tiles_n - first : 0;
+      if (rest < count) {
+        tn = first + rest;
+        break;
+      }
+      rest -= count;
+    }
+    if (tm == tiles_m) return;
+  } else {
+    // CTA -> tile, grouped 8 tile-rows at a time so that CTAs resident together
+    // share A rows and B columns in L2.
+    constexpr int GM = 8;
+    const int bid = blockIdx.x;
+    const int per_group = GM * tiles_n;
+    const int group = bid / per_group;
+    const int first_m = group * GM;
+    const int gm = min(GM, tiles_m - first_m);
+    const int in_group = bid - group * per_group;
+    tm = first_m + in_group % gm;
+    tn = in_group / gm;
+  }
   const int m0 = tm * BM, n0 = tn * BN;
   const int K = P.K;
-  if (!P.tile_live(m0, n0, BM, BN)) return;  // uniform over the CTA, before any barrier
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
@@ -290,7 +323,7 @@ cudaError_t launch_tiles_h(cudaStream_t stream, const Policy& P) {
   constexpr int TM = 4 * TDY * H, TN = 4 * TDX * H;
   const int64_t tiles_m = (P.M + TM - 1) / TM, tiles_n = (P.N + TN - 1) / TN;
   if (tiles_m * tiles_n > INT32_MAX) return cudaErrorInvalidValue;
-  const unsigned grid = (unsigned)(tiles_m * tiles_n);
+  const unsigned grid = (unsigned)count_tiles(P, TM, TN);
   if (use_packed())
     tile_kernel<Policy, true, H, TDY, TDX><<<grid, TDY * TDX, 0, stream>>>(P, (int)tiles_m, (int)tiles_n);
   else
@@ -303,13 +336,12 @@ cudaError_t launch_tiles_h(cudaStream_t stream, const Policy& P) {
 // less than half full (two resident CTAs per SM): the tail then costs half a tile time.
 template <class Policy>
 cudaError_t launch_tiles(cudaStream_t stream, const Policy& P, int sm_count = 148) {
-  const int64_t big_tiles = ((int64_t)(P.M + 127) / 128) * ((P.N + 127) / 128);
-  const int64_t mid_tiles = ((int64_t)(P.M + 63) / 64) * ((P.N + 63) / 64);
+  const int64_t big_tiles = count_tiles(P, 128, 128), mid_tiles = count_tiles(P, 64, 64);
   static const int force = [] {
     const char* e = getenv("EXOB200_FFMA_TILE");  // 32, 64, 128 or 12864 forces a tile size (timing experiments)
     return e ? atoi(e) : 0;
   }();
-  const int64_t half_tiles = ((int64_t)(P.M + 127) / 128) * ((P.N + 63) / 64);
+  const int64_t half_tiles = count_tiles(P, 128, 64);
   int tile;
   if (force == 32 || force == 64 || force == 128 || force == 12864) {
     tile = force;

@@ -28,7 +28,7 @@ struct SgemmPolicy {
   const float* __restrict__ B;
   float* __restrict__ C;
   static constexpr bool kTransposedB = false;
-  __device__ __forceinline__ bool tile_live(int, int, int, int) const { return true; }
+  static constexpr bool kUpperTriangle = false;
   struct RowCtx {};
   __device__ __forceinline__ RowCtx row_ctx(int) const { return RowCtx(); }
   __device__ __forceinline__ float4 load_a(const RowCtx&, int row, int k) const {

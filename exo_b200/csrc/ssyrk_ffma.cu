@@ -12,8 +12,9 @@
 //
 // Both operands are rows of A (k contiguous), so the B tile takes the A tile's
 // route: 128-bit global loads along k, transposed through registers into the
-// k-major shared-memory layout.  Tiles that lie entirely below the diagonal leave
-// at once; tiles on the diagonal mask their loads of C and their stores.
+// k-major shared-memory layout.  The grid holds only the tiles that reach the
+// diagonal or lie above it; tiles on the diagonal mask their loads of C and
+// their stores.
 #include "ffma_tile.cuh"
 #include "kernels.cuh"
 
@@ -29,7 +30,7 @@ struct SyrkPolicy {
   const float* __restrict__ A;
   float* __restrict__ C;
   static constexpr bool kTransposedB = true;
-  __device__ __forceinline__ bool tile_live(int m0, int n0, int, int bn) const { return n0 + bn - 1 >= m0; }
+  static constexpr bool kUpperTriangle = true;
   struct RowCtx {};
   __device__ __forceinline__ RowCtx row_ctx(int) const { return RowCtx(); }
   __device__ __forceinline__ float4 load_row(int row, int k) const {
@@ -84,7 +85,6 @@ cudaError_t launch_ssyrk_ffma(exo_b200_Context* ctx, int64_t N, int64_t K, const
   if (N > INT32_MAX || K > INT32_MAX) return cudaErrorInvalidValue;
   const bool va = (K % 4 == 0) && ffma::aligned16(A);
   const bool vc = (N % 4 == 0) && ffma::aligned16(C);
-  // the tile-size rule counts every tile of the square; about half of them are live
   const int sms = ctx->sm_count;
 #define EXOB200_SYRK(VA_, VC_) \
   return ffma::launch_tiles(ctx->stream, SyrkPolicy<VA_, VC_>{(int)N, (int)N, (int)K, A, C}, sms)
