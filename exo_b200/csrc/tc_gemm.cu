@@ -824,10 +824,10 @@ cudaError_t launch_bounded_wait_selftest(exo_b200_Context* ctx, uint64_t limit_n
 // matmul_on_cpu_static: the int8 matmul for callers that must not allocate.
 //
 // Some callers cannot call cudaMalloc at the point where they need a matmul:
-// code that runs between the begin and end of a stream capture, code that has
-// handed all device memory to its own arena and must never see the driver
-// allocator move under it, and latency-critical loops where an allocation's
-// implicit device synchronisation is not acceptable.  The regular entry points
+// code that has handed all device memory to its own arena and must never see
+// the driver allocator move under it, processes held to a fixed memory budget,
+// and latency-critical loops where an allocation's implicit device
+// synchronisation is not acceptable.  The regular entry points
 // keep a grow-only scratch buffer in their context (for the K-major copy of B
 // that the tensor-core kernel reads), so their first call with a new size
 // allocates.  This variant keeps that scratch in a fixed array inside the

@@ -161,9 +161,10 @@ void conv_nhwc_exo( void *ctxt, int_fast32_t batch_size, int_fast32_t in_h, int_
 void conv_nhwc_exo_3xtf32( void *ctxt, int_fast32_t batch_size, int_fast32_t in_h, int_fast32_t in_w, int_fast32_t in_channel, int_fast32_t out_channel, int_fast32_t kernel_dim, int_fast32_t pad, bool relu, const float* inp, float* output, const float* weights, const float* bias );
 
 /* matmul_on_cpu_static: the int8 matmul of matmul_on_cpu for callers that cannot
- * allocate device memory where they need the result -- inside a stream capture,
- * under an arena that owns all device memory, or in a loop that must not meet an
- * allocation's implicit synchronisation.  It has no counterpart in the reference
+ * allocate device memory where they need the result -- under an arena that has
+ * taken all device memory for itself, in a process that must stay inside a fixed
+ * memory budget, or in a loop that must not meet an allocation's implicit
+ * synchronisation.  It has no counterpart in the reference
  * (whose C code never allocates on a device); same arithmetic and same result
  * as matmul_on_cpu.
  *   - The first parameter is the cudaStream_t to launch on (NULL = default

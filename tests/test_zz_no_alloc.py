@@ -1,8 +1,8 @@
 """matmul_on_cpu_static -- the int8 matmul for callers that cannot allocate.
 
 Some users of this library need a matmul at a point where device allocation is
-off the table: while a stream is being captured, under a framework arena that
-owns all device memory, or in a loop where the synchronisation hidden inside
+off the table: under a framework arena that owns all device memory, inside a
+fixed memory budget, or in a loop where the synchronisation hidden inside
 cudaMalloc would break a latency budget.  For them the library keeps the
 scratch of one kernel (the K-major copy of B) in a fixed array inside the
 library image.  This test calls that entry point through the C ABI twice in a
