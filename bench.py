@@ -662,6 +662,7 @@ def run_ours(args):
                 line["sgemm_aspect_k512"] = run_shapes(lib, torch, peaks, ASPECT_SHAPES, ("ffma",), probes)
                 line["sgemm_squares"] = run_shapes(lib, torch, peaks, SQUARE_SHAPES, ("ffma",), probes)
                 line["ssyrk"] = run_ssyrk(lib, torch, probes)
+                line["conv_layers_exact"] = run_conv_layers(lib, torch, probes)
             except Exception as e:
                 line["sgemm_shapes"] = {"error": str(e)[:200]}
         if not args.no_cpu:
@@ -783,6 +784,44 @@ ASPECT_SHAPES = [(32768, 8, 512), (16384, 16, 512), (8192, 32, 512), (4096, 64, 
 # to 512, then coarser), every fourth of them here to keep the sweep short
 SQUARE_SHAPES = [(n, n, n) for n in (64, 128, 192, 256, 320, 384, 448, 512, 640, 768, 896, 1024, 1152, 1280, 1408, 1536,
                                      1664, 1792, 1920, 2048)]
+
+
+# the layer list of the reference's convolution bench (apps/x86/conv/bench_conv.cpp:46-53):
+# batch, in_h, in_w, in_chan, out_chan, kernel, pad, stride
+CONV_LAYERS = [(4, 224, 224, 3, 64, 7, 3, 2), (4, 56, 56, 64, 64, 3, 1, 1), (4, 28, 28, 128, 128, 3, 1, 2),
+               (4, 56, 56, 64, 64, 3, 0, 1), (5, 82, 102, 128, 128, 3, 0, 1)]
+
+
+def run_conv_layers(lib, torch, probes):
+    """Exact fp32 convolution (bias + ReLU) on the layers the reference's bench lists; the stride-2 ones
+    go through conv_nhwc_strided_exo (the Exo procedure itself has no stride)."""
+    out = []
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    simt_peak = probes.get("fp32_simt") or probes.get("fp32_simt_computed")
+    for (b, h, w, ci, co, k, pad, stride) in CONV_LAYERS:
+        x = torch.rand((b, h, w, ci), generator=gen, device="cuda") * 2 - 1
+        wt = torch.rand((k, k, ci, co), generator=gen, device="cuda") * 2 - 1
+        bias = torch.rand((co,), generator=gen, device="cuda") * 2 - 1
+        oh, ow = (h + 2 * pad - k) // stride + 1, (w + 2 * pad - k) // stride + 1
+        y = torch.empty((b, oh, ow, co), device="cuda")
+
+        def call():
+            lib.conv_nhwc_strided_exo(None, b, h, w, ci, co, k, pad, stride, True, x, y, wt, bias)
+
+        for _ in range(3):
+            call()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(20):
+            call()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / 20
+        tf = 2.0 * b * oh * ow * co * k * k * ci / ms / 1e9
+        out.append({"layer": [b, h, w, ci, co, k, pad, stride], "us": ms * 1e3, "tflops": tf, "frac_of_simt": tf / simt_peak})
+    lib.synchronize()
+    return out
 
 
 def run_ssyrk(lib, torch, probes):

@@ -26,6 +26,7 @@ PROTOTYPES = {
     "conv": [vp] + [i64] * 8 + [vp] * 4,
     "conv_nhwc_exo": [vp] + [i64] * 7 + [cbool] + [vp] * 4,
     "conv_nhwc_exo_3xtf32": [vp] + [i64] * 7 + [cbool] + [vp] * 4,
+    "conv_nhwc_strided_exo": [vp] + [i64] * 8 + [cbool] + [vp] * 4,
     "matmul_on_cpu": [vp, i64, i64, i64, vp, cbool, vp, vp, vp],
     "conv_on_cpu_stride_1": [vp] + [i64] * 6 + [vp] * 4 + [cbool, vp],
     "gemm_bf16_exo": [vp, i64, i64, i64, vp, vp, vp],

@@ -327,8 +327,9 @@ void conv(void* ctxt, int_fast32_t out_h, int_fast32_t out_w, int_fast32_t out_c
 
 static ConvShape nhwc_conv_shape(int_fast32_t batch_size, int_fast32_t in_h, int_fast32_t in_w,
                                  int_fast32_t in_channel, int_fast32_t out_channel, int_fast32_t kernel_dim,
-                                 int_fast32_t pad, bool relu) {
+                                 int_fast32_t pad, bool relu, int_fast32_t stride = 1) {
   ConvShape s;
+  if (stride < 1) stride = 0;  // rejected below: out_h / out_w come out as 0
   s.batch = (int)batch_size;
   s.in_h = (int)in_h;
   s.in_w = (int)in_w;
@@ -336,8 +337,10 @@ static ConvShape nhwc_conv_shape(int_fast32_t batch_size, int_fast32_t in_h, int
   s.out_c = (int)out_channel;
   s.kdim = (int)kernel_dim;
   s.pad = (int)pad;
-  s.out_h = (int)(in_h + 2 * pad - kernel_dim + 1);
-  s.out_w = (int)(in_w + 2 * pad - kernel_dim + 1);
+  s.stride = (int)stride;
+  s.out_h = stride ? (int)((in_h + 2 * pad - kernel_dim) / stride + 1) : 0;
+  s.out_w = stride ? (int)((in_w + 2 * pad - kernel_dim) / stride + 1) : 0;
+  if (in_h + 2 * pad < kernel_dim || in_w + 2 * pad < kernel_dim) s.out_h = s.out_w = 0;
   s.w_stride_ci = out_channel;
   s.w_stride_kx = in_channel * out_channel;
   s.w_stride_ky = kernel_dim * in_channel * out_channel;
@@ -351,6 +354,15 @@ void conv_nhwc_exo(void* ctxt, int_fast32_t batch_size, int_fast32_t in_h, int_f
   conv_dispatch("conv_nhwc_exo", ctxt,
                 nhwc_conv_shape(batch_size, in_h, in_w, in_channel, out_channel, kernel_dim, pad, relu), inp, output,
                 weights, bias);
+}
+
+void conv_nhwc_strided_exo(void* ctxt, int_fast32_t batch_size, int_fast32_t in_h, int_fast32_t in_w,
+                           int_fast32_t in_channel, int_fast32_t out_channel, int_fast32_t kernel_dim, int_fast32_t pad,
+                           int_fast32_t stride, bool relu, const float* inp, float* output, const float* weights,
+                           const float* bias) {
+  conv_dispatch("conv_nhwc_strided_exo", ctxt,
+                nhwc_conv_shape(batch_size, in_h, in_w, in_channel, out_channel, kernel_dim, pad, relu, stride), inp,
+                output, weights, bias, EXO_B200_SGEMM_FFMA);
 }
 
 void conv_nhwc_exo_3xtf32(void* ctxt, int_fast32_t batch_size, int_fast32_t in_h, int_fast32_t in_w,

@@ -52,8 +52,8 @@ struct ConvPolicy {
     const int oy = r / s.out_w;
     const int ox = r - oy * s.out_w;
     rc.base = (int64_t)n * s.in_h * s.in_w * s.in_c;
-    rc.iy0 = oy - s.pad;
-    rc.ix0 = ox - s.pad;
+    rc.iy0 = oy * s.stride - s.pad;
+    rc.ix0 = ox * s.stride - s.pad;
     return rc;
   }
   __device__ __forceinline__ void decode(int k, int& ky, int& kx, int& ci) const {

@@ -433,7 +433,7 @@ ConvTcParams base_params(const ConvShape& s, int elem) {
 // int8: needs the [K, Co] weight matrix contiguous (Kh,Kw,Ci,Co layout) with a
 // 16-byte pitch, and a 16-byte channel pitch in the input.
 bool tc_supported_conv_i8(const ConvShape& s, const void* inp, const void* weights) {
-  return s.in_c % 16 == 0 && s.out_c % 16 == 0 && aligned16(inp) && aligned16(weights) &&
+  return s.stride == 1 && s.in_c % 16 == 0 && s.out_c % 16 == 0 && aligned16(inp) && aligned16(weights) &&
          s.w_stride_ci == s.out_c && s.w_stride_kx == (int64_t)s.in_c * s.out_c &&
          s.w_stride_ky == (int64_t)s.kdim * s.in_c * s.out_c;
 }
@@ -458,7 +458,9 @@ cudaError_t launch_conv_i8_tc(exo_b200_Context* ctx, const ConvShape& s, float s
   return launch_conv<CONV_I8, 256>(ctx, ma, ma, mb, mb, p);
 }
 
-bool tc_supported_conv_tf32(const ConvShape& s, const void* inp) { return s.in_c % 4 == 0 && aligned16(inp); }
+bool tc_supported_conv_tf32(const ConvShape& s, const void* inp) {
+  return s.stride == 1 && s.in_c % 4 == 0 && aligned16(inp);
+}
 
 cudaError_t launch_conv_3xtf32_tc(exo_b200_Context* ctx, const ConvShape& s, const float* inp, float* out,
                                   const float* weights, const float* bias) {

@@ -18,6 +18,7 @@ cudaError_t launch_ssyrk_3xtf32_tc(exo_b200_Context* ctx, int64_t N, int64_t K, 
 
 struct ConvShape {
   int batch, in_h, in_w, in_c, out_h, out_w, out_c, kdim, pad;
+  int stride = 1;  // spatial stride (exact FFMA path only; the tensor-core paths take stride 1)
   // element strides of the weight tensor for (ky, kx, ci); co is contiguous
   int64_t w_stride_ky, w_stride_kx, w_stride_ci;
   bool relu;

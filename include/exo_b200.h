@@ -153,6 +153,13 @@ void gemm_bf16_exo( void *ctxt, int_fast32_t M, int_fast32_t N, int_fast32_t K, 
  * Exact fp32: bias-initialised FMA chain in ky -> kx -> ci order. */
 void conv_nhwc_exo( void *ctxt, int_fast32_t batch_size, int_fast32_t in_h, int_fast32_t in_w, int_fast32_t in_channel, int_fast32_t out_channel, int_fast32_t kernel_dim, int_fast32_t pad, bool relu, const float* inp, float* output, const float* weights, const float* bias );
 
+/* conv_nhwc_exo with a spatial stride >= 1: output f32[batch, (in_h + 2 pad - kernel_dim) / stride + 1,
+ * (in_w + 2 pad - kernel_dim) / stride + 1, out_channel] -- the output size of the reference's
+ * convolution harness (apps/x86/conv/conv_instance.hpp:44-45), whose layer list has two stride-2 layers
+ * (apps/x86/conv/bench_conv.cpp:47-49) that the Exo procedure does not cover ("todo: add padding,
+ * stride", apps/x86/conv/conv.py:37).  Always the exact fp32 FFMA path. */
+void conv_nhwc_strided_exo( void *ctxt, int_fast32_t batch_size, int_fast32_t in_h, int_fast32_t in_w, int_fast32_t in_channel, int_fast32_t out_channel, int_fast32_t kernel_dim, int_fast32_t pad, int_fast32_t stride, bool relu, const float* inp, float* output, const float* weights, const float* bias );
+
 /* Same contract as conv_nhwc_exo on the tensor cores: implicit GEMM whose im2col
  * addressing is done by TMA (the decomposition of tests/test_im2col.py:41-62),
  * operands split into TF32 hi + lo terms, bias and ReLU in the epilogue.  Not

@@ -66,13 +66,14 @@ class Port:
         L.oracle_ssyrk.argtypes = [_i64] * 2 + [_vp] * 2
         L.oracle_conv.argtypes = [_i64] * 8 + [_vp] * 4
         L.oracle_conv_nhwc.argtypes = [_i64] * 7 + [ctypes.c_bool] + [_vp] * 4
+        L.oracle_conv_nhwc_strided.argtypes = [_i64] * 8 + [ctypes.c_bool] + [_vp] * 4
         L.oracle_im2col_nhwc.argtypes = [_i64] * 6 + [_vp] * 2
         L.oracle_matmul_i8.argtypes = [_i64] * 3 + [_vp, ctypes.c_bool] + [_vp] * 3
         L.oracle_conv_i8.argtypes = [_i64] * 6 + [_vp] * 4 + [ctypes.c_bool, _vp]
         L.oracle_gemm_bf16.argtypes = [_i64] * 3 + [_vp] * 3
         L.oracle_bf16_widen.argtypes = [_i64, _vp, _vp]
         L.oracle_bf16_round.argtypes = [_i64, _vp, _vp]
-        for name in ("oracle_sgemm", "oracle_sgemm_naive", "oracle_ssyrk", "oracle_conv", "oracle_conv_nhwc",
+        for name in ("oracle_sgemm", "oracle_sgemm_naive", "oracle_ssyrk", "oracle_conv_nhwc_strided", "oracle_conv", "oracle_conv_nhwc",
                      "oracle_im2col_nhwc", "oracle_matmul_i8", "oracle_conv_i8",
                      "oracle_gemm_bf16", "oracle_bf16_widen", "oracle_bf16_round",
                      "oracle_set_threads"):
@@ -118,6 +119,17 @@ class Port:
         out = np.empty((n, oh, ow, co), np.float32)
         self.lib.oracle_conv_nhwc(n, ih, iw, ci, co, kh, pad, bool(relu), _ptr(inp), _ptr(out),
                                   _ptr(weights), _ptr(bias) if bias is not None else None)
+        return out
+
+    def conv_nhwc_strided(self, inp, weights, bias, pad, stride, relu=True):
+        """weights [Kh,Kw,Ci,Co], symmetric zero padding, stride >= 1."""
+        n, ih, iw, ci = inp.shape
+        kh, kw, ci2, co = weights.shape
+        assert ci == ci2 and kh == kw and stride >= 1
+        oh, ow = (ih + 2 * pad - kh) // stride + 1, (iw + 2 * pad - kw) // stride + 1
+        out = np.empty((n, oh, ow, co), np.float32)
+        self.lib.oracle_conv_nhwc_strided(n, ih, iw, ci, co, kh, pad, stride, bool(relu), _ptr(inp), _ptr(out),
+                                          _ptr(weights), _ptr(bias) if bias is not None else None)
         return out
 
     def im2col_nhwc(self, inp, kdim, pad):

@@ -152,6 +152,35 @@ void oracle_conv_nhwc(int64_t batch, int64_t in_h, int64_t in_w, int64_t in_c, i
       }
 }
 
+/* The same with a stride: out = (in + 2 pad - kdim) / stride + 1 per spatial dimension, the output
+ * size of the reference's convolution harness (apps/x86/conv/conv_instance.hpp:44-45), whose layer
+ * list holds two stride-2 layers (apps/x86/conv/bench_conv.cpp:47-49) that the Exo procedure itself
+ * cannot run ("todo: add padding, stride", apps/x86/conv/conv.py:37).  Same chain as above. */
+void oracle_conv_nhwc_strided(int64_t batch, int64_t in_h, int64_t in_w, int64_t in_c, int64_t out_c,
+                              int64_t kdim, int64_t pad, int64_t stride, bool relu, const float *inp,
+                              float *output, const float *weights, const float *bias) {
+  const int64_t out_h = (in_h + 2 * pad - kdim) / stride + 1, out_w = (in_w + 2 * pad - kdim) / stride + 1;
+#pragma omp parallel for num_threads(g_threads) collapse(2) schedule(static)
+  for (int64_t n = 0; n < batch; n++)
+    for (int64_t oy = 0; oy < out_h; oy++)
+      for (int64_t ox = 0; ox < out_w; ox++) {
+        float *o = output + ((n * out_h + oy) * out_w + ox) * out_c;
+        for (int64_t oc = 0; oc < out_c; oc++) o[oc] = bias ? bias[oc] : 0.0f;
+        for (int64_t ky = 0; ky < kdim; ky++)
+          for (int64_t kx = 0; kx < kdim; kx++) {
+            const int64_t iy = oy * stride + ky - pad, ix = ox * stride + kx - pad;
+            const bool inside = iy >= 0 && iy < in_h && ix >= 0 && ix < in_w;
+            for (int64_t ci = 0; ci < in_c; ci++) {
+              const float x = inside ? inp[((n * in_h + iy) * in_w + ix) * in_c + ci] : 0.0f;
+              const float *w = weights + ((ky * kdim + kx) * in_c + ci) * out_c;
+              for (int64_t oc = 0; oc < out_c; oc++) o[oc] = fmaf(x, w[oc], o[oc]);
+            }
+          }
+        if (relu)
+          for (int64_t oc = 0; oc < out_c; oc++) o[oc] = o[oc] > 0.0f ? o[oc] : 0.0f;
+      }
+}
+
 /* im2col marshalling stage of "im2col + SGEMM".  The reference only has a 1-D
  * schedule test of this decomposition (tests/test_im2col.py:41-62: y[c,r,i] =
  * x[c,i-r], then a matmul whose reduction runs over (c, r)); this is its 2-D

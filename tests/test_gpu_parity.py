@@ -247,6 +247,32 @@ def test_conv_nhwc_bit_exact(lib, port, torch, cfg):
     assert np.array_equal(bits(out.cpu().numpy()), bits(want))
 
 
+@pytest.mark.parametrize("cfg", [
+    # batch, h, w, ci, co, k, pad, stride: the two stride-2 layers of the reference's conv bench
+    # (apps/x86/conv/bench_conv.cpp:47-49) and ragged ones
+    (4, 224, 224, 3, 64, 7, 3, 2),
+    (4, 28, 28, 128, 128, 3, 1, 2),
+    (2, 11, 9, 5, 7, 3, 0, 3),
+    (1, 10, 10, 8, 16, 2, 1, 2),
+])
+def test_conv_strided_bit_exact(lib, port, torch, cfg):
+    b, h, w, ci, co, k, pad, stride = cfg
+    inp = inputs.uniform_f32(141, (b, h, w, ci))
+    wts = inputs.uniform_f32(142, (k, k, ci, co))
+    bias = inputs.uniform_f32(143, (co,))
+    oh, ow = (h + 2 * pad - k) // stride + 1, (w + 2 * pad - k) // stride + 1
+    out = torch.empty((b, oh, ow, co), dtype=torch.float32, device="cuda")
+    lib.conv_nhwc_strided_exo(None, b, h, w, ci, co, k, pad, stride, True, dev(torch, inp), out, dev(torch, wts),
+                              dev(torch, bias))
+    torch.cuda.synchronize()
+    port.set_threads(os.cpu_count() or 1)
+    try:
+        want = port.conv_nhwc_strided(inp, wts, bias, pad, stride, True)
+    finally:
+        port.set_threads(1)
+    assert np.array_equal(bits(out.cpu().numpy()), bits(want))
+
+
 def test_conv_equals_im2col_plus_sgemm(lib, port):
     """The decomposition of tests/test_im2col.py: marshal, then SGEMM into a
     bias-initialised C, then ReLU -- done with the GPU SGEMM -- equals the

@@ -112,6 +112,16 @@ def test_conv_layouts_agree(port):
     assert np.array_equal(bits(C.reshape(out.shape)), bits(out))
 
 
+def test_strided_conv_restatement_reduces_to_the_unit_stride_one(port):
+    """stride 1 is the pinned conv_nhwc; stride 2 equals every second output of it when the sizes line up."""
+    inp = inputs.uniform_f32(41, (2, 9, 11, 4))
+    w = inputs.uniform_f32(42, (3, 3, 4, 8))
+    bias = inputs.uniform_f32(43, (8,))
+    full = port.conv_nhwc(inp, w, bias, 1, True)
+    assert np.array_equal(bits(port.conv_nhwc_strided(inp, w, bias, 1, 1, True)), bits(full))
+    assert np.array_equal(bits(port.conv_nhwc_strided(inp, w, bias, 1, 2, True)), bits(np.ascontiguousarray(full[:, ::2, ::2])))
+
+
 @pytest.mark.parametrize("name", list(cases.I8_CASES))
 def test_i8_port_matches_fixture(port, golden, name):
     A, B, scale, act = cases.i8_inputs(name)
