@@ -33,6 +33,7 @@
 #include <stdlib.h>
 
 #include <algorithm>
+#include <type_traits>
 
 namespace exob200 {
 namespace ffma {
@@ -116,8 +117,19 @@ tile_kernel(const Policy P, int tiles_m, int tiles_n) {
   constexpr int AS_PITCH = BM + 4;  // floats; keeps 16-byte alignment, spreads the transposing stores
   constexpr int R = 4 * H;          // rows (and columns) per thread
   constexpr int BS_PITCH = Policy::kTransposedB ? BN + 4 : BN;  // the transposing stores want the same skew as A's
-  __shared__ __align__(16) float As[2][BK][AS_PITCH];
-  __shared__ __align__(16) float Bs[2][BK][BS_PITCH];
+  // Shared-memory ring of STAGES k-tiles; operands of the next STAGES - 1 tiles are in flight (A in
+  // registers, B as cp.async groups).  Three stages for the 4 x 4-per-thread configurations: those run
+  // one or two warps per scheduler, a k-tile is over in ~800 cycles, and with a single tile of
+  // look-ahead each k-tile waited about 570 cycles for its operands (ncu on 512^3: 35 of 89 cycles per
+  // k step were long-scoreboard stalls; 256^3 13.7 -> 9.8 us, 512^3 26.2 -> 18.5 us, 4096 x 64 x 4096
+  // 192 -> 128 us).  The 8 x 8-per-thread configurations keep two stages: their k-tile takes 2000
+  // cycles, which already covers the latency, and the second register set cost them 10 %
+  // (1024^3 72 -> 82 us).
+  constexpr int STAGES = (H == 1 && !Policy::kTransposedB) ? 3 : 2;
+  static_assert(STAGES * BK * (AS_PITCH + BS_PITCH) * 4 <= 48 * 1024, "static shared memory");
+  constexpr int D = STAGES - 1;  // tiles of look-ahead = register sets for A
+  __shared__ __align__(16) float As[STAGES][BK][AS_PITCH];
+  __shared__ __align__(16) float Bs[STAGES][BK][BS_PITCH];
 
   int tm, tn;
   if constexpr (Policy::kUpperTriangle) {
@@ -173,41 +185,48 @@ tile_kernel(const Policy P, int tiles_m, int tiles_n) {
 
   // A goes through registers (it is transposed on the way into shared memory);
   // B is copied global -> shared asynchronously, 16 bytes (or 4 x 4) per thread.
-  float4 pa[PA];
+  float4 pa[D][PA];
   constexpr int PBT = Policy::kTransposedB ? BN / A_RSTEP : 1;  // passes over a k-contiguous B tile
-  float4 pbt[PBT];
-  auto load_tile = [&](int k0, int buf) {
+  float4 pbt[D][PBT];
+  // `set` is a std::integral_constant: the register set is chosen at compile time
+  auto load_tile = [&](auto set, int k0, int buf, bool live) {
+    constexpr int S = decltype(set)::value;
+    if (live) {
 #pragma unroll
-    for (int h = 0; h < PA; h++) pa[h] = P.load_a(rc[h], m0 + a_row + h * A_RSTEP, k0 + a_kq);
-    if constexpr (Policy::kTransposedB) {
+      for (int h = 0; h < PA; h++) pa[S][h] = P.load_a(rc[h], m0 + a_row + h * A_RSTEP, k0 + a_kq);
+      if constexpr (Policy::kTransposedB) {
 #pragma unroll
-      for (int h = 0; h < PBT; h++) pbt[h] = P.load_bt(n0 + a_row + h * A_RSTEP, k0 + a_kq);
-    } else {
+        for (int h = 0; h < PBT; h++) pbt[S][h] = P.load_bt(n0 + a_row + h * A_RSTEP, k0 + a_kq);
+      } else {
 #pragma unroll
-      for (int h = 0; h < PB; h++)
-        P.copy_b(&Bs[buf][b_k + h * B_KSTEP][b_c4], k0 + b_k + h * B_KSTEP, n0 + b_c4);
+        for (int h = 0; h < PB; h++)
+          P.copy_b(&Bs[buf][b_k + h * B_KSTEP][b_c4], k0 + b_k + h * B_KSTEP, n0 + b_c4);
+      }
     }
+    asm volatile("cp.async.commit_group;" ::: "memory");  // one group per tile, empty past the last one
   };
-  auto store_tile = [&](int buf) {
+  auto store_tile = [&](auto set, int buf) {
+    constexpr int S = decltype(set)::value;
     if constexpr (Policy::kTransposedB) {
 #pragma unroll
       for (int h = 0; h < PBT; h++) {
         const int r = a_row + h * A_RSTEP;
-        Bs[buf][a_kq + 0][r] = pbt[h].x;
-        Bs[buf][a_kq + 1][r] = pbt[h].y;
-        Bs[buf][a_kq + 2][r] = pbt[h].z;
-        Bs[buf][a_kq + 3][r] = pbt[h].w;
+        Bs[buf][a_kq + 0][r] = pbt[S][h].x;
+        Bs[buf][a_kq + 1][r] = pbt[S][h].y;
+        Bs[buf][a_kq + 2][r] = pbt[S][h].z;
+        Bs[buf][a_kq + 3][r] = pbt[S][h].w;
       }
     }
 #pragma unroll
     for (int h = 0; h < PA; h++) {
       const int r = a_row + h * A_RSTEP;
-      As[buf][a_kq + 0][r] = pa[h].x;
-      As[buf][a_kq + 1][r] = pa[h].y;
-      As[buf][a_kq + 2][r] = pa[h].z;
-      As[buf][a_kq + 3][r] = pa[h].w;
+      As[buf][a_kq + 0][r] = pa[S][h].x;
+      As[buf][a_kq + 1][r] = pa[S][h].y;
+      As[buf][a_kq + 2][r] = pa[S][h].z;
+      As[buf][a_kq + 3][r] = pa[S][h].w;
     }
-    asm volatile("cp.async.wait_all;" ::: "memory");
+    // all but the D - 1 most recent groups have landed: the tile being published is complete
+    asm volatile("cp.async.wait_group %0;" ::"n"(D - 1) : "memory");
   };
 
   // accumulators start at the chain's first operand
@@ -232,13 +251,17 @@ tile_kernel(const Policy P, int tiles_m, int tiles_n) {
   }
 
   const int ktiles = (K + BK - 1) / BK;
-  load_tile(0, 0);
-  store_tile(0);
+  using Set0 = std::integral_constant<int, 0>;
+  using Set1 = std::integral_constant<int, D - 1>;  // the second set (the first again when D == 1)
+  load_tile(Set0{}, 0, 0, true);
+  if (D > 1) load_tile(Set1{}, BK, 1, 1 < ktiles);
+  store_tile(Set0{}, 0);
   __syncthreads();
 
-  for (int t = 0; t < ktiles; t++) {
-    const int buf = t & 1;
-    if (t + 1 < ktiles) load_tile((t + 1) * BK, buf ^ 1);
+  // One k-tile: request tile t + D into the register set / ring slot that tile t's predecessor freed,
+  // multiply tile t, publish tile t + 1.  `set` = t % D.
+  auto iteration = [&](auto set, auto next_set, int t, int buf) {
+    load_tile(set, (t + D) * BK, (buf + D) % STAGES, t + D < ktiles);
 
     const int kmax = min(BK, K - t * BK);
     auto step = [&](int kk) {
@@ -288,8 +311,17 @@ tile_kernel(const Policy P, int tiles_m, int tiles_n) {
       for (int kk = 0; kk < kmax; kk++) step(kk);  // ragged K tail: no padded steps
     }
 
-    if (t + 1 < ktiles) store_tile(buf ^ 1);
+    if (t + 1 < ktiles) store_tile(next_set, (buf + 1) % STAGES);
     __syncthreads();
+  };
+  int buf = 0;
+  for (int t = 0; t < ktiles; t += D) {
+    iteration(Set0{}, Set1{}, t, buf);
+    buf = (buf + 1) % STAGES;
+    if (D > 1 && t + 1 < ktiles) {
+      iteration(Set1{}, Set0{}, t + 1, buf);
+      buf = (buf + 1) % STAGES;
+    }
   }
 
 #pragma unroll
