@@ -11,9 +11,12 @@
 // Tiling: CTA tile 128x128, K step 16, 256 threads, each thread an 8x8
 // register tile laid out as 2x2 quadrants of 4x4 so that every shared-memory
 // read is a conflict-free 128-bit load.  A is stored k-major in shared memory
-// so that the per-k A fragment is contiguous.  The next K tile is fetched into
-// registers while the current one is multiplied (two shared-memory buffers, one
-// barrier per tile).
+// so that the per-k A fragment is contiguous.  The next K tile is fetched
+// (A into registers, B by cp.async) while the current one is multiplied, through
+// a ring of shared-memory buffers with one barrier per tile: two buffers for the
+// 8x8-per-thread configurations, three (two tiles of look-ahead) for the
+// 4x4-per-thread ones, whose few warps per SM cannot hide a global load behind
+// one tile's arithmetic.
 //
 // A Policy supplies the operand addressing:
 //   int  M, N, K                       logical extents
