@@ -33,14 +33,19 @@ struct ConvPolicy {
   const float* __restrict__ w;
   const float* __restrict__ bias;
   float* __restrict__ out;
+  int wsy, wsx, wsc;  // the weight tensor's element strides for (ky, kx, ci), checked to fit 32 bits
 
   static constexpr bool kTransposedB = false;
   static constexpr bool kUpperTriangle = false;
 
   struct RowCtx {
-    int64_t base;  // element offset of inp[n, 0, 0, 0]
+    int64_t base;  // element offset of inp[n, iy0, ix0, 0] (tap (0, 0) of this pixel; may lie in the padding)
     int iy0, ix0;  // input coordinates of tap (0, 0)
     bool valid;
+  };
+  // Cursor along K = (ky, kx, ci): decoded once with two divisions, then advanced by additions.
+  struct KCtx {
+    int k, ky, kx, ci;
   };
   __device__ __forceinline__ RowCtx row_ctx(int m) const {
     RowCtx rc;
@@ -51,47 +56,53 @@ struct ConvPolicy {
     const int r = mm - n * hw;
     const int oy = r / s.out_w;
     const int ox = r - oy * s.out_w;
-    rc.base = (int64_t)n * s.in_h * s.in_w * s.in_c;
     rc.iy0 = oy * s.stride - s.pad;
     rc.ix0 = ox * s.stride - s.pad;
+    rc.base = ((int64_t)n * s.in_h * s.in_w + (int64_t)rc.iy0 * s.in_w + rc.ix0) * s.in_c;
     return rc;
   }
-  __device__ __forceinline__ void decode(int k, int& ky, int& kx, int& ci) const {
+  __device__ __forceinline__ KCtx k_ctx(int k) const {
+    KCtx c;
+    c.k = k;
     const int tap = k / s.in_c;
-    ci = k - tap * s.in_c;
-    ky = tap / s.kdim;
-    kx = tap - ky * s.kdim;
+    c.ci = k - tap * s.in_c;
+    c.ky = tap / s.kdim;
+    c.kx = tap - c.ky * s.kdim;
+    return c;
   }
-  __device__ __forceinline__ float load_a1(const RowCtx& rc, int k) const {
-    if (k >= K) return 0.f;
-    int ky, kx, ci;
-    decode(k, ky, kx, ci);
-    const int iy = rc.iy0 + ky, ix = rc.ix0 + kx;
-    if (iy < 0 || iy >= s.in_h || ix < 0 || ix >= s.in_w) return 0.f;
-    return __ldg(inp + rc.base + ((int64_t)iy * s.in_w + ix) * s.in_c + ci);
+  __device__ __forceinline__ void k_advance(KCtx& c, int step) const {
+    c.k += step;
+    c.ci += step;
+    while (c.ci >= s.in_c) {
+      c.ci -= s.in_c;
+      if (++c.kx == s.kdim) c.kx = 0, ++c.ky;
+    }
   }
-  __device__ __forceinline__ float4 load_a(const RowCtx& rc, int, int k) const {
+  __device__ __forceinline__ bool tap_inside(const RowCtx& rc, const KCtx& c) const {
+    return (unsigned)(rc.iy0 + c.ky) < (unsigned)s.in_h && (unsigned)(rc.ix0 + c.kx) < (unsigned)s.in_w;
+  }
+  __device__ __forceinline__ const float* tap_ptr(const RowCtx& rc, const KCtx& c) const {
+    return inp + rc.base + ((c.ky * s.in_w + c.kx) * s.in_c + c.ci);
+  }
+  __device__ __forceinline__ float4 load_a(const RowCtx& rc, int, const KCtx& c) const {
     float4 v = zero4();
     if (!rc.valid) return v;
-    if (VEC) {
-      if (k >= K) return v;
-      int ky, kx, ci;
-      decode(k, ky, kx, ci);  // in_c % 4 == 0: the quad stays inside one tap
-      const int iy = rc.iy0 + ky, ix = rc.ix0 + kx;
-      if (iy < 0 || iy >= s.in_h || ix < 0 || ix >= s.in_w) return v;
-      return ldg4(inp + rc.base + ((int64_t)iy * s.in_w + ix) * s.in_c + ci);
+    if (VEC) {  // in_c % 4 == 0: the quad stays inside one tap
+      if (c.k < K && tap_inside(rc, c)) v = ldg4(tap_ptr(rc, c));
+      return v;
     }
-    v.x = load_a1(rc, k + 0);
-    v.y = load_a1(rc, k + 1);
-    v.z = load_a1(rc, k + 2);
-    v.w = load_a1(rc, k + 3);
-    return v;
+    KCtx e = c;
+    float r[4];
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      r[j] = (e.k < K && tap_inside(rc, e)) ? __ldg(tap_ptr(rc, e)) : 0.f;
+      k_advance(e, 1);
+    }
+    return make_float4(r[0], r[1], r[2], r[3]);
   }
-  __device__ __forceinline__ void copy_b(float* smem, int k, int col) const {
-    const bool kin = k < K;
-    int ky, kx, ci;
-    decode(kin ? k : 0, ky, kx, ci);
-    const float* p = w + ky * s.w_stride_ky + kx * s.w_stride_kx + ci * s.w_stride_ci;
+  __device__ __forceinline__ void copy_b(float* smem, const KCtx& c, int col) const {
+    const bool kin = c.k < K;
+    const float* p = w + (kin ? c.ky * wsy + c.kx * wsx + c.ci * wsc : 0);
     if (VEC) {
       const bool ok = kin && col < N;
       ffma::cp_async16(smem, p + (ok ? col : 0), ok);
@@ -139,11 +150,14 @@ cudaError_t launch_conv_ffma(cudaStream_t stream, const ConvShape& s, const floa
   const int64_t M = (int64_t)s.batch * s.out_h * s.out_w;
   const int64_t K = (int64_t)s.kdim * s.kdim * s.in_c;
   if (M > INT32_MAX || K > INT32_MAX) return cudaErrorInvalidValue;
+  // 32-bit offsets inside one image and inside the weight tensor
+  if ((int64_t)s.in_h * s.in_w * s.in_c > INT32_MAX || K * (int64_t)s.out_c > INT32_MAX) return cudaErrorInvalidValue;
+  const int wsy = (int)s.w_stride_ky, wsx = (int)s.w_stride_kx, wsc = (int)s.w_stride_ci;
   const bool vec = s.in_c % 4 == 0 && s.out_c % 4 == 0 && ffma::aligned16(inp) &&
                    ffma::aligned16(out) && ffma::aligned16(weights);
   if (vec)
-    return ffma::launch_tiles(stream, ConvPolicy<true>{(int)M, s.out_c, (int)K, s, inp, weights, bias, out});
-  return ffma::launch_tiles(stream, ConvPolicy<false>{(int)M, s.out_c, (int)K, s, inp, weights, bias, out});
+    return ffma::launch_tiles(stream, ConvPolicy<true>{(int)M, s.out_c, (int)K, s, inp, weights, bias, out, wsy, wsx, wsc});
+  return ffma::launch_tiles(stream, ConvPolicy<false>{(int)M, s.out_c, (int)K, s, inp, weights, bias, out, wsy, wsx, wsc});
 }
 
 }  // namespace exob200

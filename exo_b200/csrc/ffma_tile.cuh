@@ -21,13 +21,16 @@
 // A Policy supplies the operand addressing:
 //   int  M, N, K                       logical extents
 //   RowCtx row_ctx(int m)              per-row state for the A loader (computed once)
-//   float4 load_a(const RowCtx&, int m, int k)   A(m, k..k+3), zero outside
-//   void copy_b(float* smem, int k, int n)   cp.async of B(k, n..n+3) into smem, zero outside
+//   KCtx k_ctx(int k), k_advance(KCtx&, int step)   a cursor along K: the engine walks K in steps of one
+//                                      tile, so a policy whose k -> address map needs divisions (the
+//                                      convolution's (ky, kx, ci)) pays them once and then only adds
+//   float4 load_a(const RowCtx&, int m, const KCtx& k)   A(m, k..k+3), zero outside
+//   void copy_b(float* smem, const KCtx& k, int n)   cp.async of B(k, n..n+3) into smem, zero outside
 //   float4 init(int m, int n)          chain start for (m, n..n+3)
 //   void store(int m, int n, float4)   applies the epilogue and writes (bounds-checked)
 //   static constexpr bool kTransposedB B(k, n) is stored with k contiguous (an N x K row-major array):
 //                                      the B tile then takes the A tile's route through registers,
-//                                      with  float4 load_bt(int n, int k)  = B(k..k+3, n), zero outside
+//                                      with  float4 load_bt(int n, const KCtx& k)  = B(k..k+3, n), zero outside
 //   static constexpr bool kUpperTriangle  only tiles that hold an element with n >= m exist: the grid
 //                                      enumerates just those (a square problem, M == N)
 #pragma once
@@ -42,14 +45,17 @@ namespace exob200 {
 namespace ffma {
 
 constexpr int BK = 16;
-// Tile sizes from one engine (TDY x TDX threads, each 4H x 4H outputs):
-//   16 x 16, H = 2 -> 128 x 128, 256 threads, 8 x 8 per thread: the throughput configuration;
-//   16 x  8, H = 2 -> 128 x  64, 128 threads, same per-thread work: when the 128 x 128 tiles would
-//     leave a nearly empty last wave (tile counts just above a multiple of the resident CTAs);
-//   16 x 16, H = 1 ->  64 x  64, 256 threads, 4 x 4 per thread: too few 128 x 128 tiles for the machine;
-//    8 x  8, H = 1 ->  32 x  32,  64 threads, 4 x 4 per thread: too few 64 x 64 tiles.  Such problems are
-//     bound by the latency of one warp's k loop, so spreading the same warps over more SMs (one or two
-//     per scheduler instead of four) is what shortens them.
+// Tile sizes from one engine (TDY x TDX threads, each 4 HM x 4 HN outputs):
+//   16 x 16, 2 x 2 -> 128 x 128, 256 threads, 8 x 8 per thread: the throughput configuration;
+//   16 x  8, 2 x 2 -> 128 x  64, 128 threads, same per-thread work: medium problems, and when the
+//     128 x 128 tiles would leave a nearly empty last round;
+//   16 x  8, 1 x 2 ->  64 x  64, 128 threads, 4 x 8 per thread: when 128 x 64 tiles would put two CTAs on
+//     a few SMs and one on the rest (tile counts just above the SM count);
+//   16 x 16, 1 x 1 ->  64 x  64, 256 threads, 4 x 4 per thread;
+//    8 x  8, 1 x 1 ->  32 x  32,  64 threads, 4 x 4 per thread: small problems.  Those are bound by the
+//     latency of one warp's k loop, so spreading the same warps over more SMs (one or two per
+//     scheduler instead of four) is what shortens them.
+// launch_tiles() picks among them with a measured cost table.
 // Without split-K, which the reference's per-element chain order rules out, parallelism only comes
 // from M x N.
 
@@ -106,19 +112,20 @@ inline int64_t count_tiles(const Policy& P, int bm, int bn) {
 // the 128-thread 128 x 64 configuration gets that (two CTAs per SM); the 256-thread 128 x 128 one is
 // held to 128 registers so that two CTAs (16 warps) share an SM, which is worth more there than the
 // few spilled values cost (measured at 8192^3: 55.3 against 48.4 TFLOP/s with one CTA per SM).
-template <int H, int THREADS>
+template <int HM, int HN, int THREADS>
 __host__ __device__ constexpr int min_ctas() {
-  return (H == 2 && THREADS == 128) ? 2 : 512 / THREADS;
+  return (HM * HN == 4 && THREADS == 128) ? 2 : 512 / THREADS;
 }
 
-template <class Policy, bool PACKED, int H, int TDY, int TDX>
-__global__ void __launch_bounds__(TDY * TDX, min_ctas<H, TDY * TDX>())
+// HM x HN quadrants of 4 x 4 outputs per thread, TDY x TDX threads.
+template <class Policy, bool PACKED, int HM, int HN, int TDY, int TDX>
+__global__ void __launch_bounds__(TDY * TDX, min_ctas<HM, HN, TDY * TDX>())
 tile_kernel(const Policy P, int tiles_m, int tiles_n) {
   constexpr int THREADS = TDY * TDX;
   constexpr int QSM = 4 * TDY, QSN = 4 * TDX;  // rows / columns per quadrant
-  constexpr int BM = QSM * H, BN = QSN * H;
+  constexpr int BM = QSM * HM, BN = QSN * HN;
   constexpr int AS_PITCH = BM + 4;  // floats; keeps 16-byte alignment, spreads the transposing stores
-  constexpr int R = 4 * H;          // rows (and columns) per thread
+  constexpr int RM = 4 * HM, RN = 4 * HN;  // rows and columns per thread
   constexpr int BS_PITCH = Policy::kTransposedB ? BN + 4 : BN;  // the transposing stores want the same skew as A's
   // Shared-memory ring of STAGES k-tiles; operands of the next STAGES - 1 tiles are in flight (A in
   // registers, B as cp.async groups).  Three stages for the 4 x 4-per-thread configurations: those run
@@ -128,7 +135,7 @@ tile_kernel(const Policy P, int tiles_m, int tiles_n) {
   // 192 -> 128 us).  The 8 x 8-per-thread configurations keep two stages: their k-tile takes 2000
   // cycles, which already covers the latency, and the second register set cost them 10 %
   // (1024^3 72 -> 82 us).
-  constexpr int STAGES = (H == 1 && !Policy::kTransposedB) ? 3 : 2;
+  constexpr int STAGES = (HM * HN < 4 && !Policy::kTransposedB) ? 3 : 2;
   static_assert(STAGES * BK * (AS_PITCH + BS_PITCH) * 4 <= 48 * 1024, "static shared memory");
   constexpr int D = STAGES - 1;  // tiles of look-ahead = register sets for A
   __shared__ __align__(16) float As[STAGES][BK][AS_PITCH];
@@ -185,6 +192,11 @@ tile_kernel(const Policy P, int tiles_m, int tiles_n) {
   typename Policy::RowCtx rc[PA];
 #pragma unroll
   for (int h = 0; h < PA; h++) rc[h] = P.row_ctx(m0 + a_row + h * A_RSTEP);
+  // K cursors of this thread's loads: tiles are requested in increasing k, one BK apart
+  typename Policy::KCtx ka = P.k_ctx(a_kq);
+  typename Policy::KCtx kb[PB];
+#pragma unroll
+  for (int h = 0; h < PB; h++) kb[h] = P.k_ctx(b_k + h * B_KSTEP);
 
   // A goes through registers (it is transposed on the way into shared memory);
   // B is copied global -> shared asynchronously, 16 bytes (or 4 x 4) per thread.
@@ -192,21 +204,25 @@ tile_kernel(const Policy P, int tiles_m, int tiles_n) {
   constexpr int PBT = Policy::kTransposedB ? BN / A_RSTEP : 1;  // passes over a k-contiguous B tile
   float4 pbt[D][PBT];
   // `set` is a std::integral_constant: the register set is chosen at compile time
-  auto load_tile = [&](auto set, int k0, int buf, bool live) {
+  auto load_tile = [&](auto set, int buf, bool live) {  // the next tile along K
     constexpr int S = decltype(set)::value;
     if (live) {
 #pragma unroll
-      for (int h = 0; h < PA; h++) pa[S][h] = P.load_a(rc[h], m0 + a_row + h * A_RSTEP, k0 + a_kq);
+      for (int h = 0; h < PA; h++) pa[S][h] = P.load_a(rc[h], m0 + a_row + h * A_RSTEP, ka);
       if constexpr (Policy::kTransposedB) {
 #pragma unroll
-        for (int h = 0; h < PBT; h++) pbt[S][h] = P.load_bt(n0 + a_row + h * A_RSTEP, k0 + a_kq);
+        for (int h = 0; h < PBT; h++) pbt[S][h] = P.load_bt(n0 + a_row + h * A_RSTEP, ka);
       } else {
 #pragma unroll
-        for (int h = 0; h < PB; h++)
-          P.copy_b(&Bs[buf][b_k + h * B_KSTEP][b_c4], k0 + b_k + h * B_KSTEP, n0 + b_c4);
+        for (int h = 0; h < PB; h++) P.copy_b(&Bs[buf][b_k + h * B_KSTEP][b_c4], kb[h], n0 + b_c4);
       }
     }
     asm volatile("cp.async.commit_group;" ::: "memory");  // one group per tile, empty past the last one
+    P.k_advance(ka, BK);
+    if constexpr (!Policy::kTransposedB) {
+#pragma unroll
+      for (int h = 0; h < PB; h++) P.k_advance(kb[h], BK);
+    }
   };
   auto store_tile = [&](auto set, int buf) {
     constexpr int S = decltype(set)::value;
@@ -233,13 +249,13 @@ tile_kernel(const Policy P, int tiles_m, int tiles_n) {
   };
 
   // accumulators start at the chain's first operand
-  float acc[PACKED ? 1 : R][PACKED ? 1 : R];
-  uint64_t acc2[PACKED ? R : 1][PACKED ? R / 2 : 1];  // [row][column pair]
+  float acc[PACKED ? 1 : RM][PACKED ? 1 : RN];
+  uint64_t acc2[PACKED ? RM : 1][PACKED ? RN / 2 : 1];  // [row][column pair]
 #pragma unroll
-  for (int i = 0; i < R; i++) {
+  for (int i = 0; i < RM; i++) {
     const int row = m0 + (i >> 2) * QSM + ty * 4 + (i & 3);
 #pragma unroll
-    for (int jq = 0; jq < H; jq++) {
+    for (int jq = 0; jq < HN; jq++) {
       const float4 v = P.init(row, n0 + jq * QSN + tx * 4);
       if (PACKED) {
         acc2[i][jq * 2 + 0] = pack2(v.x, v.y);
@@ -256,21 +272,21 @@ tile_kernel(const Policy P, int tiles_m, int tiles_n) {
   const int ktiles = (K + BK - 1) / BK;
   using Set0 = std::integral_constant<int, 0>;
   using Set1 = std::integral_constant<int, D - 1>;  // the second set (the first again when D == 1)
-  load_tile(Set0{}, 0, 0, true);
-  if (D > 1) load_tile(Set1{}, BK, 1, 1 < ktiles);
+  load_tile(Set0{}, 0, true);
+  if (D > 1) load_tile(Set1{}, 1, 1 < ktiles);
   store_tile(Set0{}, 0);
   __syncthreads();
 
   // One k-tile: request tile t + D into the register set / ring slot that tile t's predecessor freed,
   // multiply tile t, publish tile t + 1.  `set` = t % D.
   auto iteration = [&](auto set, auto next_set, int t, int buf) {
-    load_tile(set, (t + D) * BK, (buf + D) % STAGES, t + D < ktiles);
+    load_tile(set, (buf + D) % STAGES, t + D < ktiles);  // tile t + D
 
     const int kmax = min(BK, K - t * BK);
     auto step = [&](int kk) {
-      float a[R];
+      float a[RM];
 #pragma unroll
-      for (int h = 0; h < H; h++) {
+      for (int h = 0; h < HM; h++) {
         const float4 av = *reinterpret_cast<const float4*>(&As[buf][kk][h * QSM + ty * 4]);
         a[h * 4 + 0] = av.x;
         a[h * 4 + 1] = av.y;
@@ -278,23 +294,23 @@ tile_kernel(const Policy P, int tiles_m, int tiles_n) {
         a[h * 4 + 3] = av.w;
       }
       if (PACKED) {
-        uint64_t b[R / 2];
+        uint64_t b[RN / 2];
 #pragma unroll
-        for (int h = 0; h < H; h++) {
+        for (int h = 0; h < HN; h++) {
           const ulonglong2 bv = *reinterpret_cast<const ulonglong2*>(&Bs[buf][kk][h * QSN + tx * 4]);
           b[h * 2 + 0] = bv.x;
           b[h * 2 + 1] = bv.y;
         }
 #pragma unroll
-        for (int i = 0; i < R; i++) {
+        for (int i = 0; i < RM; i++) {
           const uint64_t aa = pack2(a[i], a[i]);
 #pragma unroll
-          for (int j = 0; j < R / 2; j++) acc2[i][j] = fma2(aa, b[j], acc2[i][j]);
+          for (int j = 0; j < RN / 2; j++) acc2[i][j] = fma2(aa, b[j], acc2[i][j]);
         }
       } else {
-        float b[R];
+        float b[RN];
 #pragma unroll
-        for (int h = 0; h < H; h++) {
+        for (int h = 0; h < HN; h++) {
           const float4 bv = *reinterpret_cast<const float4*>(&Bs[buf][kk][h * QSN + tx * 4]);
           b[h * 4 + 0] = bv.x;
           b[h * 4 + 1] = bv.y;
@@ -302,9 +318,9 @@ tile_kernel(const Policy P, int tiles_m, int tiles_n) {
           b[h * 4 + 3] = bv.w;
         }
 #pragma unroll
-        for (int i = 0; i < R; i++)
+        for (int i = 0; i < RM; i++)
 #pragma unroll
-          for (int j = 0; j < R; j++) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+          for (int j = 0; j < RN; j++) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
       }
     };
     if (kmax == BK) {
@@ -328,10 +344,10 @@ tile_kernel(const Policy P, int tiles_m, int tiles_n) {
   }
 
 #pragma unroll
-  for (int i = 0; i < R; i++) {
+  for (int i = 0; i < RM; i++) {
     const int row = m0 + (i >> 2) * QSM + ty * 4 + (i & 3);
 #pragma unroll
-    for (int jq = 0; jq < H; jq++) {
+    for (int jq = 0; jq < HN; jq++) {
       float4 v;
       if (PACKED) {
         unpack2(acc2[i][jq * 2 + 0], v.x, v.y);
@@ -353,55 +369,75 @@ inline bool use_packed() {
   return packed;
 }
 
-template <class Policy, int H, int TDY, int TDX>
+template <class Policy, int HM, int HN, int TDY, int TDX>
 cudaError_t launch_tiles_h(cudaStream_t stream, const Policy& P) {
-  constexpr int TM = 4 * TDY * H, TN = 4 * TDX * H;
+  constexpr int TM = 4 * TDY * HM, TN = 4 * TDX * HN;
   const int64_t tiles_m = (P.M + TM - 1) / TM, tiles_n = (P.N + TN - 1) / TN;
   if (tiles_m * tiles_n > INT32_MAX) return cudaErrorInvalidValue;
   const unsigned grid = (unsigned)count_tiles(P, TM, TN);
   if (use_packed())
-    tile_kernel<Policy, true, H, TDY, TDX><<<grid, TDY * TDX, 0, stream>>>(P, (int)tiles_m, (int)tiles_n);
+    tile_kernel<Policy, true, HM, HN, TDY, TDX><<<grid, TDY * TDX, 0, stream>>>(P, (int)tiles_m, (int)tiles_n);
   else
-    tile_kernel<Policy, false, H, TDY, TDX><<<grid, TDY * TDX, 0, stream>>>(P, (int)tiles_m, (int)tiles_n);
+    tile_kernel<Policy, false, HM, HN, TDY, TDX><<<grid, TDY * TDX, 0, stream>>>(P, (int)tiles_m, (int)tiles_n);
   return cudaGetLastError();
 }
 
-// 128 x 128 tiles unless they would leave more than half of the SMs without work; 32 x 32
-// when even 64 x 64 tiles would leave SMs idle.  128 x 64 tiles when the last wave of 128 x 128 tiles would be
-// less than half full (two resident CTAs per SM): the tail then costs half a tile time.
+// Tile choice.  Without split-K the only freedom is the tile shape, and which one is fastest depends
+// on how many CTAs end up sharing an SM.  Each configuration was timed on a B200 with 1 .. max resident
+// CTAs per SM (cubes 256^3 .. 2048^3 and 4096 x 64 x 4096, fixed launch cost removed); the table holds
+// the nanoseconds ONE k step of the whole SM takes at that residency.  A launch is modelled as full
+// rounds at the maximum residency plus one round for the remainder, CTAs spread evenly over the SMs
+// (the block scheduler fills breadth first), and the cheapest configuration wins.  The model reproduces
+// what was found shape by shape before it: 1024^3 -> 128 x 64 (62 us; 128 x 128: 110), 1088^3 -> 64 x 64
+// with 4 x 8 per thread (77 us; 128 x 64: 111), 1536^3 -> 128 x 64 or 128 x 128 (155 / 160), 2048^3 and
+// up -> 128 x 128 unless its last round would be nearly empty (324 tiles: 578 -> 517 us with 128 x 64).
+struct TileConfig {
+  int id;             // value of EXOB200_FFMA_TILE that forces it
+  int bm, bn;         // tile extents
+  int max_resident;   // CTAs per SM by registers / threads
+  float ns[8];        // ns per k step of one SM holding 1 .. max_resident CTAs
+};
+constexpr TileConfig kTileConfigs[] = {
+    {128, 128, 128, 2, {102.5f, 185.f}},
+    {12864, 128, 64, 2, {58.f, 99.f}},
+    {6464, 64, 64, 4, {46.f, 67.5f, 87.5f, 114.5f}},  // 128 threads, 4 x 8 outputs each
+    {64, 64, 64, 2, {42.f, 73.5f}},                    // 256 threads, 4 x 4 outputs each
+    {32, 32, 32, 8, {27.f, 28.f, 34.f, 41.5f, 50.f, 58.5f, 68.f, 76.f}},
+};
+
+// Predicted ns per k step of the slowest SM for `tiles` CTAs of configuration c.
+inline double predicted_ns_per_k(const TileConfig& c, int64_t tiles, int sm_count) {
+  const int64_t per_round = (int64_t)sm_count * c.max_resident;
+  const int64_t rounds = tiles / per_round, rest = tiles - rounds * per_round;
+  double t = (double)rounds * c.ns[c.max_resident - 1];
+  if (rest > 0) t += c.ns[(rest + sm_count - 1) / sm_count - 1];
+  return t;
+}
+
 template <class Policy>
 cudaError_t launch_tiles(cudaStream_t stream, const Policy& P, int sm_count = 148) {
-  const int64_t big_tiles = count_tiles(P, 128, 128), mid_tiles = count_tiles(P, 64, 64);
   static const int force = [] {
-    const char* e = getenv("EXOB200_FFMA_TILE");  // 32, 64, 128 or 12864 forces a tile size (timing experiments)
+    const char* e = getenv("EXOB200_FFMA_TILE");  // a TileConfig id (or 64128) forces a tile size (timing experiments)
     return e ? atoi(e) : 0;
   }();
-  const int64_t half_tiles = count_tiles(P, 128, 64);
-  int tile;
-  if (force == 32 || force == 64 || force == 128 || force == 12864) {
-    tile = force;
-  } else if (big_tiles <= sm_count && half_tiles >= (2 * sm_count) / 3) {
-    // Medium problems: not enough 128 x 128 tiles for every SM, but enough 128 x 64 ones for most.
-    // One or two four-warp CTAs per SM, each thread with the full 8 x 8 register tile (twice the FMAs
-    // per shared-memory load of the 4 x 4 tiles below).  1024^3: 63 us against 78 us with 64 x 64
-    // tiles and 107 us with 128 x 128; 1000^3: 61 against 77 us.
-    tile = 12864;
-  } else if (big_tiles > sm_count || (big_tiles > sm_count / 2 && P.N > 64)) {  // N <= 64 would waste half of a 128-wide tile
-    // From half an SM count of 128 x 128 tiles on, they beat four times as many 64 x 64 tiles
-    // (1536^3, 144 tiles: 171 against 222 us; 1024^3, 64 tiles: 117 against 78 us): a lone
-    // 128 x 128 CTA takes ~112 ns per k step, two co-resident 64 x 64 CTAs ~75 ns, and more
-    // than 296 of the small ones need a second round.
-    const int64_t slots = 2 * (int64_t)sm_count, tail = big_tiles % slots;
-    // measured: 324 tiles 578 -> 517 us, 313 tiles 332 -> 299 us; but 1024 tiles (tail 136) 2564 -> 2654 us:
-    // after a few waves the CTAs have drifted apart and the half tiles' ~4 % lower efficiency is all that is left
-    tile = (big_tiles > slots && big_tiles < 2 * slots && tail <= slots / 2) ? 12864 : 128;
-  } else {
-    tile = mid_tiles > sm_count ? 64 : 32;
+  int tile = 0;
+  if (force == 64128) tile = force;
+  for (const TileConfig& c : kTileConfigs)
+    if (force == c.id) tile = force;
+  if (tile == 0) {
+    double best = 0;
+    for (const TileConfig& c : kTileConfigs) {
+      if (c.bn > 64 && P.N <= 64) continue;  // a 128-wide tile would be half empty
+      const double t = predicted_ns_per_k(c, count_tiles(P, c.bm, c.bn), sm_count);
+      if (tile == 0 || t < best) best = t, tile = c.id;
+    }
   }
-  if (tile == 128) return launch_tiles_h<Policy, 2, 16, 16>(stream, P);
-  if (tile == 12864) return launch_tiles_h<Policy, 2, 16, 8>(stream, P);
-  if (tile == 64) return launch_tiles_h<Policy, 1, 16, 16>(stream, P);
-  return launch_tiles_h<Policy, 1, 8, 8>(stream, P);
+  if (tile == 128) return launch_tiles_h<Policy, 2, 2, 16, 16>(stream, P);
+  if (tile == 12864) return launch_tiles_h<Policy, 2, 2, 16, 8>(stream, P);
+  if (tile == 6464) return launch_tiles_h<Policy, 1, 2, 16, 8>(stream, P);    // 64 x 64, 128 threads, 4 x 8 per thread
+  if (tile == 64128) return launch_tiles_h<Policy, 1, 2, 16, 16>(stream, P);  // 64 x 128, 256 threads (experiments only)
+  if (tile == 64) return launch_tiles_h<Policy, 1, 1, 16, 16>(stream, P);
+  return launch_tiles_h<Policy, 1, 1, 8, 8>(stream, P);
 }
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }

@@ -32,7 +32,10 @@ struct SyrkPolicy {
   static constexpr bool kTransposedB = true;
   static constexpr bool kUpperTriangle = true;
   struct RowCtx {};
+  using KCtx = int;  // the k index itself
   __device__ __forceinline__ RowCtx row_ctx(int) const { return RowCtx(); }
+  __device__ __forceinline__ KCtx k_ctx(int k) const { return k; }
+  __device__ __forceinline__ void k_advance(KCtx& k, int step) const { k += step; }
   __device__ __forceinline__ float4 load_row(int row, int k) const {
     float4 v = zero4();
     if (row < N) {

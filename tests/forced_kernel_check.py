@@ -76,7 +76,55 @@ def check_i8(N, M, K):
     print(f"OK i8 {N}x{M}x{K}: bit-exact")
 
 
+def check_ffma(M, N, K):
+    """The exact-fp32 tile engine under a forced tile size (EXOB200_FFMA_TILE, EXOB200_FFMA_SCALAR): SGEMM,
+    SSYRK on the upper triangle (N x N from an N x K operand) and a padded, strided convolution whose
+    implicit GEMM has about the same extents, each bit for bit against the oracle."""
+    import torch
+
+    import exo_b200
+    import oracle
+    from tests import inputs
+    from tests.guard import Guarded
+
+    lib, port = exo_b200.library(), oracle.port()
+    port.set_threads(os.cpu_count() or 1)
+    bits = lambda x: np.ascontiguousarray(x).view(np.uint32)
+    dev = lambda x: torch.from_numpy(np.ascontiguousarray(x)).cuda()
+
+    A = inputs.uniform_f32(7 + M, (M, K))
+    B = inputs.uniform_f32(8 + N, (K, N))
+    C0 = inputs.uniform_f32(9 + K, (M, N))
+    out = Guarded(torch, (M, N), torch.float32)
+    out.view.copy_(dev(C0))
+    lib.sgemm_exo_ffma(None, M, N, K, dev(A), dev(B), out.view)
+    torch.cuda.synchronize()
+    assert out.bands_intact(), "a store landed outside the output"
+    assert np.array_equal(bits(out.view.cpu().numpy()), bits(port.sgemm(A, B, C0.copy()))), "sgemm differs"
+
+    S0 = inputs.uniform_f32(10 + N, (N, N))
+    dS = dev(S0)
+    lib.ssyrk_exo_ffma(None, N, K, dev(B.T), dS)
+    torch.cuda.synchronize()
+    assert np.array_equal(bits(dS.cpu().numpy()), bits(port.ssyrk(np.ascontiguousarray(B.T), S0.copy()))), "ssyrk differs"
+
+    b, k, pad, stride, ci = 2, 3, 1, 2, max(1, K // 9)
+    h = w = max(4, int(round((M / b) ** 0.5)) * stride)
+    co = N
+    inp = inputs.uniform_f32(11, (b, h, w, ci))
+    wts = inputs.uniform_f32(12, (k, k, ci, co))
+    bias = inputs.uniform_f32(13, (co,))
+    oh, ow = (h + 2 * pad - k) // stride + 1, (w + 2 * pad - k) // stride + 1
+    cout = Guarded(torch, (b * oh * ow, co), torch.float32)
+    lib.conv_nhwc_strided_exo(None, b, h, w, ci, co, k, pad, stride, True, dev(inp), cout.view, dev(wts), dev(bias))
+    torch.cuda.synchronize()
+    assert cout.bands_intact(), "a store landed outside the output"
+    want = port.conv_nhwc_strided(inp, wts, bias, pad, stride, True).reshape(b * oh * ow, co)
+    assert np.array_equal(bits(cout.view.cpu().numpy()), bits(want)), "conv differs"
+    print(f"OK ffma {M}x{N}x{K}: sgemm, ssyrk and conv bit-exact")
+
+
 if __name__ == "__main__":
     kind = sys.argv[1]
     dims = [int(x) for x in sys.argv[2:5]]
-    {"bf16": check_bf16, "i8": check_i8}[kind](*dims)
+    {"bf16": check_bf16, "i8": check_i8, "ffma": check_ffma}[kind](*dims)

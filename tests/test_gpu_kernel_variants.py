@@ -51,6 +51,19 @@ def test_bf16_kernel_variant_against_reference_sgemm(variant, shape):
     run_forced(VARIANTS_BF16[variant], "bf16", *shape)
 
 
+# The exact-fp32 engine's tile configurations (the default dispatch picks one per shape from a cost table;
+# here each is forced onto the same ragged shape: M, N and K off every tile size, several tiles each way).
+FFMA_TILES = ["128", "12864", "6464", "64128", "64", "32"]
+
+
+@pytest.mark.parametrize("scalar", ["0", "1"])
+@pytest.mark.parametrize("tile", FFMA_TILES)
+def test_ffma_tile_configuration_bit_exact(tile, scalar):
+    if scalar == "1" and tile not in ("128", "6464"):
+        pytest.skip("the one-FMA-per-instruction build is a timing aid; two configurations cover its code")
+    run_forced({"EXOB200_FFMA_TILE": tile, "EXOB200_FFMA_SCALAR": scalar}, "ffma", 300, 333, 77)
+
+
 @pytest.mark.parametrize("variant,env", [("pair_256x256", {"EXOB200_TC2": "1"}), ("single_cta", {"EXOB200_TC2": "0"}),
                                          ("single_cta_transposed_b", {"EXOB200_TC2": "0", "EXOB200_I8_TRANSPOSE": "1"})])
 @pytest.mark.parametrize("shape", [(2048, 2048, 2048), (1000, 528, 272)])
