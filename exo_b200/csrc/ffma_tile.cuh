@@ -40,21 +40,26 @@
 
 #include <algorithm>
 #include <type_traits>
+#include <utility>
 
 namespace exob200 {
 namespace ffma {
 
 constexpr int BK = 16;
-// Tile sizes from one engine (TDY x TDX threads, each 4 HM x 4 HN outputs):
-//   16 x 16, 2 x 2 -> 128 x 128, 256 threads, 8 x 8 per thread: the throughput configuration;
-//   16 x  8, 2 x 2 -> 128 x  64, 128 threads, same per-thread work: medium problems, and when the
-//     128 x 128 tiles would leave a nearly empty last round;
-//   16 x  8, 1 x 2 ->  64 x  64, 128 threads, 4 x 8 per thread: when 128 x 64 tiles would put two CTAs on
-//     a few SMs and one on the rest (tile counts just above the SM count);
-//   16 x 16, 1 x 1 ->  64 x  64, 256 threads, 4 x 4 per thread;
-//    8 x  8, 1 x 1 ->  32 x  32,  64 threads, 4 x 4 per thread: small problems.  Those are bound by the
-//     latency of one warp's k loop, so spreading the same warps over more SMs (one or two per
-//     scheduler instead of four) is what shortens them.
+#ifndef EXOB200_FFMA_SMALL_STAGES
+#define EXOB200_FFMA_SMALL_STAGES 3  // ring depth of the configurations with fewer than 8 x 8 outputs per thread
+#endif
+// Tile sizes from one engine (TDY x TDX threads, each RM rows x 4 HN columns of outputs):
+//   16 x 16 threads, 8 x 8 each -> 128 x 128, 256 threads: the throughput configuration;
+//   16 x  8 threads, 8 x 8 each -> 128 x  64, 128 threads: medium problems, and when the 128 x 128 tiles
+//     would leave a nearly empty last round;
+//   16 x  8 threads, 4 x 8 each ->  64 x  64, 128 threads: when 128 x 64 tiles would put two CTAs on a few
+//     SMs and one on the rest (tile counts just above the SM count);
+//   16 x 16 threads, 4 x 4 each ->  64 x  64, 256 threads;
+//    8 x  8 threads, 4 x 4 each ->  32 x  32,  64 threads, and
+//   16 x  8 threads, 2 x 4 each ->  32 x  32, 128 threads: small problems.  Those are bound by the latency
+//     of one warp's k loop, so spreading the same warps over more SMs (one or two per scheduler instead
+//     of four) is what shortens them.
 // launch_tiles() picks among them with a measured cost table.
 // Without split-K, which the reference's per-element chain order rules out, parallelism only comes
 // from M x N.
@@ -95,6 +100,16 @@ __device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
   return d;
 }
 
+// f(std::integral_constant<int, 0>{}), ..., f(std::integral_constant<int, N - 1>{})
+template <class F, int... I>
+__device__ __forceinline__ void static_for_impl(F&& f, std::integer_sequence<int, I...>) {
+  (f(std::integral_constant<int, I>{}), ...);
+}
+template <int N, class F>
+__device__ __forceinline__ void static_for(F&& f) {
+  static_for_impl(f, std::make_integer_sequence<int, N>{});
+}
+
 // First tile column of tile row tm that holds an element on or above the diagonal (n >= m).
 __host__ __device__ constexpr int first_live_tile_col(int tm, int bm, int bn) { return (tm * bm) / bn; }
 // Number of tiles of an M x N problem; for an upper-triangular one only those that reach the diagonal.
@@ -112,20 +127,25 @@ inline int64_t count_tiles(const Policy& P, int bm, int bn) {
 // the 128-thread 128 x 64 configuration gets that (two CTAs per SM); the 256-thread 128 x 128 one is
 // held to 128 registers so that two CTAs (16 warps) share an SM, which is worth more there than the
 // few spilled values cost (measured at 8192^3: 55.3 against 48.4 TFLOP/s with one CTA per SM).
-template <int HM, int HN, int THREADS>
+template <int RM, int HN, int THREADS>
 __host__ __device__ constexpr int min_ctas() {
-  return (HM * HN == 4 && THREADS == 128) ? 2 : 512 / THREADS;
+  return (RM * HN == 16 && THREADS == 128) ? 2 : 512 / THREADS;
 }
 
-// HM x HN quadrants of 4 x 4 outputs per thread, TDY x TDX threads.
-template <class Policy, bool PACKED, int HM, int HN, int TDY, int TDX>
-__global__ void __launch_bounds__(TDY * TDX, min_ctas<HM, HN, TDY * TDX>())
+// RM rows (2, 4 or 8) x 4 HN columns of outputs per thread, TDY x TDX threads.  The rows come as
+// RM / QR quadrants of QR = min(RM, 4) consecutive rows, the columns as HN quadrants of 4.
+template <class Policy, bool PACKED, int RM, int HN, int TDY, int TDX>
+__global__ void __launch_bounds__(TDY * TDX, min_ctas<RM, HN, TDY * TDX>())
 tile_kernel(const Policy P, int tiles_m, int tiles_n) {
+  static_assert(RM == 2 || RM == 4 || RM == 8, "rows per thread");
   constexpr int THREADS = TDY * TDX;
-  constexpr int QSM = 4 * TDY, QSN = 4 * TDX;  // rows / columns per quadrant
+  constexpr int QR = RM < 4 ? RM : 4, HM = RM / QR;
+  constexpr int QSM = QR * TDY, QSN = 4 * TDX;  // rows / columns per quadrant
   constexpr int BM = QSM * HM, BN = QSN * HN;
   constexpr int AS_PITCH = BM + 4;  // floats; keeps 16-byte alignment, spreads the transposing stores
-  constexpr int RM = 4 * HM, RN = 4 * HN;  // rows and columns per thread
+  constexpr int RN = 4 * HN;        // columns per thread
+  static_assert(BM % (THREADS / 4) == 0 && BK % (THREADS / (BN / 4)) == 0, "the tile loaders cover whole passes");
+  static_assert(!Policy::kTransposedB || BN % (THREADS / 4) == 0, "so does the register route of a transposed B");
   constexpr int BS_PITCH = Policy::kTransposedB ? BN + 4 : BN;  // the transposing stores want the same skew as A's
   // Shared-memory ring of STAGES k-tiles; operands of the next STAGES - 1 tiles are in flight (A in
   // registers, B as cp.async groups).  Three stages for the 4 x 4-per-thread configurations: those run
@@ -135,7 +155,7 @@ tile_kernel(const Policy P, int tiles_m, int tiles_n) {
   // 192 -> 128 us).  The 8 x 8-per-thread configurations keep two stages: their k-tile takes 2000
   // cycles, which already covers the latency, and the second register set cost them 10 %
   // (1024^3 72 -> 82 us).
-  constexpr int STAGES = (HM * HN < 4 && !Policy::kTransposedB) ? 3 : 2;
+  constexpr int STAGES = (RM * HN < 16 && !Policy::kTransposedB) ? EXOB200_FFMA_SMALL_STAGES : 2;
   static_assert(STAGES * BK * (AS_PITCH + BS_PITCH) * 4 <= 48 * 1024, "static shared memory");
   constexpr int D = STAGES - 1;  // tiles of look-ahead = register sets for A
   __shared__ __align__(16) float As[STAGES][BK][AS_PITCH];
@@ -253,7 +273,7 @@ tile_kernel(const Policy P, int tiles_m, int tiles_n) {
   uint64_t acc2[PACKED ? RM : 1][PACKED ? RN / 2 : 1];  // [row][column pair]
 #pragma unroll
   for (int i = 0; i < RM; i++) {
-    const int row = m0 + (i >> 2) * QSM + ty * 4 + (i & 3);
+    const int row = m0 + (i / QR) * QSM + ty * QR + (i % QR);
 #pragma unroll
     for (int jq = 0; jq < HN; jq++) {
       const float4 v = P.init(row, n0 + jq * QSN + tx * 4);
@@ -270,11 +290,9 @@ tile_kernel(const Policy P, int tiles_m, int tiles_n) {
   }
 
   const int ktiles = (K + BK - 1) / BK;
-  using Set0 = std::integral_constant<int, 0>;
-  using Set1 = std::integral_constant<int, D - 1>;  // the second set (the first again when D == 1)
-  load_tile(Set0{}, 0, true);
-  if (D > 1) load_tile(Set1{}, 1, 1 < ktiles);
-  store_tile(Set0{}, 0);
+  // prologue: tiles 0 .. D - 1 requested, tile 0 published
+  static_for<D>([&](auto set) { load_tile(set, decltype(set)::value, decltype(set)::value < ktiles); });
+  store_tile(std::integral_constant<int, 0>{}, 0);
   __syncthreads();
 
   // One k-tile: request tile t + D into the register set / ring slot that tile t's predecessor freed,
@@ -285,13 +303,19 @@ tile_kernel(const Policy P, int tiles_m, int tiles_n) {
     const int kmax = min(BK, K - t * BK);
     auto step = [&](int kk) {
       float a[RM];
+      if constexpr (QR == 4) {
 #pragma unroll
-      for (int h = 0; h < HM; h++) {
-        const float4 av = *reinterpret_cast<const float4*>(&As[buf][kk][h * QSM + ty * 4]);
-        a[h * 4 + 0] = av.x;
-        a[h * 4 + 1] = av.y;
-        a[h * 4 + 2] = av.z;
-        a[h * 4 + 3] = av.w;
+        for (int h = 0; h < HM; h++) {
+          const float4 av = *reinterpret_cast<const float4*>(&As[buf][kk][h * QSM + ty * 4]);
+          a[h * 4 + 0] = av.x;
+          a[h * 4 + 1] = av.y;
+          a[h * 4 + 2] = av.z;
+          a[h * 4 + 3] = av.w;
+        }
+      } else {
+        const float2 av = *reinterpret_cast<const float2*>(&As[buf][kk][ty * 2]);
+        a[0] = av.x;
+        a[1] = av.y;
       }
       if (PACKED) {
         uint64_t b[RN / 2];
@@ -335,17 +359,18 @@ tile_kernel(const Policy P, int tiles_m, int tiles_n) {
   };
   int buf = 0;
   for (int t = 0; t < ktiles; t += D) {
-    iteration(Set0{}, Set1{}, t, buf);
-    buf = (buf + 1) % STAGES;
-    if (D > 1 && t + 1 < ktiles) {
-      iteration(Set1{}, Set0{}, t + 1, buf);
-      buf = (buf + 1) % STAGES;
-    }
+    static_for<D>([&](auto set) {
+      constexpr int S = decltype(set)::value;
+      if (S == 0 || t + S < ktiles) {
+        iteration(set, std::integral_constant<int, (S + 1) % D>{}, t + S, buf);
+        buf = (buf + 1) % STAGES;
+      }
+    });
   }
 
 #pragma unroll
   for (int i = 0; i < RM; i++) {
-    const int row = m0 + (i >> 2) * QSM + ty * 4 + (i & 3);
+    const int row = m0 + (i / QR) * QSM + ty * QR + (i % QR);
 #pragma unroll
     for (int jq = 0; jq < HN; jq++) {
       float4 v;
@@ -369,16 +394,16 @@ inline bool use_packed() {
   return packed;
 }
 
-template <class Policy, int HM, int HN, int TDY, int TDX>
+template <class Policy, int RM, int HN, int TDY, int TDX>
 cudaError_t launch_tiles_h(cudaStream_t stream, const Policy& P) {
-  constexpr int TM = 4 * TDY * HM, TN = 4 * TDX * HN;
+  constexpr int TM = TDY * RM, TN = 4 * TDX * HN;
   const int64_t tiles_m = (P.M + TM - 1) / TM, tiles_n = (P.N + TN - 1) / TN;
   if (tiles_m * tiles_n > INT32_MAX) return cudaErrorInvalidValue;
   const unsigned grid = (unsigned)count_tiles(P, TM, TN);
   if (use_packed())
-    tile_kernel<Policy, true, HM, HN, TDY, TDX><<<grid, TDY * TDX, 0, stream>>>(P, (int)tiles_m, (int)tiles_n);
+    tile_kernel<Policy, true, RM, HN, TDY, TDX><<<grid, TDY * TDX, 0, stream>>>(P, (int)tiles_m, (int)tiles_n);
   else
-    tile_kernel<Policy, false, HM, HN, TDY, TDX><<<grid, TDY * TDX, 0, stream>>>(P, (int)tiles_m, (int)tiles_n);
+    tile_kernel<Policy, false, RM, HN, TDY, TDX><<<grid, TDY * TDX, 0, stream>>>(P, (int)tiles_m, (int)tiles_n);
   return cudaGetLastError();
 }
 
@@ -400,9 +425,13 @@ struct TileConfig {
 constexpr TileConfig kTileConfigs[] = {
     {128, 128, 128, 2, {102.5f, 185.f}},
     {12864, 128, 64, 2, {58.f, 99.f}},
-    {6464, 64, 64, 4, {46.f, 67.5f, 87.5f, 114.5f}},  // 128 threads, 4 x 8 outputs each
-    {64, 64, 64, 2, {42.f, 73.5f}},                    // 256 threads, 4 x 4 outputs each
-    {32, 32, 32, 8, {27.f, 28.f, 34.f, 41.5f, 50.f, 58.5f, 68.f, 76.f}},
+    {6464, 64, 64, 4, {47.f, 66.f, 87.5f, 114.5f}},  // 128 threads, 4 x 8 outputs each
+    {64, 64, 64, 2, {40.5f, 71.5f}},                  // 256 threads, 4 x 4 outputs each
+    {32, 32, 32, 8, {24.f, 27.5f, 37.3f, 40.6f, 54.2f, 57.7f, 72.3f, 76.2f}},  // 64 threads, 4 x 4 each
+    // 128 threads, 2 x 4 outputs each: twice the warps of the row above on the same tile.  Alone on an SM
+    // they hide each other's latency (256^3: 9.4 -> 7.7 us); from two CTAs per SM on, the shared-memory
+    // pipe is the limit (ncu on 512^3: 76 % of its peak while active) and the 4 x 4 threads win.
+    {3224, 32, 32, 4, {18.f, 28.5f, 43.f, 56.5f}},
 };
 
 // Predicted ns per k step of the slowest SM for `tiles` CTAs of configuration c.
@@ -417,11 +446,10 @@ inline double predicted_ns_per_k(const TileConfig& c, int64_t tiles, int sm_coun
 template <class Policy>
 cudaError_t launch_tiles(cudaStream_t stream, const Policy& P, int sm_count = 148) {
   static const int force = [] {
-    const char* e = getenv("EXOB200_FFMA_TILE");  // a TileConfig id (or 64128) forces a tile size (timing experiments)
+    const char* e = getenv("EXOB200_FFMA_TILE");  // a TileConfig id forces a tile size (timing experiments)
     return e ? atoi(e) : 0;
   }();
   int tile = 0;
-  if (force == 64128) tile = force;
   for (const TileConfig& c : kTileConfigs)
     if (force == c.id) tile = force;
   if (tile == 0) {
@@ -432,12 +460,12 @@ cudaError_t launch_tiles(cudaStream_t stream, const Policy& P, int sm_count = 14
       if (tile == 0 || t < best) best = t, tile = c.id;
     }
   }
-  if (tile == 128) return launch_tiles_h<Policy, 2, 2, 16, 16>(stream, P);
-  if (tile == 12864) return launch_tiles_h<Policy, 2, 2, 16, 8>(stream, P);
-  if (tile == 6464) return launch_tiles_h<Policy, 1, 2, 16, 8>(stream, P);    // 64 x 64, 128 threads, 4 x 8 per thread
-  if (tile == 64128) return launch_tiles_h<Policy, 1, 2, 16, 16>(stream, P);  // 64 x 128, 256 threads (experiments only)
-  if (tile == 64) return launch_tiles_h<Policy, 1, 1, 16, 16>(stream, P);
-  return launch_tiles_h<Policy, 1, 1, 8, 8>(stream, P);
+  if (tile == 128) return launch_tiles_h<Policy, 8, 2, 16, 16>(stream, P);
+  if (tile == 12864) return launch_tiles_h<Policy, 8, 2, 16, 8>(stream, P);
+  if (tile == 6464) return launch_tiles_h<Policy, 4, 2, 16, 8>(stream, P);    // 64 x 64, 128 threads, 4 x 8 per thread
+  if (tile == 64) return launch_tiles_h<Policy, 4, 1, 16, 16>(stream, P);
+  if (tile == 3224) return launch_tiles_h<Policy, 2, 1, 16, 8>(stream, P);  // 32 x 32, 128 threads, 2 x 4 per thread
+  return launch_tiles_h<Policy, 4, 1, 8, 8>(stream, P);
 }
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
