@@ -930,12 +930,24 @@ def main():
                     help="bf16, 1 GPU: also time torch.matmul (cuBLAS) on the same buffers, for comparison")
     ap.add_argument("--sustained-seconds", type=float, default=2.0,
                     help="bf16: also time the launch back to back for about this long (0: skip)")
+    ap.add_argument("--time-shapes", default=None,
+                    help="comma-separated MxNxK list: time only sgemm_exo_ffma on these shapes (CUDA-graph replay, L2 "
+                         "flushed) and print one JSON line; with EXOB200_FFMA_TILE this is how the tile cost table "
+                         "of the FFMA engine was measured")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
-    if args.impl == "reference":
+    if args.time_shapes:
+        import torch
+
+        import exo_b200
+        shapes = [tuple(int(x) for x in t.split("x")) for t in args.time_shapes.split(",")]
+        rows = run_shapes(exo_b200.library(), torch, measured_peaks(), shapes, ("ffma",), {"fp32_simt_computed": 74.45})
+        print(json.dumps({"forced_tile": os.environ.get("EXOB200_FFMA_TILE"),
+                          "us": {"x".join(map(str, r["shape"])): round(r["ffma"]["us"], 2) for r in rows}}))
+    elif args.impl == "reference":
         run_reference_arm(args)
     else:
         run_ours(args)
