@@ -40,15 +40,11 @@
 
 #include <algorithm>
 #include <type_traits>
-#include <utility>
 
 namespace exob200 {
 namespace ffma {
 
 constexpr int BK = 16;
-#ifndef EXOB200_FFMA_SMALL_STAGES
-#define EXOB200_FFMA_SMALL_STAGES 3  // ring depth of the configurations with fewer than 8 x 8 outputs per thread
-#endif
 // Tile sizes from one engine (TDY x TDX threads, each RM rows x 4 HN columns of outputs):
 //   16 x 16 threads, 8 x 8 each -> 128 x 128, 256 threads: the throughput configuration;
 //   16 x  8 threads, 8 x 8 each -> 128 x  64, 128 threads: medium problems, and when the 128 x 128 tiles
@@ -100,16 +96,6 @@ __device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
   return d;
 }
 
-// f(std::integral_constant<int, 0>{}), ..., f(std::integral_constant<int, N - 1>{})
-template <class F, int... I>
-__device__ __forceinline__ void static_for_impl(F&& f, std::integer_sequence<int, I...>) {
-  (f(std::integral_constant<int, I>{}), ...);
-}
-template <int N, class F>
-__device__ __forceinline__ void static_for(F&& f) {
-  static_for_impl(f, std::make_integer_sequence<int, N>{});
-}
-
 // First tile column of tile row tm that holds an element on or above the diagonal (n >= m).
 __host__ __device__ constexpr int first_live_tile_col(int tm, int bm, int bn) { return (tm * bm) / bn; }
 // Number of tiles of an M x N problem; for an upper-triangular one only those that reach the diagonal.
@@ -155,8 +141,9 @@ tile_kernel(const Policy P, int tiles_m, int tiles_n) {
   // 192 -> 128 us).  The 8 x 8-per-thread configurations keep two stages: their k-tile takes 2000
   // cycles, which already covers the latency, and the second register set cost them 10 %
   // (1024^3 72 -> 82 us).
-  constexpr int STAGES = (RM * HN < 16 && !Policy::kTransposedB) ? EXOB200_FFMA_SMALL_STAGES : 2;
+  constexpr int STAGES = (RM * HN < 16 && !Policy::kTransposedB) ? 3 : 2;
   static_assert(STAGES * BK * (AS_PITCH + BS_PITCH) * 4 <= 48 * 1024, "static shared memory");
+  static_assert(STAGES == 2 || STAGES == 3, "the k loop below is written for one or two tiles of look-ahead");
   constexpr int D = STAGES - 1;  // tiles of look-ahead = register sets for A
   __shared__ __align__(16) float As[STAGES][BK][AS_PITCH];
   __shared__ __align__(16) float Bs[STAGES][BK][BS_PITCH];
@@ -290,9 +277,15 @@ tile_kernel(const Policy P, int tiles_m, int tiles_n) {
   }
 
   const int ktiles = (K + BK - 1) / BK;
+  // The loop over the look-ahead is written out for D = 1 and D = 2.  (A compile-time loop over D
+  // through a generic lambda compiled to a slower k loop: 1024^3 65.5 -> 71.6 us with 128 x 64 tiles;
+  // rings of four and five stages, tried that way, were within 1 % of three.)
+  using Set0 = std::integral_constant<int, 0>;
+  using Set1 = std::integral_constant<int, D - 1>;  // the second set (the first again when D == 1)
   // prologue: tiles 0 .. D - 1 requested, tile 0 published
-  static_for<D>([&](auto set) { load_tile(set, decltype(set)::value, decltype(set)::value < ktiles); });
-  store_tile(std::integral_constant<int, 0>{}, 0);
+  load_tile(Set0{}, 0, true);
+  if (D > 1) load_tile(Set1{}, 1, 1 < ktiles);
+  store_tile(Set0{}, 0);
   __syncthreads();
 
   // One k-tile: request tile t + D into the register set / ring slot that tile t's predecessor freed,
@@ -359,13 +352,12 @@ tile_kernel(const Policy P, int tiles_m, int tiles_n) {
   };
   int buf = 0;
   for (int t = 0; t < ktiles; t += D) {
-    static_for<D>([&](auto set) {
-      constexpr int S = decltype(set)::value;
-      if (S == 0 || t + S < ktiles) {
-        iteration(set, std::integral_constant<int, (S + 1) % D>{}, t + S, buf);
-        buf = (buf + 1) % STAGES;
-      }
-    });
+    iteration(Set0{}, Set1{}, t, buf);
+    buf = (buf + 1) % STAGES;
+    if (D > 1 && t + 1 < ktiles) {
+      iteration(Set1{}, Set0{}, t + 1, buf);
+      buf = (buf + 1) % STAGES;
+    }
   }
 
 #pragma unroll
