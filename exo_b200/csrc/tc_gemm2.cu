@@ -79,8 +79,13 @@ __device__ __forceinline__ uint32_t mapa(uint32_t local_addr, uint32_t rank) {
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
+// Arrive on a barrier of another CTA of the cluster.  Default semantics (release at CTA scope): the
+// barrier only hands a tensor-memory accumulator back, and the tcgen05 fences on both sides order those
+// accesses.  With .release.cluster the instruction held its thread for about 1.3 us each time (it waits
+// for the thread's earlier global and bulk stores to be visible cluster-wide), which kept the issuing
+// thread -- and the tensor pipe -- waiting at every tile boundary.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 __device__ __forceinline__ void st_cluster_u32(uint32_t cluster_addr, uint32_t v) {
   asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
@@ -615,21 +620,29 @@ gemm_tc2t_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           break;
         }
         tc_fence_after();
-        for (int kb = 0; kb < d && ok; kb++) ok = hi_step(kb);
+        // The upper half starts as soon as its accumulator is free and keeps going while the lower
+        // accumulator still drains: at least d k-blocks ahead, at most STAGES2T - 1 (a stage is only
+        // released by the lower half, and the producer needs one to load into).
+        int hi_kb = 0;
+        while (ok && hi_kb < num_kb && hi_kb < STAGES2T - 1 &&
+               (hi_kb < d || !mbar_try_wait(tempty_bar(1), acc_phase ^ 1u))) {
+          ok = hi_step(hi_kb++);
+          if (ok && hi_kb == num_kb) tc_commit_pair(tfull_bar(0));  // upper accumulator complete
+        }
         if (!ok) break;
-        if (d == num_kb) tc_commit_pair(tfull_bar(0));
         if (!mbar_wait(tempty_bar(1), acc_phase ^ 1u, abort_flag, WAIT_LIMIT_NS)) {
           give_up(44);
           break;
         }
         tc_fence_after();
         for (int kb = 0; kb < num_kb; kb++) {
-          if (kb + d < num_kb) {
-            if (!hi_step(kb + d)) {
+          // steady state: the upper half d k-blocks ahead (the lead of the start shrinks back to d)
+          if (hi_kb < num_kb && hi_kb - kb <= d) {
+            if (!hi_step(hi_kb++)) {
               ok = false;
               break;
             }
-            if (kb + d == num_kb - 1) tc_commit_pair(tfull_bar(0));  // upper accumulator complete
+            if (hi_kb == num_kb) tc_commit_pair(tfull_bar(0));
           }
           // the lower half's stage was waited for when the upper half used it
           issue(lo_stage, 1, kb == 0);
