@@ -55,7 +55,7 @@ cudaError_t launch_bounded_wait_selftest(exo_b200_Context* ctx, uint64_t limit_n
 bool collect_static_status();
 
 // ---- CTA-pair (cta_group::2) variants of the bf16 and int8 GEMMs (tc_gemm2.cu)
-bool tc2_wanted(int64_t M, int64_t N);
+bool tc2_wanted(int64_t M, int64_t N, int64_t min_tiles);
 cudaError_t launch_gemm_bf16_tc2(exo_b200_Context* ctx, int64_t M, int64_t N, int64_t K, const uint16_t* A,
                                  const uint16_t* B, uint16_t* C);
 cudaError_t launch_matmul_i8_tc2(exo_b200_Context* ctx, int64_t rows, int64_t cols, int64_t K, float scale, bool act,

@@ -674,7 +674,7 @@ cudaError_t launch_gemm_bf16_tc(exo_b200_Context* ctx, int64_t M, int64_t N, int
     release_scratch(ctx, 1);
     return e;
   }
-  if (tc2_wanted(M, N)) return launch_gemm_bf16_tc2(ctx, M, N, K, A, B, C);
+  if (tc2_wanted(M, N, 128)) return launch_gemm_bf16_tc2(ctx, M, N, K, A, B, C);
   CUtensorMap ma, mb;
   if (!make_kmajor_map(&ma, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, A, M, K, K * 2, BM)) return cudaErrorUnknown;
   if (!make_kmajor_map(&mb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, B, N, K, K * 2, BN)) return cudaErrorUnknown;
@@ -698,7 +698,7 @@ cudaError_t launch_matmul_i8_tc(exo_b200_Context* ctx, int64_t N, int64_t M, int
   }();
   if (allow_mn && cols % 16 == 0 && aligned16(B)) {
     // B's pitch satisfies TMA: read it MN-major in place, no pre-pass, no scratch
-    if (tc2_wanted(rows, cols)) return launch_matmul_i8_tc2(ctx, rows, cols, K, scale, act, A, B, C);
+    if (tc2_wanted(rows, cols, 4 * 74)) return launch_matmul_i8_tc2(ctx, rows, cols, K, scale, act, A, B, C);
     CUtensorMap ma, mb;
     if (!make_kmajor_map(&ma, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, A, rows, K, K, BM)) return cudaErrorUnknown;
     if (!make_mnmajor_map(&mb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, B, K, cols, cols, ROW_BYTES)) return cudaErrorUnknown;

@@ -899,10 +899,14 @@ cudaError_t launch_tc2(exo_b200_Context* ctx, const CUtensorMap& ma, const CUten
 }  // namespace
 
 // The pair kernel keeps the tensor pipe busier (96 % against 81 % active in ncu
-// captures of the bf16 GEMM) and is used once there are enough 256 x 256 tiles
-// to give every pair several; smaller problems quantise better on the 128 x 256
-// tiles of the single-CTA kernel.  EXOB200_TC2=0 switches it off, =1 forces it.
-bool tc2_wanted(int64_t M, int64_t N) {
+// captures of the bf16 GEMM) and is used once there are enough 256 x 256 tiles;
+// smaller problems quantise better on the 128 x 256 tiles of the single-CTA
+// kernel.  Measured crossover, bf16 (TFLOP/s pair / single): 64 tiles 896 / 932,
+// 128 tiles 1375 / 1360, 144 tiles 1375 / 1349, 192 tiles 1382 / 1287, 256 tiles
+// 1396 / 1287; int8 at 256 tiles (4096^3) still favours the single-CTA kernel
+// (52.1 against 53.9 us), so it keeps the threshold of four tiles per pair.
+// EXOB200_TC2=0 switches the pair kernels off, =1 forces them.
+bool tc2_wanted(int64_t M, int64_t N, int64_t min_tiles) {
   static const int mode = [] {
     const char* e = getenv("EXOB200_TC2");
     return e ? atoi(e) : -1;
@@ -910,7 +914,7 @@ bool tc2_wanted(int64_t M, int64_t N) {
   if (mode == 0) return false;
   if (mode == 1) return true;
   const int64_t tiles = ((M + 255) / 256) * ((N + 255) / 256);
-  return tiles >= 4 * 74;
+  return tiles >= min_tiles;
 }
 
 cudaError_t launch_gemm_bf16_tc2(exo_b200_Context* ctx, int64_t M, int64_t N, int64_t K, const uint16_t* A,
@@ -931,7 +935,9 @@ cudaError_t launch_gemm_bf16_tc2(exo_b200_Context* ctx, int64_t M, int64_t N, in
     return e ? atoi(e) : -1;
   }();
   const int64_t tall_tiles = ((M + 4 * BM - 1) / (4 * BM)) * ((N + BN2 - 1) / BN2);
-  if (tall == 1 || (tall == -1 && tall_tiles >= 4 * 74)) {
+  // (256 such tiles: 1414 against 1483 TFLOP/s for the 256 x 256 variant, the fourth round is half empty;
+  // 288: 1527 against 1468; 384: 1475 against 1457; 512: 1484 against 1442)
+  if (tall == 1 || (tall == -1 && tall_tiles >= 280)) {
     // C as 32 x 32 boxes of 64-byte rows for the staged epilogue; needs a 16-byte pitch and base
     CUtensorMap mc = ma;
     const int tma_store = ep.vec_ok;
