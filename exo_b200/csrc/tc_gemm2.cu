@@ -953,6 +953,11 @@ cudaError_t launch_gemm_bf16_tc2(exo_b200_Context* ctx, int64_t M, int64_t N, in
   return launch_tc2<M2_BF16>(ctx, ma, mb, M, N, K, ep);
 }
 
+// The 512 x 256 variant for int8, from four such tiles per pair: 8192^3 350 us against 362 (256 x 256 per
+// pair) and 367 (single CTA); at 4096^3 (128 tiles, a 73 % full second round) it loses, 56.2 against 52.9
+// and 51.6 us, and 6144^3 (288 tiles) is a tie.
+constexpr int64_t I8_TALL_MIN_TILES = 4 * 74;
+
 cudaError_t launch_matmul_i8_tc2(exo_b200_Context* ctx, int64_t rows, int64_t cols, int64_t K, float scale, bool act,
                                  const int8_t* A, const int8_t* B, int8_t* C) {
   CUtensorMap ma, mb;
@@ -962,6 +967,13 @@ cudaError_t launch_matmul_i8_tc2(exo_b200_Context* ctx, int64_t rows, int64_t co
   if (!make_tiled_map(&ma, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, A, da, sa, boxa)) return cudaErrorUnknown;
   if (!make_tiled_map(&mb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, B, db, sb, boxb)) return cudaErrorUnknown;
   Epi2 ep{C, cols, scale, act ? 1 : 0, (cols % 16 == 0 && aligned16(C)) ? 1 : 0};
+  static const int tall = [] {
+    const char* e = getenv("EXOB200_TC2_TALL");
+    return e ? atoi(e) : -1;
+  }();
+  const int64_t tall_tiles = ((rows + 4 * BM - 1) / (4 * BM)) * ((cols + BN2 - 1) / BN2);
+  if (tall == 1 || (tall == -1 && tall_tiles >= I8_TALL_MIN_TILES))
+    return launch_tc2t<M2_I8>(ctx, ma, mb, ma, 0, rows, cols, K, ep);  // 16-byte global stores: no map for C
   return launch_tc2<M2_I8>(ctx, ma, mb, rows, cols, K, ep);
 }
 

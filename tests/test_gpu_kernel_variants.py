@@ -64,7 +64,9 @@ def test_ffma_tile_configuration_bit_exact(tile, scalar):
     run_forced({"EXOB200_FFMA_TILE": tile, "EXOB200_FFMA_SCALAR": scalar}, "ffma", 300, 333, 77)
 
 
-@pytest.mark.parametrize("variant,env", [("pair_256x256", {"EXOB200_TC2": "1"}), ("single_cta", {"EXOB200_TC2": "0"}),
+@pytest.mark.parametrize("variant,env", [("pair_256x256", {"EXOB200_TC2": "1", "EXOB200_TC2_TALL": "0"}),
+                                         ("pair_512x256", {"EXOB200_TC2": "1", "EXOB200_TC2_TALL": "1"}),
+                                         ("single_cta", {"EXOB200_TC2": "0"}),
                                          ("single_cta_transposed_b", {"EXOB200_TC2": "0", "EXOB200_I8_TRANSPOSE": "1"})])
 @pytest.mark.parametrize("shape", [(2048, 2048, 2048), (1000, 528, 272)])
 def test_i8_kernel_variant_bit_exact(variant, env, shape):
