@@ -421,7 +421,7 @@ class Workload:
     # -- the same conv on the tensor cores (TMA implicit im2col, 3xTF32)
     def _setup_conv_3xtf32(self):
         self._setup_conv()
-        self.launches_per_step = 3  # input split, weight split, conv kernel
+        self.launches_per_step = 2  # one pre-pass (input and weight split), the conv kernel
 
     def step_conv_3xtf32(self):
         b, h, w, ci, co, k, pad = self.cv
@@ -435,7 +435,7 @@ class Workload:
 
     def _setup_conv_ref_3xtf32(self):
         self._setup_conv(cv=(5, 82, 102, 128, 128, 3, 0))
-        self.launches_per_step = 3
+        self.launches_per_step = 2
 
     step_conv_ref_3xtf32 = step_conv_3xtf32
 
@@ -447,7 +447,7 @@ class Workload:
 
     def _setup_conv1x1_3xtf32(self):
         self._setup_conv(cv=(8, 28, 28, 256, 512, 1, 0))
-        self.launches_per_step = 3
+        self.launches_per_step = 2
 
     step_conv1x1_3xtf32 = step_conv_3xtf32
 
@@ -744,6 +744,7 @@ def run_sweep(lib, torch, peaks, skip, probes=None):
     i8_peak = probes.get("int8_tensor") or peaks["bf16_tflops"] * 2
     i8_name = "int8 tensor measured (tcgen05.mma probe)" if probes.get("int8_tensor") else "2 x bf16 measured (nominal int8 ratio)"
     tf32_peak = probes.get("tf32_tensor") or peaks["bf16_tflops"] / 2
+    flush, flush_ms = None, 0.0
     for name in ("sgemm_ffma", "sgemm_3xtf32", "i8", "i8_512", "conv", "conv_3xtf32", "conv1x1", "conv1x1_3xtf32", "conv_ref", "conv_ref_3xtf32",
                  "conv_i8", "bf16"):
         if name == skip:
@@ -763,6 +764,25 @@ def run_sweep(lib, torch, peaks, skip, probes=None):
                 peak, pname = peaks["bf16_tflops"], "bf16 measured"
             out[name] = {"tflops": tf, "ms": ms, "peak": peak, "frac": tf / peak, "peak_is": pname,
                          "launches_per_step": wl.launches_per_step}
+            if ms < 0.2:
+                # A step this short is paced by the host (a call through ctypes takes about as long): also time
+                # it on the device alone, replayed from a CUDA graph with an L2 flush before every step.
+                if flush is None:
+                    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+                    flush_ms = graph_replay_ms(torch, lambda: flush.fill_(1))
+
+                def body():
+                    flush.fill_(1)
+                    wl.step()
+
+                try:
+                    dev_ms = max(graph_replay_ms(torch, body) - flush_ms, 1e-6)
+                    out[name]["device_us"] = dev_ms * 1e3
+                    out[name]["tflops_device"] = wl.flops_total / (dev_ms / 1e3) / 1e12
+                    out[name]["frac_device"] = out[name]["tflops_device"] / peak
+                except Exception as e:
+                    out[name]["device_us_error"] = str(e)[:200]
+                    torch.cuda.synchronize()
             del wl
             torch.cuda.empty_cache()
         except Exception as e:  # a failing side workload must not lose the headline line
@@ -854,6 +874,26 @@ def run_ssyrk(lib, torch, probes):
     return out
 
 
+def graph_replay_ms(torch, body, R=10):
+    """Device time of one `body`: R of them captured in a CUDA graph, median of 5 replays, per body."""
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for _ in range(R):
+            body()
+    g.replay()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(5):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+    times.sort()
+    return times[len(times) // 2] / R
+
+
 def run_shapes(lib, torch, peaks, shapes=None, paths=("ffma", "3xtf32"), probes=None):
     """The SGEMM shape sweep (squares and ragged / skinny shapes) on both fp32
     paths, device time per launch.  Small shapes finish faster than the host can
@@ -864,25 +904,9 @@ def run_shapes(lib, torch, peaks, shapes=None, paths=("ffma", "3xtf32"), probes=
     tf32_peak = probes.get("tf32_tensor") or peaks["bf16_tflops"] / 2
     hbm = peaks["hbm_gbs"]
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
-    R = 10
 
     def replay_ms(body):
-        g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g):
-            for _ in range(R):
-                body()
-        g.replay()
-        torch.cuda.synchronize()
-        times = []
-        for _ in range(5):
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            g.replay()
-            e1.record()
-            torch.cuda.synchronize()
-            times.append(e0.elapsed_time(e1))
-        times.sort()
-        return times[len(times) // 2] / R
+        return graph_replay_ms(torch, body)
 
     flush_ms = replay_ms(lambda: flush.fill_(1))
     out = []
