@@ -15,7 +15,9 @@ FILES = ["test_x86_sgemm.txt", "test_x86_conv.txt", "test_gemmini_matmul.txt", "
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    # the exo-lang/exo checkout: argument, else $EXO_REFERENCE, else a "reference" directory beside this repository
+    ref = sys.argv[1] if len(sys.argv) > 1 else os.environ.get(
+        "EXO_REFERENCE", os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(HERE))), "reference"))
     out = []
     for f in FILES:
         text = open(os.path.join(ref, "tests", "golden", "test_apps", f)).read()
