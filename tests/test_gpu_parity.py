@@ -229,6 +229,8 @@ def test_conv_specialized_reference_fill(lib, port, golden):
     (2, 9, 11, 8, 16, 3, 1, True),
     (1, 7, 5, 3, 5, 3, 0, False),        # ragged channels: scalar loads
     (3, 6, 6, 4, 130, 5, 2, True),
+    (1, 6, 6, 1, 4, 3, 1, True),         # one input channel: a k-tile of 16 walks through 16 taps
+    (2, 8, 8, 20, 12, 3, 1, True),       # Ci = 20: vector loads, a k-tile straddles a tap boundary mid-way
 ])
 def test_conv_nhwc_bit_exact(lib, port, torch, cfg):
     b, h, w, ci, co, k, pad, relu = cfg
