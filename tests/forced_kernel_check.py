@@ -124,7 +124,31 @@ def check_ffma(M, N, K):
     print(f"OK ffma {M}x{N}x{K}: sgemm, ssyrk and conv bit-exact")
 
 
+def check_sgemm(M, N, K):
+    """sgemm_exo_ffma alone (for switches that only move the SGEMM's kernel choice), bit for bit."""
+    import torch
+
+    import exo_b200
+    import oracle
+    from tests import inputs
+    from tests.guard import Guarded
+
+    lib, port = exo_b200.library(), oracle.port()
+    port.set_threads(os.cpu_count() or 1)
+    A = inputs.uniform_f32(17 + M, (M, K))
+    B = inputs.uniform_f32(18 + N, (K, N))
+    C0 = inputs.uniform_f32(19 + K, (M, N))
+    out = Guarded(torch, (M, N), torch.float32)
+    out.view.copy_(torch.from_numpy(C0).cuda())
+    lib.sgemm_exo_ffma(None, M, N, K, torch.from_numpy(A).cuda(), torch.from_numpy(B).cuda(), out.view)
+    torch.cuda.synchronize()
+    assert out.bands_intact(), "a store landed outside the output"
+    want = port.sgemm(A, B, C0.copy())
+    assert np.array_equal(out.view.cpu().numpy().view(np.uint32), want.view(np.uint32)), "sgemm differs"
+    print(f"OK sgemm {M}x{N}x{K}: bit-exact")
+
+
 if __name__ == "__main__":
     kind = sys.argv[1]
     dims = [int(x) for x in sys.argv[2:5]]
-    {"bf16": check_bf16, "i8": check_i8, "ffma": check_ffma}[kind](*dims)
+    {"bf16": check_bf16, "i8": check_i8, "ffma": check_ffma, "sgemm": check_sgemm}[kind](*dims)

@@ -64,6 +64,13 @@ def test_ffma_tile_configuration_bit_exact(tile, scalar):
     run_forced({"EXOB200_FFMA_TILE": tile, "EXOB200_FFMA_SCALAR": scalar}, "ffma", 300, 333, 77)
 
 
+@pytest.mark.parametrize("shape", [(17, 4099, 513), (32, 8192, 300), (12, 1000, 700)])
+def test_skinny_kernel_beyond_its_default_range(shape):
+    """The skinny-M kernel is only dispatched for at most 8 rows and at least 8192 columns; it accepts up to
+    32 rows, so that range is forced here."""
+    run_forced({"EXOB200_SKINNY_MAX_M": "32"}, "sgemm", *shape)
+
+
 @pytest.mark.parametrize("variant,env", [("pair_256x256", {"EXOB200_TC2": "1", "EXOB200_TC2_TALL": "0"}),
                                          ("pair_512x256", {"EXOB200_TC2": "1", "EXOB200_TC2_TALL": "1"}),
                                          ("single_cta", {"EXOB200_TC2": "0"}),
