@@ -471,7 +471,7 @@ template <int MODE>
 __global__ void __launch_bounds__(THREADS2T, 1)
 gemm_tc2t_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmC, int M, int N, int K, Epi2 ep, DeviceStatus* status,
-                 int tiles_m, int tiles_n, int GM, int skew, int relax, int tma_store) {
+                 int tiles_m, int tiles_n, int GM, int skew, int relax, int tma_store, int split_tail) {
   using C = Cfg2<MODE>;
   constexpr int BK = ROW_BYTES / C::ELEM;
   constexpr uint32_t IDESC =
@@ -524,6 +524,31 @@ gemm_tc2t_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int num_tiles = tiles_m * tiles_n;  // 512 x 256 tiles
   const int num_kb = (K + BK - 1) / BK;
   const int d = min(skew, num_kb);
+  // Work items of this pair: tiles pair, pair + num_pairs, ... as long as a whole round of pairs has one each.
+  // A last, partial round of `rest` tiles would keep `rest` pairs busy for a whole tile while the others wait;
+  // when there are pairs enough (2 rest <= num_pairs) it is split into 2 rest half tiles (the 256 x 256 upper or
+  // lower half), one per pair, and takes half as long.  32768 x 16384: 4096 tiles on 74 pairs = 55 rounds + 26
+  // tiles, i.e. 55.5 instead of 56 rounds.
+  const int full_tiles = (num_tiles / num_pairs) * num_pairs;
+  const int rest = num_tiles - full_tiles;
+  const bool split_rest = split_tail && rest > 0 && 2 * rest <= num_pairs;
+  // the item after this pair's full rounds: tile index (or -1) and which halves (0 = both, 1 = upper only, 2 = lower only)
+  int last_tile = -1, last_mode = 0;
+  if (split_rest) {
+    if (pair < 2 * rest) last_tile = full_tiles + (pair >> 1), last_mode = 1 + (pair & 1);
+  } else if (pair < rest) {
+    last_tile = full_tiles + pair;
+  }
+  const int my_items = full_tiles / num_pairs + (last_tile >= 0 ? 1 : 0);
+  auto item = [&](int i, int& t, int& mode) {
+    if (i < full_tiles / num_pairs) {
+      t = pair + i * num_pairs;
+      mode = 0;
+    } else {
+      t = last_tile;
+      mode = last_mode;
+    }
+  };
   auto tile_coord = [&](int t, int& tm, int& tn) {
     const int per_group = GM * tiles_n;
     const int group = t / per_group;
@@ -544,10 +569,12 @@ gemm_tc2t_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = pair; t < num_tiles && ok; t += num_pairs) {
-        int tm, tn;
+      for (int it = 0; it < my_items && ok; it++) {
+        int t, mode, tm, tn;
+        item(it, t, mode);
         tile_coord(t, tm, tn);
-        const int m0 = tm * 4 * BM + (int)rank * BM;  // this CTA's rows of the upper half; lower half: + 2 BM
+        // this CTA's rows of the upper half (lower half: + 2 BM); a half tile's rows go where the upper half's do
+        const int m0 = tm * 4 * BM + (int)rank * BM + (mode == 2 ? 2 * BM : 0);
         const int n0 = tn * BN2 + (int)rank * BHALF;
         for (int kb = 0; kb < num_kb; kb++) {
           // this thread is normally a ring ahead: sleeping between polls (relax ns) instead of
@@ -560,10 +587,11 @@ gemm_tc2t_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
           const uint32_t bar0 = mapa(full_bar(stage), 0);
           const uint32_t dst = tiles + stage * STAGE2T_BYTES;
-          if (rank == 0) mbar_arrive_expect_tx(full_bar(stage), 2 * STAGE2T_BYTES);
+          if (rank == 0)
+            mbar_arrive_expect_tx(full_bar(stage), 2 * (mode == 0 ? STAGE2T_BYTES : STAGE2T_BYTES - A_TILE_BYTES));
           const int k0 = kb * BK;
           tma_load_2d_pair(dst, &tmA, bar0, k0, m0);
-          tma_load_2d_pair(dst + A_TILE_BYTES, &tmA, bar0, k0, m0 + 2 * BM);
+          if (mode == 0) tma_load_2d_pair(dst + A_TILE_BYTES, &tmA, bar0, k0, m0 + 2 * BM);
           if (C::BMN)
             tma_load_2d_pair(dst + 2 * A_TILE_BYTES, &tmB, bar0, n0, k0);
           else
@@ -614,12 +642,24 @@ gemm_tc2t_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
         return true;
       };
-      for (int t = pair; t < num_tiles && ok; t += num_pairs) {
+      for (int it = 0; it < my_items && ok; it++) {
+        int t, mode;
+        item(it, t, mode);
         if (!mbar_wait(tempty_bar(0), acc_phase ^ 1u, abort_flag, WAIT_LIMIT_NS)) {
           give_up(42);
           break;
         }
         tc_fence_after();
+        if (mode != 0) {
+          // a half tile (always this pair's last item): accumulator 0 only, and the stage is released right away
+          for (int kb = 0; kb < num_kb && ok; kb++) {
+            const int stage = hi_stage;
+            ok = hi_step(kb);
+            if (ok) tc_commit_pair(empty_bar(stage));
+          }
+          if (ok) tc_commit_pair(tfull_bar(0));
+          break;
+        }
         // The upper half starts as soon as its accumulator is free and keeps going while the lower
         // accumulator still drains: at least d k-blocks ahead, at most STAGES2T - 1 (a stage is only
         // released by the lower half, and the producer needs one to load into).
@@ -711,14 +751,43 @@ gemm_tc2t_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     auto acc_addr = [&](int half) {
       return tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(half * BN2 + part * (BN2 / 2));
     };
-    for (int t = pair; t < num_tiles && ok; t += num_pairs) {
-      int tm, tn;
+    for (int it = 0; it < my_items && ok; it++) {
+      int t, mode, tm, tn;
+      item(it, t, mode);
       tile_coord(t, tm, tn);
       const int n0 = tn * BN2;
       const int c0 = n0 + part * (BN2 / 2);
-      const int mu = tm * 4 * BM + (int)rank * BM + q * 32;  // this warp's first row of the upper half
-      const int ml = mu + 2 * BM;                             // ... and of the lower half
+      // this warp's first row of the upper half (of the one half, for a half tile) and of the lower half
+      const int mu = tm * 4 * BM + (int)rank * BM + q * 32 + (mode == 2 ? 2 * BM : 0);
+      const int ml = mu + 2 * BM;
       uint32_t r0[32], r1[32], r2[32], r3[32];
+      if (mode != 0) {
+        // a half tile: accumulator 0 only
+        if (!(ok = wait_full(0))) break;
+        tmem_ld_32x32(acc_addr(0), r0);
+        tmem_ld_32x32(acc_addr(0) + 32, r1);
+        tmem_ld_32x32(acc_addr(0) + 64, r2);
+        tmem_ld_32x32(acc_addr(0) + 96, r3);
+        tmem_ld_wait();
+        hand_back(0);
+        if (MODE == M2_BF16 && tma_store) {
+          uint32_t p0[16], p1[16], p2[16], p3[16];
+          pack(r0, p0);
+          pack(r1, p1);
+          pack(r2, p2);
+          pack(r3, p3);
+          stage_store(p0, mu, c0);
+          stage_store(p1, mu, c0 + 32);
+          stage_store(p2, mu, c0 + 64);
+          stage_store(p3, mu, c0 + 96);
+        } else {
+          store_chunk2<MODE>(ep, r0, mu + lane, c0, M, N);
+          store_chunk2<MODE>(ep, r1, mu + lane, c0 + 32, M, N);
+          store_chunk2<MODE>(ep, r2, mu + lane, c0 + 64, M, N);
+          store_chunk2<MODE>(ep, r3, mu + lane, c0 + 96, M, N);
+        }
+        break;
+      }
       if (MODE == M2_BF16 && tma_store) {
         // Upper accumulator: this warp's four 32-column chunks, all loads in flight at once, then the
         // accumulator goes back to the MMA thread; conversion and stores follow off the critical path.
@@ -836,8 +905,12 @@ cudaError_t launch_tc2t(exo_b200_Context* ctx, const CUtensorMap& ma, const CUte
     const char* e = getenv("EXOB200_TC2T_DIRECT");  // 1: 16-byte global stores instead of staged TMA stores
     return e ? atoi(e) : 0;
   }();
+  static const int split_tail = [] {
+    const char* e = getenv("EXOB200_TC2T_SPLIT_TAIL");  // 0: a partial last round keeps whole tiles
+    return e ? atoi(e) : 1;
+  }();
   return cudaLaunchKernelEx(&cfg, gemm_tc2t_kernel<MODE>, ma, mb, mc, (int)M, (int)N, (int)K, ep, ctx->status_dev,
-                            (int)tiles_m, (int)tiles_n, gm, skew, relax, (tma_store && !direct) ? 1 : 0);
+                            (int)tiles_m, (int)tiles_n, gm, skew, relax, (tma_store && !direct) ? 1 : 0, split_tail);
 }
 
 template <int MODE>

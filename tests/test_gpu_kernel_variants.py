@@ -43,7 +43,8 @@ VARIANTS_BF16 = {
 
 
 @pytest.mark.parametrize("variant", list(VARIANTS_BF16))
-@pytest.mark.parametrize("shape", [(2048, 2048, 2048), (1100, 776, 520), (513, 264, 72), (300, 1001, 136)])
+@pytest.mark.parametrize("shape", [(2048, 2048, 2048), (1100, 776, 520), (513, 264, 72), (300, 1001, 136),
+                                   (5000, 2040, 72)])  # 80 tiles of 512 x 256: a last round of 6, split into halves
 def test_bf16_kernel_variant_against_reference_sgemm(variant, shape):
     """The 2048^3 sub-block (and two ragged shapes: M, N and K all off the tile
     sizes) through each kernel, against the reference fp32 SGEMM chain on the
@@ -75,7 +76,7 @@ def test_skinny_kernel_beyond_its_default_range(shape):
                                          ("pair_512x256", {"EXOB200_TC2": "1", "EXOB200_TC2_TALL": "1"}),
                                          ("single_cta", {"EXOB200_TC2": "0"}),
                                          ("single_cta_transposed_b", {"EXOB200_TC2": "0", "EXOB200_I8_TRANSPOSE": "1"})])
-@pytest.mark.parametrize("shape", [(2048, 2048, 2048), (1000, 528, 272)])
+@pytest.mark.parametrize("shape", [(2048, 2048, 2048), (1000, 528, 272), (5000, 2048, 272)])
 def test_i8_kernel_variant_bit_exact(variant, env, shape):
     run_forced(env, "i8", *shape)
 
@@ -98,7 +99,8 @@ def test_bf16_headline_shape_rows_against_oracle(port, torch_mod):
     lib.gemm_bf16_exo(None, M, N, K, A, B, out.view)
     torch.cuda.synchronize()
     assert out.bands_intact()
-    rows = [0, 1, 127, 128, 255, 256, 383, 384, 511, 512, 16383, 16384, 20000, 32255, 32256, M - 129, M - 2, M - 1]
+    rows = [0, 1, 127, 128, 255, 256, 383, 384, 511, 512, 16383, 16384, 20000, 31020, 31237, 32255, 32256, M - 129, M - 2,
+            M - 1]  # the last four tile rows hold the half tiles of the split last round
     idx = torch.tensor(rows, device="cuda")
     got_bits = out.view[idx].view(torch.int16).cpu().numpy().view(np.uint16)
     A_rows = A[idx].view(torch.int16).cpu().numpy().view(np.uint16)
