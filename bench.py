@@ -768,11 +768,11 @@ def run_sweep(lib, torch, peaks, skip, probes=None):
                 # A step this short is paced by the host (a call through ctypes takes about as long): also time
                 # it on the device alone, replayed from a CUDA graph with an L2 flush before every step.
                 if flush is None:
-                    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
-                    flush_ms = graph_replay_ms(torch, lambda: flush.fill_(1))
+                    flush = L2Flush(torch)
+                    flush_ms = graph_replay_ms(torch, flush)
 
                 def body():
-                    flush.fill_(1)
+                    flush()
                     wl.step()
 
                 try:
@@ -874,6 +874,22 @@ def run_ssyrk(lib, torch, probes):
     return out
 
 
+class L2Flush:
+    """Flushes L2 between timed launches: a 256 MB write (larger than the 126 MB L2), then a 256 MB read of a
+    second buffer.  The write alone leaves L2 full of dirty lines that are written back while the next kernel
+    runs, which costs an HBM-bound kernel DRAM bandwidth that is not its own (1 x 8192 x 2048: 18.0 us after
+    the write alone, 14.7 us after write + read, 13.7 us after a read-only flush, 11.8 us warm); after the read
+    L2 holds clean lines of an unrelated buffer."""
+
+    def __init__(self, torch):
+        self.dirty = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+        self.clean = torch.zeros(256 << 20, dtype=torch.uint8, device="cuda")
+
+    def __call__(self):
+        self.dirty.fill_(1)
+        self.clean.max()
+
+
 def graph_replay_ms(torch, body, R=10):
     """Device time of one `body`: R of them captured in a CUDA graph, median of 5 replays, per body."""
     g = torch.cuda.CUDAGraph()
@@ -898,17 +914,18 @@ def run_shapes(lib, torch, peaks, shapes=None, paths=("ffma", "3xtf32"), probes=
     """The SGEMM shape sweep (squares and ragged / skinny shapes) on both fp32
     paths, device time per launch.  Small shapes finish faster than the host can
     launch them, so launches are replayed from a CUDA graph: R x [L2 flush (a
-    256 MB write), GEMM], minus a graph of R flushes alone; median of 5 replays."""
+    256 MB write, then a 256 MB read), GEMM], minus a graph of R flushes alone;
+    median of 5 replays."""
     probes = probes or {}
     simt_peak = probes.get("fp32_simt") or probes.get("fp32_simt_computed")
     tf32_peak = probes.get("tf32_tensor") or peaks["bf16_tflops"] / 2
     hbm = peaks["hbm_gbs"]
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    flush = L2Flush(torch)
 
     def replay_ms(body):
         return graph_replay_ms(torch, body)
 
-    flush_ms = replay_ms(lambda: flush.fill_(1))
+    flush_ms = replay_ms(flush)
     out = []
     gen = torch.Generator(device="cuda").manual_seed(3)
     for (M, N, K) in (shapes or SGEMM_SHAPES):
@@ -918,22 +935,36 @@ def run_shapes(lib, torch, peaks, shapes=None, paths=("ffma", "3xtf32"), probes=
         flops = 2.0 * M * N * K
         nbytes = 4.0 * (M * K + K * N + 2 * M * N)
         row = {"shape": [M, N, K], "flop_per_byte": flops / nbytes}
+        big = twin = None
         for path, fn in (("ffma", lib.sgemm_exo_ffma), ("3xtf32", lib.sgemm_exo_3xtf32)):
             if path not in paths:
                 continue
             for _ in range(3):
                 fn(None, M, N, K, A, B, C)  # warm-up: also sizes the scratch before capture
             torch.cuda.synchronize()
+            # let the clocks recover: a small shape timed right after a power-capped large one inherits its
+            # low clock (1000^3 measured 83.6 us directly after the 4096^3 rows, 63.1 us on its own)
+            time.sleep(0.1)
 
-            # operands larger than L2 (126 MB) need no flush: they evict themselves.  (The flush is a 256 MB
-            # write, and its dirty lines are written back while the next kernel runs: for the HBM-bound
-            # 1 x 8192 x 8192 that adds DRAM traffic of its own, 56 - 58 us against 51 us without.)
+            # operands larger than L2 (126 MB) need no flush: they evict themselves
             flushed = nbytes <= 1.5 * 126e6
+
+            # ... but the tail of the previous launch's pass is still there, so those launches alternate
+            # between two copies of the larger operand
+            if not flushed and twin is None:
+                big = A if A.numel() >= B.numel() else B
+                twin = big.clone()
+            toggle = [0]
 
             def body():
                 if flushed:
-                    flush.fill_(1)
-                fn(None, M, N, K, A, B, C)
+                    flush()
+                    fn(None, M, N, K, A, B, C)
+                else:
+                    toggle[0] ^= 1
+                    a = twin if (toggle[0] and big is A) else A
+                    b = twin if (toggle[0] and big is B) else B
+                    fn(None, M, N, K, a, b, C)
 
             ms = max(replay_ms(body) - (flush_ms if flushed else 0.0), 1e-6)
             tf, gbs = flops / ms / 1e9, nbytes / ms / 1e6
@@ -941,7 +972,7 @@ def run_shapes(lib, torch, peaks, shapes=None, paths=("ffma", "3xtf32"), probes=
             # the roofline that binds: min(compute peak, bandwidth x arithmetic intensity)
             ceiling = min(peak_tf, hbm * row["flop_per_byte"] / 1e3)
             row[path] = {"us": ms * 1e3, "tflops": tf, "gbs": gbs, "bound": "hbm" if ceiling < peak_tf else "compute",
-                         "frac_of_roofline": tf / ceiling, "l2": "flushed" if flushed else "operands larger than L2"}
+                         "frac_of_roofline": tf / ceiling, "l2": "flushed" if flushed else "operands larger than L2, two copies alternating"}
         out.append(row)
     lib.synchronize()
     return out
