@@ -500,22 +500,34 @@ __host__ __device__ constexpr int tl_stage_floats() { return ROWS * TL_PITCH + T
 template <int ROWS>
 __host__ __device__ constexpr int tl_smem() { return TL_STAGES * tl_stage_floats<ROWS>() * (int)sizeof(float); }  // 110 KiB / 42.5 KiB
 
-template <int NQ, int ROWS>  // NQ = ceil(N / 4): column quads per row, 1..4
-__global__ void __launch_bounds__(ROWS)
+// NQ = ceil(N / 4): column quads per row, 1..4.  A thread owns QPT quads of one row (NQ / QPT threads per row,
+// in adjacent lanes, which read the row's A value as one broadcast): with a whole row per thread there were
+// only M / 32 warps, two per scheduler, and the k step waited on its shared-memory loads (ncu on
+// 32768 x 8 x 512: short-scoreboard stalls 1.9 per issue, 33 % issue active).  Measured, us, quads per thread
+// 1 / 2 / 4: 32768 x 8 x 512 21.1 / 24.6 / -; 16384 x 16 x 512 26.0 / 18.4 / 23.2; 32768 x 16 x 2048
+// 178 / 102 / 118; 4096 x 8 x 4096 89.7 / 120.8 / -; 20000 x 12 x 300 (three quads) 26.1 for one, 20.5 for all
+// three per thread.  Hence one quad per thread up to N = 8, two for N = 13 .. 16, the row for N = 9 .. 12.
+template <int NQ, int QPT, int ROWS>  // QPT: quads per thread (NQ / QPT threads per row)
+__global__ void __launch_bounds__(ROWS * (NQ / QPT))
 sgemm_tall_kernel(int M, int N, int K, const float* __restrict__ A, const float* __restrict__ B,
                   float* __restrict__ C, int a_vec, int b_vec) {
+  static_assert(NQ % QPT == 0, "whole threads per row");
   extern __shared__ __align__(16) float tl_smem_buf[];
   constexpr int STAGE = tl_stage_floats<ROWS>();
+  constexpr int TPR = NQ / QPT;  // threads per row
+  constexpr int THREADS = ROWS * TPR;
   const int tid = threadIdx.x;
   const int m0 = blockIdx.x * ROWS;
-  const int row = m0 + tid;
+  const int r_local = tid / TPR, q0 = (tid % TPR) * QPT;
+  const int row = m0 + r_local;
 
-  uint64_t acc2[NQ][2];
+  uint64_t acc2[QPT][2];
 #pragma unroll
-  for (int q = 0; q < NQ; q++) {
+  for (int q = 0; q < QPT; q++) {
     float v[4];
 #pragma unroll
-    for (int j = 0; j < 4; j++) v[j] = (row < M && q * 4 + j < N) ? C[(int64_t)row * N + q * 4 + j] : 0.f;
+    for (int j = 0; j < 4; j++)
+      v[j] = (row < M && (q0 + q) * 4 + j < N) ? C[(int64_t)row * N + (q0 + q) * 4 + j] : 0.f;
     acc2[q][0] = ffma::pack2(v[0], v[1]);
     acc2[q][1] = ffma::pack2(v[2], v[3]);
   }
@@ -526,10 +538,11 @@ sgemm_tall_kernel(int M, int N, int K, const float* __restrict__ A, const float*
       float* as = tl_smem_buf + (st % TL_STAGES) * STAGE;
       float* bs = as + ROWS * TL_PITCH;
       const int k0 = st * TL_KS;
-      // A: ROWS rows x 8 k-quads, 8 quads per thread; 8 consecutive threads cover one row segment
+      // A: ROWS rows x 8 k-quads; 8 consecutive threads cover one row segment
 #pragma unroll
-      for (int i = 0; i < 8; i++) {
-        const int e = tid + i * ROWS;
+      for (int i = 0; i < (ROWS * 8 + THREADS - 1) / THREADS; i++) {
+        const int e = tid + i * THREADS;
+        if ((ROWS * 8) % THREADS != 0 && e >= ROWS * 8) break;
         const int r = e >> 3, kq = (e & 7) * 4;
         const bool rin = m0 + r < M;
         const float* src = A + (rin ? (int64_t)(m0 + r) * K : 0);
@@ -546,13 +559,13 @@ sgemm_tall_kernel(int M, int N, int K, const float* __restrict__ A, const float*
       }
       // B: 32 k x 32 columns (zero beyond N)
       if (b_vec) {  // N % 4 == 0
-        for (int e = tid; e < TL_KS * 8; e += ROWS) {
+        for (int e = tid; e < TL_KS * 8; e += THREADS) {
           const int kk = e >> 3, c = (e & 7) * 4;
           const bool ok = k0 + kk < K && c < N;
           ffma::cp_async16(bs + kk * 32 + c, B + (ok ? (int64_t)(k0 + kk) * N + c : 0), ok);
         }
       } else {
-        for (int e = tid; e < TL_KS * 32; e += ROWS) {
+        for (int e = tid; e < TL_KS * 32; e += THREADS) {
           const int kk = e >> 5, c = e & 31;
           const bool ok = k0 + kk < K && c < N;
           ffma::cp_async4(bs + kk * 32 + c, B + (ok ? (int64_t)(k0 + kk) * N + c : 0), ok);
@@ -567,13 +580,13 @@ sgemm_tall_kernel(int M, int N, int K, const float* __restrict__ A, const float*
     asm volatile("cp.async.wait_group %0;" ::"n"(TL_STAGES - 2) : "memory");
     __syncthreads();
     issue(st + TL_STAGES - 1);
-    const float* as = tl_smem_buf + (st % TL_STAGES) * STAGE + tid * TL_PITCH;
-    const float* bs = tl_smem_buf + (st % TL_STAGES) * STAGE + ROWS * TL_PITCH;
+    const float* as = tl_smem_buf + (st % TL_STAGES) * STAGE + r_local * TL_PITCH;
+    const float* bs = tl_smem_buf + (st % TL_STAGES) * STAGE + ROWS * TL_PITCH + q0 * 4;
     const int kmax = min(TL_KS, K - st * TL_KS);
     auto step = [&](float a, int kk) {
       const uint64_t aa = ffma::pack2(a, a);
 #pragma unroll
-      for (int q = 0; q < NQ; q++) {
+      for (int q = 0; q < QPT; q++) {
         const ulonglong2 bv = *reinterpret_cast<const ulonglong2*>(bs + kk * 32 + q * 4);
         acc2[q][0] = ffma::fma2(aa, bv.x, acc2[q][0]);
         acc2[q][1] = ffma::fma2(aa, bv.y, acc2[q][1]);
@@ -594,31 +607,47 @@ sgemm_tall_kernel(int M, int N, int K, const float* __restrict__ A, const float*
   }
   if (row < M) {
 #pragma unroll
-    for (int q = 0; q < NQ; q++) {
+    for (int q = 0; q < QPT; q++) {
       float v[4];
       ffma::unpack2(acc2[q][0], v[0], v[1]);
       ffma::unpack2(acc2[q][1], v[2], v[3]);
 #pragma unroll
       for (int j = 0; j < 4; j++)
-        if (q * 4 + j < N) C[(int64_t)row * N + q * 4 + j] = v[j];
+        if ((q0 + q) * 4 + j < N) C[(int64_t)row * N + (q0 + q) * 4 + j] = v[j];
     }
   }
 }
 
-template <int NQ, int ROWS>
+template <int NQ, int QPT, int ROWS>
 cudaError_t launch_tall_r(int device, cudaStream_t stream, int M, int N, int K, const float* A, const float* B,
                           float* C, int a_vec, int b_vec) {
-  EXOB200_SMEM_ATTR_ONCE((sgemm_tall_kernel<NQ, ROWS>), tl_smem<ROWS>(), device);
-  sgemm_tall_kernel<NQ, ROWS><<<(unsigned)((M + ROWS - 1) / ROWS), ROWS, tl_smem<ROWS>(), stream>>>(M, N, K, A, B, C,
-                                                                                                   a_vec, b_vec);
+  EXOB200_SMEM_ATTR_ONCE((sgemm_tall_kernel<NQ, QPT, ROWS>), tl_smem<ROWS>(), device);
+  sgemm_tall_kernel<NQ, QPT, ROWS><<<(unsigned)((M + ROWS - 1) / ROWS), ROWS * (NQ / QPT), tl_smem<ROWS>(), stream>>>(
+      M, N, K, A, B, C, a_vec, b_vec);
   return cudaGetLastError();
 }
 
 template <int NQ>
 cudaError_t launch_tall(int device, cudaStream_t stream, int M, int N, int K, const float* A, const float* B, float* C,
                         int a_vec, int b_vec) {
+  static const int force = [] {
+    const char* e = getenv("EXOB200_TALL_QPT");  // quads per thread (timing experiments); 0 / unset: the default
+    return e ? atoi(e) : 0;
+  }();
   // 32-row (one warp) CTAs were measured too: slower than 128-row CTAs from 8192 rows up, equal below
-  return launch_tall_r<NQ, 128>(device, stream, M, N, K, A, B, C, a_vec, b_vec);
+  if constexpr (NQ == 1) {
+    return launch_tall_r<1, 1, 128>(device, stream, M, N, K, A, B, C, a_vec, b_vec);
+  } else if constexpr (NQ == 3) {  // three threads per row straddle warps: the whole row per thread is faster here
+    if (force == 1) return launch_tall_r<3, 1, 128>(device, stream, M, N, K, A, B, C, a_vec, b_vec);
+    return launch_tall_r<3, 3, 128>(device, stream, M, N, K, A, B, C, a_vec, b_vec);
+  } else if constexpr (NQ == 2) {
+    if (force == 2) return launch_tall_r<2, 2, 128>(device, stream, M, N, K, A, B, C, a_vec, b_vec);
+    return launch_tall_r<2, 1, 128>(device, stream, M, N, K, A, B, C, a_vec, b_vec);
+  } else {
+    if (force == 1) return launch_tall_r<4, 1, 128>(device, stream, M, N, K, A, B, C, a_vec, b_vec);
+    if (force == 4) return launch_tall_r<4, 4, 128>(device, stream, M, N, K, A, B, C, a_vec, b_vec);
+    return launch_tall_r<4, 2, 128>(device, stream, M, N, K, A, B, C, a_vec, b_vec);
+  }
 }
 
 }  // namespace
