@@ -111,7 +111,11 @@ constexpr int SK_STAGES = 9;    // 108 KiB of shared memory: two CTAs per SM
 constexpr int SK_THREADS = 128;
 constexpr int SK_SMEM = SK_STAGES * (SK_KS * SK_W + SK_KS * 32) * (int)sizeof(float);  // 9 x 12 KiB
 
-template <bool VB>
+// RPT rows per thread: 4 (eight row groups: up to 32 rows), or 2 (up to 16 rows) for the at most 8 rows the
+// default dispatch sends here -- with four rows per thread those keep one warp of the four busy.  Measured, us,
+// 4 / 2 / 1 rows per thread: 8 x 8192 x 512 14.1 / 12.4 / 13.1; 8 x 8192 x 4096 101.8 / 83.7 / 87.7;
+// 8 x 32768 x 512 31.1 / 31.4 / 39.9 (one row per thread needs a shared-memory load per four FMAs).
+template <bool VB, int RPT>
 __global__ void __launch_bounds__(SK_THREADS)
 sgemm_skinny_kernel(int M, int N, int K, const float* __restrict__ A, const float* __restrict__ B,
                     float* __restrict__ C) {
@@ -121,17 +125,17 @@ sgemm_skinny_kernel(int M, int N, int K, const float* __restrict__ A, const floa
 
   const int tid = threadIdx.x;
   const int cq = tid & 15, rg = tid >> 4;
-  const int n0 = blockIdx.x * SK_W, m0 = blockIdx.y * 32;
+  const int n0 = blockIdx.x * SK_W, m0 = blockIdx.y * (8 * RPT);
   const int col = n0 + cq * 4;
-  const int rows_here = min(32, M - m0);
-  const bool live = rg * 4 < rows_here;
+  const int rows_here = min(8 * RPT, M - m0);
+  const bool live = rg * RPT < rows_here;
 
-  float acc[4][4];
+  float acc[RPT][4];
 #pragma unroll
-  for (int i = 0; i < 4; i++)
+  for (int i = 0; i < RPT; i++)
 #pragma unroll
     for (int j = 0; j < 4; j++) {
-      const int r = m0 + rg * 4 + i, c = col + j;
+      const int r = m0 + rg * RPT + i, c = col + j;
       acc[i][j] = (r < M && c < N) ? C[(int64_t)r * N + c] : 0.f;
     }
 
@@ -178,10 +182,16 @@ sgemm_skinny_kernel(int M, int N, int K, const float* __restrict__ A, const floa
       const int kmax = min(SK_KS, K - st * SK_KS);
       auto step = [&](int kk) {
         const float4 b = *reinterpret_cast<const float4*>(&Bs[buf][kk][cq * 4]);
-        const float4 a = *reinterpret_cast<const float4*>(&As[buf][kk][rg * 4]);
-        const float av[4] = {a.x, a.y, a.z, a.w};
+        float av[4];
+        if constexpr (RPT == 4) {
+          const float4 a = *reinterpret_cast<const float4*>(&As[buf][kk][rg * 4]);
+          av[0] = a.x, av[1] = a.y, av[2] = a.z, av[3] = a.w;
+        } else {
+          const float2 a = *reinterpret_cast<const float2*>(&As[buf][kk][rg * 2]);
+          av[0] = a.x, av[1] = a.y;
+        }
 #pragma unroll
-        for (int i = 0; i < 4; i++) {
+        for (int i = 0; i < RPT; i++) {
           acc[i][0] = fmaf(av[i], b.x, acc[i][0]);
           acc[i][1] = fmaf(av[i], b.y, acc[i][1]);
           acc[i][2] = fmaf(av[i], b.z, acc[i][2]);
@@ -197,10 +207,10 @@ sgemm_skinny_kernel(int M, int N, int K, const float* __restrict__ A, const floa
     }
   }
 #pragma unroll
-  for (int i = 0; i < 4; i++)
+  for (int i = 0; i < RPT; i++)
 #pragma unroll
     for (int j = 0; j < 4; j++) {
-      const int r = m0 + rg * 4 + i, c = col + j;
+      const int r = m0 + rg * RPT + i, c = col + j;
       if (r < M && c < N) C[(int64_t)r * N + c] = acc[i][j];
     }
 }
@@ -715,14 +725,17 @@ cudaError_t launch_sgemm_ffma(exo_b200_Context* ctx, int64_t M, int64_t N, int64
     return e ? atoi(e) : 8;
   }();
   if (M <= skinny_max_m && (N >= 8192 || skinny_max_m != 8)) {
-    dim3 grid((unsigned)((N + SK_W - 1) / SK_W), (unsigned)((M + 31) / 32));
-    if (vb) {
-      EXOB200_SMEM_ATTR_ONCE(sgemm_skinny_kernel<true>, SK_SMEM, ctx->device);
-      sgemm_skinny_kernel<true><<<grid, SK_THREADS, SK_SMEM, stream>>>((int)M, (int)N, (int)K, A, B, C);
-    } else {
-      EXOB200_SMEM_ATTR_ONCE(sgemm_skinny_kernel<false>, SK_SMEM, ctx->device);
-      sgemm_skinny_kernel<false><<<grid, SK_THREADS, SK_SMEM, stream>>>((int)M, (int)N, (int)K, A, B, C);
-    }
+#define EXOB200_SKINNY(VB_, RPT_)                                                                            \
+  {                                                                                                        \
+    dim3 grid((unsigned)((N + SK_W - 1) / SK_W), (unsigned)((M + 8 * RPT_ - 1) / (8 * RPT_)));             \
+    EXOB200_SMEM_ATTR_ONCE((sgemm_skinny_kernel<VB_, RPT_>), SK_SMEM, ctx->device);                        \
+    sgemm_skinny_kernel<VB_, RPT_><<<grid, SK_THREADS, SK_SMEM, stream>>>((int)M, (int)N, (int)K, A, B, C); \
+  }
+    if (M <= 8 && vb) EXOB200_SKINNY(true, 2)
+    else if (M <= 8) EXOB200_SKINNY(false, 2)
+    else if (vb) EXOB200_SKINNY(true, 4)
+    else EXOB200_SKINNY(false, 4)
+#undef EXOB200_SKINNY
     return cudaGetLastError();
   }
 #define EXOB200_LAUNCH(VA_, VB_) \
