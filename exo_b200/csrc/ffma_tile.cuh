@@ -53,7 +53,8 @@ constexpr int BK = 16;
 //     SMs and one on the rest (tile counts just above the SM count);
 //   16 x 16 threads, 4 x 4 each ->  64 x  64, 256 threads;
 //    8 x  8 threads, 4 x 4 each ->  32 x  32,  64 threads, and
-//   16 x  8 threads, 2 x 4 each ->  32 x  32, 128 threads: small problems.  Those are bound by the latency
+//   16 x  8 threads, 2 x 4 each ->  32 x  32, 128 threads, and
+//    8 x 16 threads, 2 x 4 each ->  16 x  64, 128 threads (at most 16 rows): small problems.  Those are bound by the latency
 //     of one warp's k loop, so spreading the same warps over more SMs (one or two per scheduler instead
 //     of four) is what shortens them.
 // launch_tiles() picks among them with a measured cost table.
@@ -130,7 +131,8 @@ tile_kernel(const Policy P, int tiles_m, int tiles_n) {
   constexpr int BM = QSM * HM, BN = QSN * HN;
   constexpr int AS_PITCH = BM + 4;  // floats; keeps 16-byte alignment, spreads the transposing stores
   constexpr int RN = 4 * HN;        // columns per thread
-  static_assert(BM % (THREADS / 4) == 0 && BK % (THREADS / (BN / 4)) == 0, "the tile loaders cover whole passes");
+  static_assert((BM % (THREADS / 4) == 0 || BM < THREADS / 4) && BK % (THREADS / (BN / 4)) == 0,
+                "the tile loaders cover whole passes (or, for A, part of one)");
   static_assert(!Policy::kTransposedB || BN % (THREADS / 4) == 0, "so does the register route of a transposed B");
   constexpr int BS_PITCH = Policy::kTransposedB ? BN + 4 : BN;  // the transposing stores want the same skew as A's
   // Shared-memory ring of STAGES k-tiles; operands of the next STAGES - 1 tiles are in flight (A in
@@ -190,7 +192,8 @@ tile_kernel(const Policy P, int tiles_m, int tiles_n) {
   // global -> register staging coordinates
   // A tile: BM rows x 16 k.  thread -> rows tid/4 (+ THREADS/4 per pass), k quad (tid%4)*4
   const int a_row = tid >> 2, a_kq = (tid & 3) * 4;
-  constexpr int A_RSTEP = THREADS / 4, PA = BM / A_RSTEP;  // passes over the A tile
+  constexpr int A_RSTEP = THREADS / 4, PA = (BM + A_RSTEP - 1) / A_RSTEP;  // passes over the A tile
+  constexpr bool A_PART = BM < A_RSTEP;  // a tile with fewer rows than one pass covers: some threads load no A
   // B tile: 16 k x BN cols = 16 * BN/4 column quads, PB per thread
   constexpr int QPR = BN / 4;  // quads per k row
   const int b_k = tid / QPR, b_c4 = (tid % QPR) * 4;
@@ -215,7 +218,8 @@ tile_kernel(const Policy P, int tiles_m, int tiles_n) {
     constexpr int S = decltype(set)::value;
     if (live) {
 #pragma unroll
-      for (int h = 0; h < PA; h++) pa[S][h] = P.load_a(rc[h], m0 + a_row + h * A_RSTEP, ka);
+      for (int h = 0; h < PA; h++)
+        if (!A_PART || a_row < BM) pa[S][h] = P.load_a(rc[h], m0 + a_row + h * A_RSTEP, ka);
       if constexpr (Policy::kTransposedB) {
 #pragma unroll
         for (int h = 0; h < PBT; h++) pbt[S][h] = P.load_bt(n0 + a_row + h * A_RSTEP, ka);
@@ -246,6 +250,7 @@ tile_kernel(const Policy P, int tiles_m, int tiles_n) {
 #pragma unroll
     for (int h = 0; h < PA; h++) {
       const int r = a_row + h * A_RSTEP;
+      if (A_PART && r >= BM) continue;
       As[buf][a_kq + 0][r] = pa[S][h].x;
       As[buf][a_kq + 1][r] = pa[S][h].y;
       As[buf][a_kq + 2][r] = pa[S][h].z;
@@ -424,6 +429,9 @@ constexpr TileConfig kTileConfigs[] = {
     // they hide each other's latency (256^3: 9.4 -> 7.7 us); from two CTAs per SM on, the shared-memory
     // pipe is the limit (ncu on 512^3: 76 % of its peak while active) and the 4 x 4 threads win.
     {3224, 32, 32, 4, {18.f, 28.5f, 43.f, 56.5f}},
+    // 16 x 64, 128 threads, 2 x 4 outputs each: problems of up to 16 rows, which leave half of a 32-row tile
+    // empty (16 x 16384 x 512: 18.8 against 22.6 us on 32 x 32 tiles; 16 x 32768 x 512: 33.1 against 39.9)
+    {1664, 16, 64, 4, {21.f, 30.f, 44.f, 58.f}},
 };
 
 // Predicted ns per k step of the slowest SM for `tiles` CTAs of configuration c.
@@ -448,6 +456,7 @@ cudaError_t launch_tiles(cudaStream_t stream, const Policy& P, int sm_count = 14
     double best = 0;
     for (const TileConfig& c : kTileConfigs) {
       if (c.bn > 64 && P.N <= 64) continue;  // a 128-wide tile would be half empty
+      if (c.bm == 16 && P.M > 16) continue;   // measured only where it is meant for
       const double t = predicted_ns_per_k(c, count_tiles(P, c.bm, c.bn), sm_count);
       if (tile == 0 || t < best) best = t, tile = c.id;
     }
@@ -457,6 +466,7 @@ cudaError_t launch_tiles(cudaStream_t stream, const Policy& P, int sm_count = 14
   if (tile == 6464) return launch_tiles_h<Policy, 4, 2, 16, 8>(stream, P);    // 64 x 64, 128 threads, 4 x 8 per thread
   if (tile == 64) return launch_tiles_h<Policy, 4, 1, 16, 16>(stream, P);
   if (tile == 3224) return launch_tiles_h<Policy, 2, 1, 16, 8>(stream, P);  // 32 x 32, 128 threads, 2 x 4 per thread
+  if (tile == 1664) return launch_tiles_h<Policy, 2, 1, 8, 16>(stream, P);  // 16 x 64, 128 threads, 2 x 4 per thread
   return launch_tiles_h<Policy, 4, 1, 8, 8>(stream, P);
 }
 
