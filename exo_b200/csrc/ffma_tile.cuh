@@ -54,7 +54,8 @@ constexpr int BK = 16;
 //   16 x 16 threads, 4 x 4 each ->  64 x  64, 256 threads;
 //    8 x  8 threads, 4 x 4 each ->  32 x  32,  64 threads, and
 //   16 x  8 threads, 2 x 4 each ->  32 x  32, 128 threads, and
-//    8 x 16 threads, 2 x 4 each ->  16 x  64, 128 threads (at most 16 rows): small problems.  Those are bound by the latency
+//    8 x 16 threads, 2 x 4 each ->  16 x  64, 128 threads (at most 16 rows), and
+//    4 x 32 threads, 2 x 4 each ->   8 x 128, 128 threads (at most 8 rows): small problems.  Those are bound by the latency
 //     of one warp's k loop, so spreading the same warps over more SMs (one or two per scheduler instead
 //     of four) is what shortens them.
 // launch_tiles() picks among them with a measured cost table.
@@ -432,6 +433,8 @@ constexpr TileConfig kTileConfigs[] = {
     // 16 x 64, 128 threads, 2 x 4 outputs each: problems of up to 16 rows, which leave half of a 32-row tile
     // empty (16 x 16384 x 512: 18.8 against 22.6 us on 32 x 32 tiles; 16 x 32768 x 512: 33.1 against 39.9)
     {1664, 16, 64, 4, {21.f, 30.f, 44.f, 58.f}},
+    // 8 x 128, 128 threads, 2 x 4 outputs each: at most 8 rows (8 x 32768 x 512: 19.4 us; 30.8 on 16 x 64 tiles)
+    {8128, 8, 128, 4, {21.f, 30.f, 44.f, 58.f}},
 };
 
 // Predicted ns per k step of the slowest SM for `tiles` CTAs of configuration c.
@@ -456,7 +459,7 @@ cudaError_t launch_tiles(cudaStream_t stream, const Policy& P, int sm_count = 14
     double best = 0;
     for (const TileConfig& c : kTileConfigs) {
       if (c.bn > 64 && P.N <= 64) continue;  // a 128-wide tile would be half empty
-      if (c.bm == 16 && P.M > 16) continue;   // measured only where it is meant for
+      if (c.bm <= 16 && P.M > c.bm) continue;  // measured only where they are meant for
       const double t = predicted_ns_per_k(c, count_tiles(P, c.bm, c.bn), sm_count);
       if (tile == 0 || t < best) best = t, tile = c.id;
     }
@@ -467,6 +470,7 @@ cudaError_t launch_tiles(cudaStream_t stream, const Policy& P, int sm_count = 14
   if (tile == 64) return launch_tiles_h<Policy, 4, 1, 16, 16>(stream, P);
   if (tile == 3224) return launch_tiles_h<Policy, 2, 1, 16, 8>(stream, P);  // 32 x 32, 128 threads, 2 x 4 per thread
   if (tile == 1664) return launch_tiles_h<Policy, 2, 1, 8, 16>(stream, P);  // 16 x 64, 128 threads, 2 x 4 per thread
+  if (tile == 8128) return launch_tiles_h<Policy, 2, 1, 4, 32>(stream, P);  // 8 x 128, 128 threads, 2 x 4 per thread
   return launch_tiles_h<Policy, 4, 1, 8, 8>(stream, P);
 }
 

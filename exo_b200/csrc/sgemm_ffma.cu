@@ -716,7 +716,7 @@ cudaError_t launch_sgemm_ffma(exo_b200_Context* ctx, int64_t M, int64_t N, int64
     return cudaGetLastError();
   }
   // The skinny kernel (a CTA per 64 columns, all rows) only beats the tile engine when there are very few rows
-  // and enough columns for every SM: 8 x 32768 x 512 31.8 against 38.8 us.  From a dozen rows on the tile
+  // and enough columns for every SM.  From a dozen rows on the tile
   // engine's 32 x 32 tiles win although most of their rows are padding, because they give the machine two to
   // four times the CTAs: 17 x 4099 x 513 18.2 against 21.6 us, 32 x 8192 x 512 18.5 against 22.4,
   // 24 x 4096 x 1024 28.6 against 38.4, 32 x 2048 x 2048 55.6 against 86.2 (12 x 1000 x 700: a tie).
@@ -724,7 +724,10 @@ cudaError_t launch_sgemm_ffma(exo_b200_Context* ctx, int64_t M, int64_t N, int64
     const char* e = getenv("EXOB200_SKINNY_MAX_M");  // rows up to which the skinny kernel is used (timing experiments)
     return e ? atoi(e) : 8;
   }();
-  if (M <= skinny_max_m && (N >= 8192 || skinny_max_m != 8)) {
+  // ... and beyond 16384 columns the engine's 8 x 128 tiles take over (8 x 32768 x 512: 19.4 against 31.9 us,
+  // 6 x 65536 x 256: 18.7 against 31.6; at 8192 columns the skinny kernel still wins, 12.5 against 15.4,
+  // and 83.9 against 108.7 us at K = 4096)
+  if (M <= skinny_max_m && ((N >= 8192 && N <= 16384) || skinny_max_m != 8)) {
 #define EXOB200_SKINNY(VB_, RPT_)                                                                            \
   {                                                                                                        \
     dim3 grid((unsigned)((N + SK_W - 1) / SK_W), (unsigned)((M + 8 * RPT_ - 1) / (8 * RPT_)));             \

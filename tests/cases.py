@@ -17,7 +17,8 @@ SGEMM_CASES = [
 SGEMM_EXTRA_CASES = [(1500, 8, 515), (2048, 16, 64), (1025, 13, 130), (3000, 1, 33), (20000, 5, 40), (4, 512, 300), (2, 8192, 1024), (3, 70, 1000), (4, 33, 31), (2, 4099, 97), (5, 64, 40), (32, 100, 513), (64, 64, 64), (65, 129, 17),
                      (1, 6404, 700), (2, 7000, 515),
                      (8, 8192, 300), (5, 8196, 129), (7, 8193, 65),
-                     (1100, 11, 77), (1024, 12, 64)]  # + the tall kernel with three column quads  # + the skinny kernel (a handful of rows, >= 8192 columns)  # the TMA-fed GEMV kernel with a partial last strip and a ragged K tail
+                     (1100, 11, 77), (1024, 12, 64),
+                     (8, 32768, 70), (6, 40001, 33), (16, 16384, 40), (13, 70, 90)]  # the engine's 8- and 16-row tiles  # + the tall kernel with three column quads  # + the skinny kernel (a handful of rows, >= 8192 columns)  # the TMA-fed GEMV kernel with a partial last strip and a ragged K tail
 # large outputs are held as SHA-256 + a strided sample: the remaining shapes of the fp32 shape sweep
 SGEMM_DIGEST_CASES = [(1000, 1000, 1000), (1024, 1024, 1024), (512, 512, 512), (2048, 2048, 2048),
                       (4096, 64, 4096), (1, 8192, 8192)]

@@ -54,7 +54,7 @@ def test_bf16_kernel_variant_against_reference_sgemm(variant, shape):
 
 # The exact-fp32 engine's tile configurations (the default dispatch picks one per shape from a cost table;
 # here each is forced onto the same ragged shape: M, N and K off every tile size, several tiles each way).
-FFMA_TILES = ["128", "12864", "6464", "64", "32", "3224", "1664"]
+FFMA_TILES = ["128", "12864", "6464", "64", "32", "3224", "1664", "8128"]
 
 
 @pytest.mark.parametrize("scalar", ["0", "1"])
