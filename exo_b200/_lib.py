@@ -58,6 +58,7 @@ SUPPORT = {
     "exo_b200_synchronize": ([vp], ctypes.c_int),
     "exo_b200_selftest_bounded_wait": ([vp, ctypes.c_int], ctypes.c_int),
     "exo_b200_measure_peak": ([ctypes.c_int, ctypes.c_int], ctypes.c_double),
+    "exo_b200_sgemm_kernel_choice": ([i64, i64, i64], ctypes.c_int),
     "exo_b200_last_error": ([], ctypes.c_int),
     "exo_b200_last_error_string": ([], ctypes.c_char_p),
     "exo_b200_version": ([], ctypes.c_char_p),

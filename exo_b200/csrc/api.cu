@@ -526,6 +526,22 @@ void tiled_conv_auto(int batch_size, int in_row_dim, int in_col_dim, int in_chan
                    in_channels, in_row_dim, output, bias, input, weights, act_, &c_scale);
 }
 
+int exo_b200_sgemm_kernel_choice(int_fast32_t M, int_fast32_t N, int_fast32_t K) {
+  if (M < 1 || N < 1 || K < 1 || M > INT32_MAX || N > INT32_MAX || K > INT32_MAX) return -1;
+  const int plan = sgemm_ffma_plan(M, N, K, K % 4 == 0, N % 4 == 0);
+  if (plan <= EXO_B200_SGEMM_SKINNY) return plan;
+  int rows = plan, cols = plan;  // square configurations are named by their edge
+  switch (plan) {
+    case 12864: rows = 128, cols = 64; break;
+    case 6464: rows = cols = 64; break;
+    case 3224: rows = cols = 32; break;
+    case 1664: rows = 16, cols = 64; break;
+    case 8128: rows = 8, cols = 128; break;
+    default: break;
+  }
+  return EXO_B200_SGEMM_TILES + 1000 * rows + cols;
+}
+
 int exo_b200_selftest_bounded_wait(exo_b200_Context* ctxt, int limit_us) {
   clear_error();
   ContextUse use(resolve_context(ctxt));

@@ -446,24 +446,29 @@ inline double predicted_ns_per_k(const TileConfig& c, int64_t tiles, int sm_coun
   return t;
 }
 
+// The configuration (TileConfig::id) launch_tiles uses for this problem.
 template <class Policy>
-cudaError_t launch_tiles(cudaStream_t stream, const Policy& P, int sm_count = 148) {
+int choose_tile(const Policy& P, int sm_count = 148) {
   static const int force = [] {
     const char* e = getenv("EXOB200_FFMA_TILE");  // a TileConfig id forces a tile size (timing experiments)
     return e ? atoi(e) : 0;
   }();
-  int tile = 0;
   for (const TileConfig& c : kTileConfigs)
-    if (force == c.id) tile = force;
-  if (tile == 0) {
-    double best = 0;
-    for (const TileConfig& c : kTileConfigs) {
-      if (c.bn > 64 && P.N <= 64) continue;  // a 128-wide tile would be half empty
-      if (c.bm <= 16 && P.M > c.bm) continue;  // measured only where they are meant for
-      const double t = predicted_ns_per_k(c, count_tiles(P, c.bm, c.bn), sm_count);
-      if (tile == 0 || t < best) best = t, tile = c.id;
-    }
+    if (force == c.id) return force;
+  int tile = 0;
+  double best = 0;
+  for (const TileConfig& c : kTileConfigs) {
+    if (c.bn > 64 && P.N <= 64) continue;    // a 128-wide tile would be half empty
+    if (c.bm <= 16 && P.M > c.bm) continue;  // measured only where they are meant for
+    const double t = predicted_ns_per_k(c, count_tiles(P, c.bm, c.bn), sm_count);
+    if (tile == 0 || t < best) best = t, tile = c.id;
   }
+  return tile;
+}
+
+template <class Policy>
+cudaError_t launch_tiles(cudaStream_t stream, const Policy& P, int sm_count = 148) {
+  const int tile = choose_tile(P, sm_count);
   if (tile == 128) return launch_tiles_h<Policy, 8, 2, 16, 16>(stream, P);
   if (tile == 12864) return launch_tiles_h<Policy, 8, 2, 16, 8>(stream, P);
   if (tile == 6464) return launch_tiles_h<Policy, 4, 2, 16, 8>(stream, P);    // 64 x 64, 128 threads, 4 x 8 per thread

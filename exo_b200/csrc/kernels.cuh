@@ -14,6 +14,8 @@ cudaError_t launch_sgemm_ffma(exo_b200_Context* ctx, int64_t M, int64_t N, int64
 
 // C += A * A^T on the upper triangle (ssyrk_ffma.cu); the 3xTF32 variant is in tc_gemm.cu
 cudaError_t launch_ssyrk_ffma(exo_b200_Context* ctx, int64_t N, int64_t K, const float* A, float* C);
+// which kernel launch_sgemm_ffma takes: 1 tall, 2 TMA GEMV, 3 cp.async GEMV, 4 skinny, else the tile configuration id
+int sgemm_ffma_plan(int64_t M, int64_t N, int64_t K, bool va, bool vb);
 cudaError_t launch_ssyrk_3xtf32_tc(exo_b200_Context* ctx, int64_t N, int64_t K, const float* A, float* C);
 
 struct ConvShape {

@@ -662,13 +662,42 @@ cudaError_t launch_tall(int device, cudaStream_t stream, int M, int N, int K, co
 
 }  // namespace
 
+namespace {
+int skinny_max_rows() {
+  static const int n = [] {
+    const char* e = getenv("EXOB200_SKINNY_MAX_M");  // rows up to which the skinny kernel is used (timing experiments)
+    return e ? atoi(e) : 8;
+  }();
+  return n;
+}
+bool gemv_tma_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("EXOB200_GEMV_TMA");  // =0: use the cp.async ring instead (timing experiments)
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
+}  // namespace
+
+// Which kernel the exact SGEMM takes for a shape (va / vb: 16-byte aligned operands with K % 4 == 0 / N % 4 == 0):
+// 1 tall, 2 TMA-fed GEMV, 3 cp.async GEMV, 4 skinny, otherwise the tile engine's configuration id.
+int sgemm_ffma_plan(int64_t M, int64_t N, int64_t K, bool va, bool vb) {
+  (void)va;
+  if (N <= 16 && M >= 1024) return 1;
+  if (gemv_tma_enabled() && M <= 2 && vb && K >= 512) return 2;
+  if (M <= 4) return 3;
+  if (M <= skinny_max_rows() && ((N >= 8192 && N <= 16384) || skinny_max_rows() != 8)) return 4;
+  return ffma::choose_tile(SgemmPolicy<true, true>{(int)M, (int)N, (int)K, nullptr, nullptr, nullptr});
+}
+
 cudaError_t launch_sgemm_ffma(exo_b200_Context* ctx, int64_t M, int64_t N, int64_t K, const float* A,
                               const float* B, float* C) {
   cudaStream_t stream = ctx->stream;
   if (M > INT32_MAX || N > INT32_MAX || K > INT32_MAX) return cudaErrorInvalidValue;
   const bool va = (K % 4 == 0) && ffma::aligned16(A);
   const bool vb = (N % 4 == 0) && ffma::aligned16(B) && ffma::aligned16(C);
-  if (N <= 16 && M >= 1024) {  // wider rows reuse too little of each B fragment here; the tile kernel takes them
+  const int plan = sgemm_ffma_plan(M, N, K, va, vb);
+  if (plan == 1) {  // wider rows reuse too little of each B fragment here; the tile kernel takes them
     const int a_vec = va ? 1 : 0, b_vec = vb ? 1 : 0;
     const int m = (int)M, n = (int)N, k = (int)K;
     switch ((n + 3) / 4) {
@@ -678,11 +707,7 @@ cudaError_t launch_sgemm_ffma(exo_b200_Context* ctx, int64_t M, int64_t N, int64
       default: return launch_tall<4>(ctx->device, stream, m, n, k, A, B, C, a_vec, b_vec);
     }
   }
-  static const bool gemv_tma = [] {
-    const char* e = getenv("EXOB200_GEMV_TMA");  // =0: use the cp.async ring instead (timing experiments)
-    return !(e && e[0] == '0');
-  }();
-  if (gemv_tma && M <= 2 && vb && K >= 512) {
+  if (plan == 2) {
     const int W = (N + 63) / 64 >= 200 ? 64 : 32;
     CUtensorMap mb;
     cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)K};
@@ -704,7 +729,7 @@ cudaError_t launch_sgemm_ffma(exo_b200_Context* ctx, int64_t M, int64_t N, int64
 #undef EXOB200_GEMV
     return cudaGetLastError();
   }
-  if (M <= 4) {
+  if (plan == 3) {
     const unsigned grid = (unsigned)((N + GV_W - 1) / GV_W);
     if (vb) {
       EXOB200_SMEM_ATTR_ONCE(sgemm_gemv_kernel<true>, GV_SMEM, ctx->device);
@@ -720,14 +745,7 @@ cudaError_t launch_sgemm_ffma(exo_b200_Context* ctx, int64_t M, int64_t N, int64
   // engine's 32 x 32 tiles win although most of their rows are padding, because they give the machine two to
   // four times the CTAs: 17 x 4099 x 513 18.2 against 21.6 us, 32 x 8192 x 512 18.5 against 22.4,
   // 24 x 4096 x 1024 28.6 against 38.4, 32 x 2048 x 2048 55.6 against 86.2 (12 x 1000 x 700: a tie).
-  static const int skinny_max_m = [] {
-    const char* e = getenv("EXOB200_SKINNY_MAX_M");  // rows up to which the skinny kernel is used (timing experiments)
-    return e ? atoi(e) : 8;
-  }();
-  // ... and beyond 16384 columns the engine's 8 x 128 tiles take over (8 x 32768 x 512: 19.4 against 31.9 us,
-  // 6 x 65536 x 256: 18.7 against 31.6; at 8192 columns the skinny kernel still wins, 12.5 against 15.4,
-  // and 83.9 against 108.7 us at K = 4096)
-  if (M <= skinny_max_m && ((N >= 8192 && N <= 16384) || skinny_max_m != 8)) {
+  if (plan == 4) {
 #define EXOB200_SKINNY(VB_, RPT_)                                                                            \
   {                                                                                                        \
     dim3 grid((unsigned)((N + SK_W - 1) / SK_W), (unsigned)((M + 8 * RPT_ - 1) / (8 * RPT_)));             \

@@ -258,6 +258,15 @@ enum { EXO_B200_PEAK_FP32_SIMT = 0, EXO_B200_PEAK_INT8_TENSOR = 1, EXO_B200_PEAK
        EXO_B200_PEAK_TF32_TENSOR = 3 };
 double exo_b200_measure_peak( int what, int milliseconds );
 
+/* Which kernel sgemm_exo_ffma takes for a problem whose operands are 16-byte aligned (no counterpart in the
+ * reference; needs no GPU): EXO_B200_SGEMM_TALL / _GEMV_TMA / _GEMV / _SKINNY for the kernels that serve few
+ * columns or few rows, otherwise the tile engine's configuration as 1000 * tile_rows + tile_cols plus
+ * EXO_B200_SGEMM_TILES (e.g. 128064 + EXO_B200_SGEMM_TILES for 128 x 64 tiles); two 64 x 64 and two 32 x 32
+ * configurations differ in threads per tile and report the same value.  -1 for sizes below 1. */
+enum { EXO_B200_SGEMM_TALL = 1, EXO_B200_SGEMM_GEMV_TMA = 2, EXO_B200_SGEMM_GEMV = 3, EXO_B200_SGEMM_SKINNY = 4,
+       EXO_B200_SGEMM_TILES = 1000000 };
+int exo_b200_sgemm_kernel_choice( int_fast32_t M, int_fast32_t N, int_fast32_t K );
+
 /* Error of the most recent call on this thread (EXO_B200_OK if it succeeded). */
 int exo_b200_last_error( void );
 const char* exo_b200_last_error_string( void );

@@ -121,6 +121,31 @@ def test_invalid_arguments_are_reported_not_computed(built):
     assert not C.any()
 
 
+def test_sgemm_kernel_choice_is_pinned(built):
+    """The exact SGEMM's dispatch (host logic, no GPU needed): the special kernels for few rows or columns and
+    the tile configuration the measured cost table picks for the shapes it was fitted on.  A change of the
+    table or of a threshold that moves one of these has to be a decision, not an accident."""
+    import exo_b200
+
+    f = exo_b200.library().dll.exo_b200_sgemm_kernel_choice
+    tiles = lambda r, c: 1000000 + 1000 * r + c
+    expected = {
+        (32768, 8, 512): 1, (16384, 16, 512): 1, (1024, 16, 64): 1,          # tall kernel
+        (1, 8192, 8192): 2, (2, 8192, 1024): 2,                              # TMA-fed GEMV
+        (1, 8192, 300): 3, (3, 100, 100): 3, (4, 512, 300): 3, (1, 8193, 8192): 3,  # cp.async GEMV
+        (8, 8192, 512): 4, (5, 16384, 1024): 4,                              # skinny kernel
+        (8, 32768, 512): tiles(8, 128), (6, 65536, 256): tiles(8, 128),
+        (16, 16384, 512): tiles(16, 64), (12, 1000, 700): tiles(32, 32), (17, 4099, 513): tiles(32, 32),
+        (256, 256, 256): tiles(32, 32), (512, 512, 512): tiles(32, 32), (4096, 64, 4096): tiles(32, 32),
+        (1024, 1024, 1024): tiles(128, 64), (1000, 1000, 1000): tiles(128, 64), (1536, 1536, 1536): tiles(128, 64),
+        (1088, 1088, 1088): tiles(64, 64), (1280, 1280, 1280): tiles(64, 64),
+        (2048, 2048, 2048): tiles(128, 128), (8192, 8192, 8192): tiles(128, 128),
+    }
+    got = {shape: f(*shape) for shape in expected}
+    assert got == expected
+    assert f(0, 4, 4) == -1 and f(4, 4, -1) == -1
+
+
 def test_no_cpu_fallback_without_a_device(built):
     """On a machine without a GPU a valid call must fail loudly, not compute."""
     import torch
